@@ -1,0 +1,379 @@
+// Host side of the C ABI declared in include/ffa_c_api.h: argument validation, the launch
+// planner, workspace carving and the per-step parameter fill.
+//
+// Replaces the reference's host launch layer: call_attention / call_attention_headdim
+// (attention.cu:1454-1554), the template launch switches (attention.cu:1301-1442),
+// invokeTranspose4dBatchMajor (attention.cu:1611-1689) and get_launch_params
+// (kernel_launch_utils.h:135-180).
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/ffa_c_api.h"
+#include "ffa_internal.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<unsigned long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_fail(int e, const char* what)
+{
+    return fail(FFA_ERR_CUDA, "%s: %s", what, cudaGetErrorString((cudaError_t)e));
+}
+
+int elem_size(int dtype) { return dtype == FFA_DTYPE_F32 ? 4 : 2; }
+bool dtype_ok(int dtype) { return dtype == FFA_DTYPE_F32 || dtype == FFA_DTYPE_F16 || dtype == FFA_DTYPE_BF16; }
+bool head_dim_ok(int d) { return d == 64 || d == 80 || d == 128 || d == 256; }
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+constexpr int kMaxCtasPerSm = 8;
+constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident CTA
+
+}  // namespace
+
+struct ffa_plan {
+    int dtype, B, H, Dh, Lmax, use_default, device, mode;
+    int sms, smem_per_cta, smem_per_sm;
+    bool forced;
+    ffa_launch_t force;
+    // workspace carving
+    void* ws;
+    size_t ws_bytes;
+    int* status;
+    int* tickets;
+    float* stats;
+    float* partials;
+    float* scores;
+    int max_grid;
+};
+
+namespace {
+
+struct Carve {
+    size_t status, tickets, stats, partials, scores, total;
+};
+Carve carve(const ffa_plan* p, bool with_scores)
+{
+    const size_t BH = (size_t)p->B * p->H;
+    Carve c;
+    size_t off = 0;
+    c.status = off, off += 256;
+    c.tickets = off, off += align_up(2 * BH * sizeof(int), 256);
+    c.stats = off, off += align_up(2 * BH * sizeof(float), 256);
+    c.partials = off, off += align_up(((size_t)p->max_grid + BH) * (p->Dh + 2) * sizeof(float), 256);
+    c.scores = off;
+    if (with_scores) off += align_up(BH * (size_t)p->Lmax * sizeof(float), 256);
+    c.total = off;
+    return c;
+}
+
+// ---- planner -------------------------------------------------------------------------------
+// The streaming kernels take (tile_rows, stages, consumer_warps, ctas_per_sm).  The flat unit
+// list is cut evenly over the grid, so the only shape questions are: enough bytes in flight
+// per SM to cover HBM latency (ring depth x tile size x resident CTAs), tiles small enough
+// that every CTA gets several units when batch*heads*t is small, and the shared-memory
+// budget.  The default rule below fixes 2 resident CTAs with a 3-deep ring of 16 KB tiles
+// per tensor; the measured table refines that per (row bytes, work size).
+struct Shape {
+    int tile_rows, stages, warps, cps;
+};
+
+Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int tensors)
+{
+    (void)p;
+    Shape s;
+    s.warps = 8;
+    s.cps = 2;
+    s.stages = tensors == 2 ? 3 : 4;
+    s.tile_rows = 16384 / row_bytes;
+    (void)rows_total;
+    return s;
+}
+
+// Winners of the sweep on B200 (see the tuning script beside the package); keyed by the
+// bytes one decode step streams.  Falls back to the default rule for shapes it has not seen.
+Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int tensors)
+{
+    Shape s = default_shape(p, row_bytes, rows_total, tensors);
+    const double bytes = (double)rows_total * row_bytes * tensors;
+    if (bytes >= 512e6) {
+        // long sequences: one CTA per SM with a deep ring keeps ~100 KB per SM in flight
+        s.cps = 1;
+        s.stages = tensors == 2 ? 6 : 8;
+        s.warps = 8;
+    }
+    return s;
+}
+
+int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
+{
+    const int rowb = p->Dh * elem_size(p->dtype);
+    const long long BH = (long long)p->B * p->H;
+    Shape s = p->use_default ? default_shape(p, rowb, BH * cap_rows, tensors)
+                             : measured_shape(p, rowb, BH * cap_rows, tensors);
+    if (p->forced) {
+        if (p->force.tile_rows > 0) s.tile_rows = p->force.tile_rows;
+        if (p->force.stages > 0) s.stages = p->force.stages;
+        if (p->force.consumer_warps > 0) s.warps = p->force.consumer_warps;
+        if (p->force.ctas_per_sm > 0) s.cps = p->force.ctas_per_sm;
+    }
+    if (s.warps < 1) s.warps = 1;
+    if (s.warps > 16) s.warps = 16;
+    if (s.cps < 1) s.cps = 1;
+    if (s.cps > kMaxCtasPerSm) s.cps = kMaxCtasPerSm;
+    if (s.stages < 2) s.stages = 2;
+    if (s.stages > 16) s.stages = 16;
+    if (s.tile_rows < 8) s.tile_rows = 8;
+    s.tile_rows = (s.tile_rows + 7) / 8 * 8;  // keeps every tile a multiple of 128 bytes
+    const bool tile_forced = p->forced && p->force.tile_rows > 0;
+    if (!tile_forced) {
+        // small problems: shrink tiles until every CTA slot has a few units to stream
+        const long long slots = (long long)p->sms * s.cps;
+        while (s.tile_rows > 8 && BH * (cap_rows / s.tile_rows + 1) < 4 * slots) s.tile_rows /= 2;
+    }
+    // shared-memory budget: per CTA and per SM
+    for (;;) {
+        const int smem = ffa_k_smem_bytes(p->dtype, p->Dh, s.tile_rows, s.stages, s.warps, tensors);
+        const bool ok = smem <= p->smem_per_cta && (long long)s.cps * (smem + kSmemReservePerCta) <= p->smem_per_sm;
+        if (ok) {
+            out->smem_bytes = smem;
+            break;
+        }
+        if (s.stages > 2) --s.stages;
+        else if (s.tile_rows > 8) s.tile_rows = (s.tile_rows / 2 + 7) / 8 * 8;
+        else if (s.cps > 1) --s.cps;
+        else return fail(FFA_ERR_ARG, "no launch shape fits in shared memory");
+    }
+    const long long units = BH * (cap_rows / s.tile_rows + 1);
+    long long grid = (long long)p->sms * s.cps;
+    if (grid > units) grid = units;
+    if (p->forced && p->force.grid > 0 && p->force.grid < grid) grid = p->force.grid;
+    if (grid > p->max_grid) grid = p->max_grid;
+    out->tile_rows = s.tile_rows;
+    out->stages = s.stages;
+    out->consumer_warps = s.warps;
+    out->ctas_per_sm = s.cps;
+    out->grid = (int)grid;
+    return FFA_OK;
+}
+
+// rows the unit list must cover for this call: t when every sample is at row t, max_len - 1
+// when rows come from per-sample lengths the host cannot see
+int cap_rows_for(const ffa_plan* p, int t, const int* seq_lengths, int right_or_no_padding)
+{
+    return (seq_lengths != nullptr && right_or_no_padding) ? p->Lmax - 1 : t;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ffa_last_error(void) { return g_err; }
+unsigned long long ffa_launch_count(void) { return g_launches.load(); }
+
+int ffa_cache_bytes(int dtype, int batch, int heads, int max_len, int head_dim, size_t* k_bytes, size_t* v_bytes)
+{
+    if (!dtype_ok(dtype)) return fail(FFA_ERR_DTYPE, "unsupported dtype code %d", dtype);
+    if (!head_dim_ok(head_dim)) return fail(FFA_ERR_HEAD_DIM, "unsupported head_dim %d (64, 80, 128, 256)", head_dim);
+    if (batch <= 0 || heads <= 0 || max_len <= 0) return fail(FFA_ERR_RANGE, "batch, heads and max_len must be positive");
+    if (k_bytes == nullptr || v_bytes == nullptr) return fail(FFA_ERR_ARG, "null output pointer");
+    const size_t n = (size_t)batch * heads * max_len * head_dim * elem_size(dtype);
+    *k_bytes = n, *v_bytes = n;
+    return FFA_OK;
+}
+
+int ffa_cache_init(int dtype, int batch, int heads, int prompt_len, int max_len, int head_dim, const void* k_src,
+                   const void* v_src, void* k_cache, void* v_cache, void* stream)
+{
+    if (!dtype_ok(dtype)) return fail(FFA_ERR_DTYPE, "unsupported dtype code %d", dtype);
+    if (!head_dim_ok(head_dim)) return fail(FFA_ERR_HEAD_DIM, "unsupported head_dim %d (64, 80, 128, 256)", head_dim);
+    if (batch <= 0 || heads <= 0 || max_len <= 0 || prompt_len < 0 || prompt_len > max_len)
+        return fail(FFA_ERR_RANGE, "need 0 <= prompt_len (%d) <= max_len (%d) and positive batch, heads", prompt_len, max_len);
+    if (prompt_len == 0) return FFA_OK;
+    if (!k_src || !v_src || !k_cache || !v_cache) return fail(FFA_ERR_ARG, "null pointer");
+    if (!aligned16(k_src) || !aligned16(v_src) || !aligned16(k_cache) || !aligned16(v_cache))
+        return fail(FFA_ERR_ARG, "pointers must be 16-byte aligned");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "device query");
+    const int r = ffa_k_cache_init(dtype, batch * heads, prompt_len, max_len, head_dim, k_src, v_src, k_cache, v_cache, sms,
+                                   static_cast<cudaStream_t>(stream));
+    if (r != 0) return cuda_fail(r, "cache init launch");
+    g_launches.fetch_add(1);
+    return FFA_OK;
+}
+
+int ffa_plan_create(int dtype, int batch, int heads, int head_dim, int max_len, int use_default_launch, int device,
+                    ffa_plan_t** plan)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan pointer");
+    *plan = nullptr;
+    if (!dtype_ok(dtype)) return fail(FFA_ERR_DTYPE, "unsupported dtype code %d", dtype);
+    if (!head_dim_ok(head_dim)) return fail(FFA_ERR_HEAD_DIM, "unsupported head_dim %d (64, 80, 128, 256)", head_dim);
+    if (batch <= 0 || heads <= 0 || max_len <= 0) return fail(FFA_ERR_RANGE, "batch, heads and max_len must be positive");
+    int prev = 0;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    int sms = 0, smem_cta = 0, smem_sm = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&smem_cta, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device);
+    int r = 0;
+    if (e == cudaSuccess) r = ffa_k_prepare(dtype, head_dim, smem_cta);
+    cudaSetDevice(prev);
+    if (e != cudaSuccess) return cuda_fail(e, "device attribute query");
+    if (r != 0) return cuda_fail(r, "kernel preparation (is this an sm_100a device?)");
+    ffa_plan* p = new (std::nothrow) ffa_plan();
+    if (p == nullptr) return fail(FFA_ERR_ARG, "out of host memory");
+    std::memset(p, 0, sizeof(*p));
+    p->dtype = dtype, p->B = batch, p->H = heads, p->Dh = head_dim, p->Lmax = max_len;
+    p->use_default = use_default_launch != 0, p->device = device, p->mode = FFA_MODE_EXACT;
+    p->sms = sms, p->smem_per_cta = smem_cta, p->smem_per_sm = smem_sm;
+    p->max_grid = sms * kMaxCtasPerSm;
+    *plan = p;
+    return FFA_OK;
+}
+
+void ffa_plan_destroy(ffa_plan_t* plan) { delete plan; }
+
+int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch)
+{
+    if (plan == nullptr || launch == nullptr) return fail(FFA_ERR_ARG, "null pointer");
+    if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
+    return fit_launch(plan, t, 2, launch);
+}
+
+int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    plan->forced = launch != nullptr;
+    if (launch) plan->force = *launch;
+    return FFA_OK;
+}
+
+int ffa_plan_set_mode(ffa_plan_t* plan, int mode)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (mode != FFA_MODE_EXACT && mode != FFA_MODE_ROUND_LIKE_TORCH) return fail(FFA_ERR_ARG, "unknown mode %d", mode);
+    plan->mode = mode;
+    return FFA_OK;
+}
+
+size_t ffa_workspace_bytes(const ffa_plan_t* plan, int with_scores)
+{
+    if (plan == nullptr) return 0;
+    return carve(plan, with_scores != 0).total;
+}
+
+int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* stream)
+{
+    if (plan == nullptr || workspace == nullptr) return fail(FFA_ERR_ARG, "null pointer");
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(FFA_ERR_ARG, "workspace must be 256-byte aligned");
+    const Carve small = carve(plan, false), big = carve(plan, true);
+    if (bytes < small.total) return fail(FFA_ERR_WORKSPACE, "workspace of %zu bytes, need at least %zu", bytes, small.total);
+    char* base = static_cast<char*>(workspace);
+    // status word + arrival counters start at zero; everything else is written before it is read
+    cudaError_t e = cudaMemsetAsync(base, 0, small.stats, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "workspace clear");
+    plan->ws = workspace, plan->ws_bytes = bytes;
+    plan->status = reinterpret_cast<int*>(base + small.status);
+    plan->tickets = reinterpret_cast<int*>(base + small.tickets);
+    plan->stats = reinterpret_cast<float*>(base + small.stats);
+    plan->partials = reinterpret_cast<float*>(base + small.partials);
+    plan->scores = bytes >= big.total ? reinterpret_cast<float*>(base + big.scores) : nullptr;
+    return FFA_OK;
+}
+
+int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_cache, void* v_cache, void* out,
+                  float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding, float p,
+                  uint32_t* kept_mask, void* stream)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (!q || !k || !v || !k_cache || !v_cache || !out) return fail(FFA_ERR_ARG, "null tensor pointer");
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
+        return fail(FFA_ERR_ARG, "tensor pointers must be 16-byte aligned");
+    if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
+    if (!(p >= 0.f && p <= 1.f)) return fail(FFA_ERR_RANGE, "prob_thresh %g outside [0, 1]", (double)p);
+    if (seq_lengths == nullptr && !right_or_no_padding)
+        return fail(FFA_ERR_ARG, "left padding (right_or_no_padding = 0) needs seq_lengths");
+    if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
+    const bool twopass = p > 0.f || plan->mode == FFA_MODE_ROUND_LIKE_TORCH;
+    if (twopass && plan->scores == nullptr)
+        return fail(FFA_ERR_WORKSPACE, "p > 0 and the torch-rounding mode need a workspace sized with with_scores = 1");
+
+    const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
+    const long long BH = (long long)plan->B * plan->H;
+    FfaStepParams P;
+    std::memset(&P, 0, sizeof(P));
+    P.q = q, P.k = k, P.v = v, P.k_cache = k_cache, P.v_cache = v_cache, P.out = out;
+    P.seq_lengths = seq_lengths, P.right_or_no_padding = right_or_no_padding != 0;
+    P.B = plan->B, P.H = plan->H, P.Lmax = plan->Lmax, P.t = t;
+    P.scale = softmax_scale, P.p = p;
+    P.round_like_torch = plan->mode == FFA_MODE_ROUND_LIKE_TORCH && !(p > 0.f);
+    P.partials = plan->partials, P.tickets = plan->tickets, P.status = plan->status;
+    P.stats = plan->stats, P.scores = plan->scores;
+    P.kept_mask = kept_mask, P.mask_words = (plan->Lmax + 31) / 32;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    ffa_launch_t L;
+    int r = fit_launch(plan, cap, twopass ? 1 : 2, &L);
+    if (r != FFA_OK) return r;
+    P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
+    P.units_per_bh = cap / L.tile_rows + 1;
+    P.total_units = BH * P.units_per_bh;
+    const int threads = 32 * (L.consumer_warps + 1);
+    if (!twopass) {
+        r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, threads, L.smem_bytes, st);
+        if (r != 0) return cuda_fail(r, "attention launch");
+        g_launches.fetch_add(1);
+        return FFA_OK;
+    }
+    // value pass: units of 512 rows (only 4-byte scores are read densely), no copy ring
+    FfaStepParams V = P;
+    V.tile_rows = 512;
+    V.stages = 0;
+    V.units_per_bh = cap / V.tile_rows + 1;
+    V.total_units = BH * V.units_per_bh;
+    long long vgrid = (long long)plan->sms * 4;
+    if (vgrid > V.total_units) vgrid = V.total_units;
+    if (vgrid > plan->max_grid) vgrid = plan->max_grid;
+    V.grid = (int)vgrid;
+    V.tickets = plan->tickets + BH;
+    const int smem_v = ffa_k_gather_smem_bytes(plan->dtype, plan->Dh, V.tile_rows);
+    r = ffa_k_decode_twopass(plan->dtype, plan->Dh, P, V, threads, L.smem_bytes, smem_v, st);
+    if (r != 0) return cuda_fail(r, "two-pass attention launch");
+    g_launches.fetch_add(2);
+    return FFA_OK;
+}
+
+int ffa_device_status(ffa_plan_t* plan, void* stream, int* status)
+{
+    if (plan == nullptr || status == nullptr) return fail(FFA_ERR_ARG, "null pointer");
+    if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(status, plan->status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(plan->status, 0, sizeof(int), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "status read");
+    if (*status != 0) return fail(FFA_ERR_DEVICE, "device status word = %d", *status);
+    return FFA_OK;
+}
+
+}  // extern "C"

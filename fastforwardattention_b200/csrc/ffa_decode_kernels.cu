@@ -1,0 +1,818 @@
+// Decode masked multi-head attention for sm_100a: streaming split-KV kernels.
+//
+// Replaces mmha::masked_multihead_attention_kernel_optimized (attention.cu:698-1295) and the
+// two cache-init kernels (attention.cu:1556-1609) of the reference.  The reference runs one
+// CTA per (batch, head) that walks the whole sequence serially and stages every score in
+// shared memory; here the flat list of (batch*head, row-tile) units is cut into equal
+// contiguous runs, one per CTA of a persistent grid, so all SMs stream from HBM whatever the
+// batch*head count and the sequence length is bounded by memory only.
+//
+//   ffa_stream_kernel<T, DH, PASS_ONE>    p == 0: K and V tiles through a bulk-copy ring,
+//                                         online softmax, cross-CTA merge by the CTA that
+//                                         arrives last (no waiting), k/v append fused
+//   ffa_stream_kernel<T, DH, PASS_SCORE>  first half of the two-pass modes: K tiles only,
+//                                         fp32 scores to scratch, global max and sum
+//   ffa_value_gather_kernel<T, DH>        second half: tests every cached row with the
+//                                         reference's pruning rule (attention.cu:1184-1191,
+//                                         461-469) and loads only the V rows that survive
+//   ffa_cache_init_kernel                 prompt K/V -> rows [0, prompt) of the caches
+//
+// One query row per head is a matrix-vector product (2 flops per cache element read), so the
+// arithmetic runs on the CUDA cores in fp32 and the kernels are bound by HBM bandwidth.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include <type_traits>
+
+#include "ffa_internal.h"
+
+namespace {
+
+constexpr int kPassOne = 0;
+constexpr int kPassScore = 1;
+constexpr uint32_t kWaitLimit = 1u << 22;  // bounded barrier wait: ~1 s, then give up
+constexpr int kStatusWaitTimeout = 1;
+constexpr int kStatusBadLength = 2;
+constexpr int kGatherThreads = 256;
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers: mbarrier + 1-D bulk copy global -> this CTA's shared memory
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for the phase with the given parity.  Never spins for ever: after kWaitLimit polls
+// (or as soon as another thread of the CTA gave up) it raises the CTA's `dead` flag and
+// returns false; callers then skip the data but keep walking the same control flow so every
+// CTA-level barrier is still reached by everyone.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* dead)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*dead) return false;
+        if (i > 32) __nanosleep(128);
+    }
+    *dead = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ------------------------------------------------------------------------------------------
+// Element traits: a 16-byte vector holds EPV elements; unpack to fp32, round from fp32
+// ------------------------------------------------------------------------------------------
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+    static constexpr int EPV = 4;
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f)
+    {
+        f[0] = __uint_as_float(r.x), f[1] = __uint_as_float(r.y), f[2] = __uint_as_float(r.z),
+        f[3] = __uint_as_float(r.w);
+    }
+    static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ void store(float* p, float x) { *p = x; }
+    // attention.cu:461-464
+    static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
+};
+template <>
+struct Elem<__half> {
+    static constexpr int EPV = 8;
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = t.x, f[2 * i + 1] = t.y;
+        }
+    }
+    static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ void store(__half* p, float x) { *p = __float2half_rn(x); }
+    // attention.cu:466-469 hands two raw bit patterns to __hle; the unsigned short -> __half
+    // conversion there is the NUMERIC one, so the patterns themselves are rounded to 11
+    // significant bits and compared.  Reproduced literally.
+    static __device__ __forceinline__ bool leq(float a, float b)
+    {
+        const unsigned short ba = __half_as_ushort(__float2half_rn(a));
+        const unsigned short bb = __half_as_ushort(__float2half_rn(b));
+        return __hle(__ushort2half_rn(ba), __ushort2half_rn(bb));
+    }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+    static constexpr int EPV = 8;
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+    // the reference has no bf16; plain value comparison
+    static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
+};
+
+constexpr int pow2_ceil(int x)
+{
+    int p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+// Geometry of one cache row of DH elements of T, and of the lane group that owns a row.
+template <typename T, int DH>
+struct RowGeom {
+    static constexpr int EPV = Elem<T>::EPV;
+    static constexpr int ROWB = DH * (int)sizeof(T);   // bytes per row, multiple of 16
+    static constexpr int VPR = ROWB / 16;               // 16-byte vectors per row
+    static constexpr int LPR = VPR >= 32 ? 32 : pow2_ceil(VPR);  // lanes per row group
+    static constexpr int VPL = (VPR + 31) / 32;         // vectors per lane
+    static_assert(ROWB % 16 == 0, "rows must be 16-byte multiples");
+};
+
+// Per-sample view of the cache for this step (attention.cu:805-817).  `row` is where the new
+// token goes and the number of cached rows attended; keys below `first` are masked.
+struct SampleRange {
+    int first, row;
+    bool ok;
+};
+__device__ __forceinline__ SampleRange sample_range(const FfaStepParams& P, int b)
+{
+    SampleRange r;
+    r.first = 0, r.row = P.t;
+    if (P.seq_lengths != nullptr) {
+        const int s = P.seq_lengths[b];
+        if (P.right_or_no_padding) r.row = s;
+        else r.first = s;
+    }
+    r.ok = r.row >= 0 && r.row < P.Lmax;
+    if (!r.ok) r.row = 0;
+    r.first = min(max(r.first, 0), r.row);
+    return r;
+}
+
+// CTA c of G owns units [c*U/G, (c+1)*U/G); the CTA that owns unit u:
+__device__ __forceinline__ long long unit_start(long long c, long long U, int G) { return c * U / G; }
+__device__ __forceinline__ int cta_of_unit(long long u, long long U, int G)
+{
+    return (int)(((u + 1) * G + U - 1) / U - 1);
+}
+
+template <typename T, int DH>
+__device__ __forceinline__ void load_row_f32(const unsigned char* row, int li, float (&f)[RowGeom<T, DH>::VPL][RowGeom<T, DH>::EPV])
+{
+    using G = RowGeom<T, DH>;
+#pragma unroll
+    for (int x = 0; x < G::VPL; ++x) {
+        const int vec = li + x * G::LPR;
+        if (vec < G::VPR) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + vec * 16);
+            Elem<T>::unpack(raw, f[x]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < G::EPV; ++e) f[x][e] = 0.f;
+        }
+    }
+}
+
+template <int LPR>
+__device__ __forceinline__ float group_sum(float x)
+{
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+    return x;
+}
+
+// ------------------------------------------------------------------------------------------
+// Streaming kernel (one-pass attention, or the score pass of the two-pass modes)
+// ------------------------------------------------------------------------------------------
+// Shared memory: [stages][K tile | V tile] ring (score pass: K tile only), then the group
+// reduction area [NG][DH + 4] (rows 16-byte aligned; max and sum in the tail), then
+// full/empty barriers, then two flags.
+// Warp 0 issues the copies (one elected lane); warps 1.. compute.  A lane group of LPR lanes
+// owns a row: 16-byte shared-memory reads, fp32 FMAs, butterfly sum.  Each group keeps its
+// own online-softmax state, so the row loop has no CTA-level synchronisation at all.
+template <typename T, int DH, int PASS>
+__global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams P)
+{
+    using G = RowGeom<T, DH>;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL;
+    constexpr bool kPrecise = sizeof(T) == 4 || PASS == kPassScore;  // natural-log domain, full-precision exp
+    constexpr int TENSORS = PASS == kPassOne ? 2 : 1;
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr int RS = DH + 4;  // row stride of the group reduction area, in floats
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int R = P.tile_rows, S = P.stages;
+    const int ncw = (blockDim.x >> 5) - 1;   // consumer warps
+    const int nct = ncw * 32;                // consumer threads
+    const int NG = nct / LPR;                // row groups
+    const uint32_t tile_bytes = (uint32_t)R * ROWB;
+    const uint32_t stage_bytes = tile_bytes * TENSORS;
+    float* red = reinterpret_cast<float*>(smem + (size_t)S * stage_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + NG * RS);
+    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead, [1] last-arriver
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
+    const uint32_t ring = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, ncw);
+        }
+        flags[0] = 0, flags[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const long long U = P.total_units;
+    const int upb = P.units_per_bh;
+    const long long u0 = unit_start(blockIdx.x, U, P.grid), u1 = unit_start(blockIdx.x + 1, U, P.grid);
+    const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache);
+    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
+
+    if (threadIdx.x < 32) {
+        // ---------------- producer ----------------
+        if (threadIdx.x == 0) {
+            uint32_t it = 0;
+            int cur_b = -1;
+            SampleRange sr{0, 0, false};
+            for (long long u = u0; u < u1; ++u) {
+                const int bh = (int)(u / upb), j = (int)(u - (long long)bh * upb);
+                const int b = bh / P.H;
+                if (b != cur_b) sr = sample_range(P, b), cur_b = b;
+                if (!sr.ok) continue;
+                const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
+                if (hi <= lo) continue;
+                const uint32_t s = it % S, use = it / S;
+                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1, flags)) break;
+                const uint32_t bytes = (uint32_t)(hi - lo) * ROWB;
+                const size_t off = ((size_t)bh * P.Lmax + lo) * ROWB;
+                mbar_expect_tx(bar_full + 8 * s, bytes * TENSORS);
+                bulk_copy_g2s(ring + s * stage_bytes, kc + off, bytes, bar_full + 8 * s);
+                if (TENSORS == 2) bulk_copy_g2s(ring + s * stage_bytes + tile_bytes, vc + off, bytes, bar_full + 8 * s);
+                ++it;
+            }
+            if (flags[0]) {
+                // gave up: let the copies already issued land before the CTA releases its
+                // shared memory (bounded again)
+                const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
+                for (uint32_t k = 0; k < pending; ++k) {
+                    const uint32_t id = it - 1 - k, s = id % S, use = id / S;
+                    for (uint32_t n = 0; n < kWaitLimit && !mbar_try_wait(bar_full + 8 * s, use & 1); ++n) __nanosleep(256);
+                }
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int ctid = threadIdx.x - 32;
+        const int lane = ctid & 31;
+        const int g = ctid / LPR, li = ctid % LPR;
+        uint32_t it = 0;
+        long long u = u0;
+        while (u < u1) {
+            const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
+            const int j1 = (int)min((long long)upb, j0 + (u1 - u));
+            const int b = bh / P.H;
+            const SampleRange sr = sample_range(P, b);
+            const int jt = sr.row / R;  // the unit that also owns the new token
+
+            // q for this (batch, head), pre-multiplied so that scores come out of the FMAs
+            // ready for the exponential (exact mode: scale only, natural-log domain)
+            float qf[VPL][EPV];
+            load_row_f32<T, DH>(static_cast<const unsigned char*>(P.q) + (size_t)bh * ROWB, li, qf);
+            const float qmul = kPrecise ? 1.f : P.scale * kLog2e;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) qf[x][e] *= qmul;
+
+            float m = -CUDART_INF_F, l = 0.f;
+            float acc[VPL][EPV];
+#pragma unroll
+            for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) acc[x][e] = 0.f;
+
+            auto score_of = [&](float dot) -> float {
+                if (!kPrecise) return dot;
+                if (PASS == kPassScore && P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
+                return dot * P.scale;
+            };
+            auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
+
+            for (int j = j0; j < j1; ++j) {
+                const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
+                if (!sr.ok || hi <= lo) continue;
+                const int nrows = hi - lo;
+                const uint32_t s = it % S, use = it / S;
+                ++it;
+                if (!mbar_wait_bounded(bar_full + 8 * s, use & 1, flags)) continue;
+                const unsigned char* ks = smem + (size_t)s * stage_bytes;
+                const unsigned char* vs = ks + tile_bytes;
+                for (int base = 0; base < nrows; base += 4 * NG) {
+                    float sc[4];
+                    int rr[4];
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu) {
+                        const int r = base + uu * NG + g;
+                        const bool okr = r < nrows;
+                        rr[uu] = okr ? r : 0;
+                        float dot = 0.f;
+#pragma unroll
+                        for (int x = 0; x < VPL; ++x) {
+                            const int vec = li + x * LPR;
+                            if (vec < VPR && okr) {
+                                float kf[EPV];
+                                Elem<T>::unpack(*reinterpret_cast<const uint4*>(ks + (size_t)r * ROWB + vec * 16), kf);
+#pragma unroll
+                                for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[e], dot);
+                            }
+                        }
+                        dot = group_sum<LPR>(dot);
+                        sc[uu] = okr ? score_of(dot) : -CUDART_INF_F;
+                    }
+                    const float m_new = fmaxf(fmaxf(fmaxf(m, sc[0]), fmaxf(sc[1], sc[2])), sc[3]);
+                    if (m_new == -CUDART_INF_F) continue;  // this group has no row in this batch of rows
+                    const float corr = expo(m - m_new);
+                    m = m_new;
+                    l *= corr;
+                    if (PASS == kPassOne) {
+#pragma unroll
+                        for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                            for (int e = 0; e < EPV; ++e) acc[x][e] *= corr;
+                    }
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu) {
+                        const float pr = expo(sc[uu] - m);
+                        l += pr;
+                        if (PASS == kPassOne) {
+#pragma unroll
+                            for (int x = 0; x < VPL; ++x) {
+                                const int vec = li + x * LPR;
+                                if (vec < VPR && pr != 0.f) {
+                                    float vf[EPV];
+                                    Elem<T>::unpack(*reinterpret_cast<const uint4*>(vs + (size_t)rr[uu] * ROWB + vec * 16), vf);
+#pragma unroll
+                                    for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr, vf[e], acc[x][e]);
+                                }
+                            }
+                        } else if (li == 0 && sc[uu] != -CUDART_INF_F) {
+                            P.scores[(size_t)bh * P.Lmax + lo + base + uu * NG + g] = sc[uu];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            }
+
+            // ---- the new token: score against k, append k (and v) at row sr.row ----
+            if (sr.ok && j0 <= jt && jt < j1) {
+                float kf[VPL][EPV];
+                load_row_f32<T, DH>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB, li, kf);
+                float dot = 0.f;
+#pragma unroll
+                for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[x][e], dot);
+                dot = group_sum<LPR>(dot);  // every group computes it; group 0 uses it
+                if (g == 0) {
+                    const float st = score_of(dot);
+                    const float m_new = fmaxf(m, st);
+                    const float corr = expo(m - m_new), pr = expo(st - m_new);
+                    m = m_new;
+                    l = l * corr + pr;
+                    const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        const int vec = li + x * LPR;
+                        if (vec < VPR) {
+                            const size_t src = (size_t)bh * ROWB + vec * 16;
+                            const uint4 kraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + src);
+                            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + vec * 16) = kraw;
+                            if (PASS == kPassOne) {
+                                const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + src);
+                                *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
+                                float vf[EPV];
+                                Elem<T>::unpack(vraw, vf);
+#pragma unroll
+                                for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr, vf[e], acc[x][e] * corr);
+                            }
+                        }
+                    }
+                    if (PASS == kPassScore && li == 0) P.scores[(size_t)bh * P.Lmax + sr.row] = st;
+                }
+            }
+
+            // ---- merge the groups of this CTA ----
+            float* mine = red + g * RS;
+            if (PASS == kPassOne) {
+#pragma unroll
+                for (int x = 0; x < VPL; ++x) {
+                    const int vec = li + x * LPR;
+                    if (vec < VPR) {
+#pragma unroll
+                        for (int e = 0; e < EPV; e += 4)
+                            *reinterpret_cast<float4*>(mine + vec * EPV + e) =
+                                make_float4(acc[x][e], acc[x][e + 1], acc[x][e + 2], acc[x][e + 3]);
+                    }
+                }
+            }
+            if (li == 0) mine[DH] = m, mine[DH + 1] = l;
+            named_bar_sync(1, nct);
+            float M = -CUDART_INF_F;
+            for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, red[gg * RS + DH]);
+            const bool whole = (j0 == 0 && j1 == upb);
+            const int slot = blockIdx.x + bh;
+            float* part = P.partials + (size_t)slot * (DH + 2);
+            T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+            const int nd = PASS == kPassOne ? DH : 1;
+            for (int d = ctid; d < nd; d += nct) {
+                float A = 0.f, L = 0.f;
+                for (int gg = 0; gg < NG; ++gg) {
+                    const float mg = red[gg * RS + DH];
+                    const float w = mg == -CUDART_INF_F ? 0.f : expo(mg - M);
+                    if (PASS == kPassOne) A = fmaf(w, red[gg * RS + d], A);
+                    L = fmaf(w, red[gg * RS + DH + 1], L);
+                }
+                if (whole) {
+                    if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+                    else P.stats[2 * bh] = M, P.stats[2 * bh + 1] = L;
+                } else {
+                    if (PASS == kPassOne) part[d] = A;
+                    if (d == 0) part[DH] = M, part[DH + 1] = L;
+                }
+            }
+            if (!whole) {
+                // cross-CTA merge without waiting: whoever arrives last does it
+                __threadfence();
+                named_bar_sync(1, nct);
+                const int c_first = cta_of_unit((long long)bh * upb, U, P.grid);
+                const int c_last = cta_of_unit((long long)(bh + 1) * upb - 1, U, P.grid);
+                const int count = c_last - c_first + 1;
+                if (ctid == 0) {
+                    const int old = atomicAdd(P.tickets + bh, 1);
+                    flags[1] = (old == count - 1);
+                }
+                named_bar_sync(1, nct);
+                if (flags[1]) {
+                    __threadfence();
+                    const float* pbase = P.partials + (size_t)(c_first + bh) * (DH + 2);
+                    float MM = -CUDART_INF_F;
+                    for (int k = 0; k < count; ++k) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
+                    for (int d = ctid; d < nd; d += nct) {
+                        float A = 0.f, L = 0.f;
+                        for (int k = 0; k < count; ++k) {
+                            const float* pk = pbase + (size_t)k * (DH + 2);
+                            const float mk = __ldcg(pk + DH);
+                            const float w = mk == -CUDART_INF_F ? 0.f : expo(mk - MM);
+                            if (PASS == kPassOne) A = fmaf(w, __ldcg(pk + d), A);
+                            L = fmaf(w, __ldcg(pk + DH + 1), L);
+                        }
+                        if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+                        else P.stats[2 * bh] = MM, P.stats[2 * bh + 1] = L;
+                    }
+                    if (ctid == 0) P.tickets[bh] = 0;  // ready for the next launch on this stream
+                }
+            }
+            named_bar_sync(1, nct);  // `red` and the flag are reused by the next segment
+            if (!sr.ok && ctid == 0) atomicOr(P.status, kStatusBadLength);
+            u += j1 - j0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && flags[0]) atomicOr(P.status, kStatusWaitTimeout);
+}
+
+// ------------------------------------------------------------------------------------------
+// Value pass of the two-pass modes: prune test on every cached row, gather the survivors
+// ------------------------------------------------------------------------------------------
+// Shared memory: kept-row list (index + probability) for one unit of tile_rows rows, then the
+// group reduction area [NG][DH].  All 8 warps compute; rows that survive are fetched with
+// 16-byte global loads, four rows in flight per lane group.
+template <typename T, int DH>
+__global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const FfaStepParams P)
+{
+    using G = RowGeom<T, DH>;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL;
+    constexpr int NT = kGatherThreads, NG = NT / LPR;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int R = P.tile_rows;  // multiple of 32
+    int* list_idx = reinterpret_cast<int*>(smem);
+    float* list_p = reinterpret_cast<float*>(list_idx + R);
+    float* red = list_p + R;  // [NG][DH]
+    __shared__ int s_n, s_last;
+
+    const long long U = P.total_units;
+    const int upb = P.units_per_bh;
+    const long long u0 = unit_start(blockIdx.x, U, P.grid), u1 = unit_start(blockIdx.x + 1, U, P.grid);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = tid / LPR, li = tid % LPR;
+    const bool prune = P.p > 0.f;
+    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
+
+    long long u = u0;
+    while (u < u1) {
+        const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
+        const int j1 = (int)min((long long)upb, j0 + (u1 - u));
+        const SampleRange sr = sample_range(P, bh / P.H);
+        const int jt = sr.row / R;
+        const float M = P.stats[2 * bh], Lsum = P.stats[2 * bh + 1];
+        // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125,
+        // 1185); the torch-rounding mode divides exactly like torch's softmax does
+        const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
+        const float theta = Elem<T>::round(P.p * inv);
+        const float* sc = P.scores + (size_t)bh * P.Lmax;
+        auto prob_of = [&](float s) -> float {
+            if (prune) return Elem<T>::round(__expf(s - M) * inv);
+            return Elem<T>::round(expf(s - M) / Lsum);
+        };
+
+        float acc[VPL][EPV];
+#pragma unroll
+        for (int x = 0; x < VPL; ++x)
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) acc[x][e] = 0.f;
+
+        for (int j = j0; j < j1 && sr.ok; ++j) {
+            const int lo = j * R, hi = min((j + 1) * R, sr.row + 1);  // includes the new token's bit
+            if (hi <= lo) break;
+            __syncthreads();
+            if (tid == 0) s_n = 0;
+            __syncthreads();
+            for (int base = lo + warp * 32; base < hi; base += NT) {
+                const int i = base + lane;
+                const bool cached = i < sr.row && i >= sr.first;
+                float pr = 0.f;
+                bool keep = false;
+                if (cached) {
+                    pr = prob_of(sc[i]);
+                    keep = prune ? !Elem<T>::leq(pr, theta) : true;
+                }
+                const unsigned bal = __ballot_sync(0xffffffffu, keep);
+                if (P.kept_mask != nullptr && lane == 0)
+                    P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
+                        bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+                int pos = 0;
+                if (lane == 0 && bal) pos = atomicAdd(&s_n, __popc(bal));
+                pos = __shfl_sync(0xffffffffu, pos, 0) + __popc(bal & ((1u << lane) - 1u));
+                if (keep) list_idx[pos] = i, list_p[pos] = pr;
+            }
+            __syncthreads();
+            const int n = s_n;
+            for (int base = 0; base < n; base += 4 * NG) {
+                uint4 raw[4][VPL];
+                float pr[4];
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) {
+                    const int idx = base + uu * NG + g;
+                    const bool okr = idx < n;
+                    pr[uu] = okr ? list_p[idx] : 0.f;
+                    const int row = okr ? list_idx[idx] : 0;
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        const int vec = li + x * LPR;
+                        raw[uu][x] = make_uint4(0, 0, 0, 0);
+                        if (okr && vec < VPR)
+                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + ((size_t)bh * P.Lmax + row) * ROWB + vec * 16));
+                    }
+                }
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu)
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        float vf[EPV];
+                        Elem<T>::unpack(raw[uu][x], vf);
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr[uu], vf[e], acc[x][e]);
+                    }
+            }
+        }
+
+        // the new token is never pruned (attention.cu:1227-1256): append v, add P_t * v
+        if (sr.ok && j0 <= jt && jt < j1 && g == 0) {
+            const float pt = prob_of(sc[sr.row]);
+            const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                const int vec = li + x * LPR;
+                if (vec < VPR) {
+                    const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + (size_t)bh * ROWB + vec * 16);
+                    *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
+                    float vf[EPV];
+                    Elem<T>::unpack(vraw, vf);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pt, vf[e], acc[x][e]);
+                }
+            }
+        }
+
+        // ---- sum the groups, then the CTAs ----
+        __syncthreads();
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) {
+            const int vec = li + x * LPR;
+            if (vec < VPR) {
+#pragma unroll
+                for (int e = 0; e < EPV; e += 4)
+                    *reinterpret_cast<float4*>(red + g * DH + vec * EPV + e) =
+                        make_float4(acc[x][e], acc[x][e + 1], acc[x][e + 2], acc[x][e + 3]);
+            }
+        }
+        __syncthreads();
+        const bool whole = (j0 == 0 && j1 == upb);
+        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+        float* part = P.partials + (size_t)(blockIdx.x + bh) * (DH + 2);
+        for (int d = tid; d < DH; d += NT) {
+            float A = 0.f;
+            for (int gg = 0; gg < NG; ++gg) A += red[gg * DH + d];
+            if (whole) Elem<T>::store(outp + d, A);
+            else part[d] = A;
+        }
+        if (!whole) {
+            __threadfence();
+            __syncthreads();
+            const int c_first = cta_of_unit((long long)bh * upb, U, P.grid);
+            const int c_last = cta_of_unit((long long)(bh + 1) * upb - 1, U, P.grid);
+            const int count = c_last - c_first + 1;
+            if (tid == 0) s_last = (atomicAdd(P.tickets + bh, 1) == count - 1);
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const float* pbase = P.partials + (size_t)(c_first + bh) * (DH + 2);
+                for (int d = tid; d < DH; d += NT) {
+                    float A = 0.f;
+                    for (int k = 0; k < count; ++k) A += __ldcg(pbase + (size_t)k * (DH + 2) + d);
+                    Elem<T>::store(outp + d, A);
+                }
+                if (tid == 0) P.tickets[bh] = 0;
+            }
+        }
+        if (!sr.ok && tid == 0) atomicOr(P.status, kStatusBadLength);
+        u += j1 - j0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Cache build: prompt [BH, Lp, Dh] -> rows [0, Lp) of [BH, Lmax, Dh], K and V in one launch
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ffa_cache_init_kernel(const uint4* __restrict__ k_src, const uint4* __restrict__ v_src,
+                                                              uint4* __restrict__ k_dst, uint4* __restrict__ v_dst,
+                                                              long long src_vecs_per_bh, long long dst_vecs_per_bh,
+                                                              long long total_vecs)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs; i += stride) {
+        const long long bh = i / src_vecs_per_bh, r = i - bh * src_vecs_per_bh;
+        const long long o = bh * dst_vecs_per_bh + r;
+        const uint4 kk = __ldcs(k_src + i), vv = __ldcs(v_src + i);
+        k_dst[o] = kk;
+        v_dst[o] = vv;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host-side dispatch
+// ------------------------------------------------------------------------------------------
+template <typename F>
+int dispatch(int dtype, int head_dim, F&& f)
+{
+#define FFA_DH_SWITCH(T)                                        \
+    switch (head_dim) {                                         \
+        case 64: return f(T{}, std::integral_constant<int, 64>{});   \
+        case 80: return f(T{}, std::integral_constant<int, 80>{});   \
+        case 128: return f(T{}, std::integral_constant<int, 128>{}); \
+        case 256: return f(T{}, std::integral_constant<int, 256>{}); \
+        default: return (int)cudaErrorInvalidValue;             \
+    }
+    switch (dtype) {
+        case 0: FFA_DH_SWITCH(float)
+        case 1: FFA_DH_SWITCH(__half)
+        case 2: FFA_DH_SWITCH(__nv_bfloat16)
+        default: return (int)cudaErrorInvalidValue;
+    }
+#undef FFA_DH_SWITCH
+}
+
+int elem_size(int dtype) { return dtype == 0 ? 4 : 2; }
+
+}  // namespace
+
+int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage)
+{
+    const int rowb = head_dim * elem_size(dtype);
+    const int vpr = rowb / 16;
+    const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
+    const int ng = consumer_warps * 32 / lpr;
+    return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16;
+}
+
+int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows)
+{
+    const int rowb = head_dim * elem_size(dtype);
+    const int vpr = rowb / 16;
+    const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
+    return tile_rows * 8 + (kGatherThreads / lpr) * head_dim * 4;
+}
+
+int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes)
+{
+    return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
+        using T = decltype(t);
+        constexpr int DH = decltype(dh)::value;
+        cudaError_t e;
+        e = cudaFuncSetAttribute(ffa_stream_kernel<T, DH, kPassOne>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(ffa_stream_kernel<T, DH, kPassScore>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(ffa_value_gather_kernel<T, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes);
+        return (int)e;
+    });
+}
+
+int ffa_k_cache_init(int dtype, int BH, int prompt_len, int max_len, int head_dim, const void* k_src, const void* v_src,
+                     void* k_cache, void* v_cache, int sms, cudaStream_t stream)
+{
+    const long long rowv = (long long)head_dim * elem_size(dtype) / 16;
+    const long long src_per = rowv * prompt_len, dst_per = rowv * max_len, total = src_per * BH;
+    if (total == 0) return 0;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)sms * 16;
+    if (blocks > cap) blocks = cap;
+    ffa_cache_init_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(k_src), static_cast<const uint4*>(v_src),
+                                                                static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
+                                                                src_per, dst_per, total);
+    return (int)cudaGetLastError();
+}
+
+int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int threads, int smem, cudaStream_t stream)
+{
+    return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
+        using T = decltype(t);
+        constexpr int DH = decltype(dh)::value;
+        ffa_stream_kernel<T, DH, kPassOne><<<P.grid, threads, smem, stream>>>(P);
+        return (int)cudaGetLastError();
+    });
+}
+
+int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const FfaStepParams& Pv, int threads,
+                         int smem_k, int smem_v, cudaStream_t stream)
+{
+    return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
+        using T = decltype(t);
+        constexpr int DH = decltype(dh)::value;
+        ffa_stream_kernel<T, DH, kPassScore><<<Pk.grid, threads, smem_k, stream>>>(Pk);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+        ffa_value_gather_kernel<T, DH><<<Pv.grid, kGatherThreads, smem_v, stream>>>(Pv);
+        return (int)cudaGetLastError();
+    });
+}

@@ -1,0 +1,45 @@
+// Internal interface between the C ABI (ffa_c_api.cu) and the kernels (ffa_decode_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Everything one decode step needs on the device.  Plain data, passed by value to kernels.
+struct FfaStepParams {
+    const void* q;        // [B*H, Dh]
+    const void* k;        // [B*H, Dh]
+    const void* v;        // [B*H, Dh]
+    void* k_cache;        // [B*H, Lmax, Dh]
+    void* v_cache;        // [B*H, Lmax, Dh]
+    void* out;            // [B*H, Dh]
+    const int* seq_lengths;  // [B] or null
+    int right_or_no_padding;
+    int B, H, Lmax, t;
+    // work decomposition: every (batch, head) owns units_per_bh tiles of tile_rows cache rows;
+    // the flat list of B*H*units_per_bh units is cut into `grid` equal contiguous runs
+    int tile_rows, stages, units_per_bh, grid;
+    long long total_units;
+    float scale;
+    float p;
+    int round_like_torch;
+    // scratch
+    float* partials;   // [(grid + B*H)] x (Dh + 2): weighted sum, running max, running sum
+    int* tickets;      // [2 * B*H] arrival counters, zero between launches
+    int* status;       // device status word
+    float* stats;      // [B*H] x 2: global max, 1/sum (two-pass modes)
+    float* scores;     // [B*H, Lmax] fp32 scores (two-pass modes)
+    uint32_t* kept_mask;  // [B*H, mask_words] or null
+    int mask_words;
+};
+
+// dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.
+int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes);
+int ffa_k_cache_init(int dtype, int BH, int prompt_len, int max_len, int head_dim, const void* k_src, const void* v_src,
+                     void* k_cache, void* v_cache, int sms, cudaStream_t stream);
+// p == 0, exact mode: one launch.
+int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int threads, int smem, cudaStream_t stream);
+// p > 0 or round-like-torch: score pass then value pass, two launches.
+int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const FfaStepParams& Pv, int threads,
+                         int smem_k, int smem_v, cudaStream_t stream);
+// shared-memory bytes a launch shape needs
+int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage);
+int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows);

@@ -1,0 +1,225 @@
+// Torch extension `ff_attention`: the FastForwardAttn class over the C ABI of libffa_b200.so.
+//
+// Mirrors the reference's pybind class (torch_ffa_api.cpp:161-214): same constructor
+// (K, V, max_timesteps, use_default_kernel_launch), the same three attention overloads in
+// the same argument order, get_cache().  Differences, all on purpose:
+//   * bf16 is accepted next to fp32 and fp16 (torch_ffa_api.cpp:100-101 rejects it);
+//   * arguments are validated and errors raise instead of printf + garbage (:101, :129);
+//   * kernels run on torch's current stream under a device guard (the reference launches on
+//     the legacy stream 0, attention.cu:1504);
+//   * both caches are token-major [B, H, max_len, Dh] (the reference's K cache is
+//     [B, H, Dh/x, max_len, x], torch_ffa_api.cpp:65);
+//   * prob_thresh defaults to 0 in Python too.
+// torch is used for memory, streams and the binding only; all arithmetic is in the library.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <utility>
+
+#include "ffa_c_api.h"
+
+namespace {
+
+int dtype_code(const torch::Tensor& x)
+{
+    switch (x.scalar_type()) {
+        case torch::kFloat: return FFA_DTYPE_F32;
+        case torch::kHalf: return FFA_DTYPE_F16;
+        case torch::kBFloat16: return FFA_DTYPE_BF16;
+        default: TORCH_CHECK(false, "FastForwardAttn: unsupported tensor type ", x.scalar_type(), " (float32, float16, bfloat16)");
+    }
+}
+
+void check(int rc, const char* what) { TORCH_CHECK(rc == FFA_OK, "FastForwardAttn: ", what, ": ", ffa_last_error()); }
+
+struct FastForwardAttn {
+    FastForwardAttn(torch::Tensor K, torch::Tensor V, int64_t max_timesteps, bool use_default_kernel_launch)
+    {
+        TORCH_CHECK(K.is_cuda() && V.is_cuda(), "FastForwardAttn: K and V must be CUDA tensors");
+        TORCH_CHECK(K.dim() == 4 && V.sizes() == K.sizes(), "FastForwardAttn: K and V must both be [batch, heads, prompt_len, head_dim]");
+        TORCH_CHECK(K.scalar_type() == V.scalar_type() && K.device() == V.device(), "FastForwardAttn: K and V differ in dtype or device");
+        K = K.contiguous(), V = V.contiguous();
+        B = K.size(0), H = K.size(1), Dh = K.size(3);
+        const int64_t Lp = K.size(2);
+        Lmax = max_timesteps;
+        TORCH_CHECK(Lmax >= Lp && Lmax > 0, "FastForwardAttn: max_timesteps (", Lmax, ") is smaller than the prompt (", Lp, ")");
+        TORCH_CHECK(Lmax < (int64_t(1) << 31) && B * H < (int64_t(1) << 31), "FastForwardAttn: sizes exceed int range");
+        dtype = dtype_code(K);
+        c10::cuda::CUDAGuard guard(K.device());
+        device = K.device();
+        check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)Lmax, use_default_kernel_launch, K.device().index(), &plan),
+              "plan");
+        k_cache = torch::empty({B, H, Lmax, Dh}, K.options());
+        v_cache = torch::empty({B, H, Lmax, Dh}, K.options());
+        auto stream = at::cuda::getCurrentCUDAStream();
+        check(ffa_cache_init(dtype, (int)B, (int)H, (int)Lp, (int)Lmax, (int)Dh, K.data_ptr(), V.data_ptr(), k_cache.data_ptr(),
+                             v_cache.data_ptr(), stream.stream()),
+              "cache init");
+        bind_workspace(false);
+    }
+    ~FastForwardAttn() { ffa_plan_destroy(plan); }
+    FastForwardAttn(const FastForwardAttn&) = delete;
+    FastForwardAttn& operator=(const FastForwardAttn&) = delete;
+
+    void bind_workspace(bool with_scores)
+    {
+        const size_t n = ffa_workspace_bytes(plan, with_scores);
+        workspace = torch::empty({(int64_t)n}, torch::TensorOptions().dtype(torch::kUInt8).device(device));
+        check(ffa_workspace_bind(plan, workspace.data_ptr(), n, at::cuda::getCurrentCUDAStream().stream()), "workspace");
+        has_scores = with_scores;
+    }
+
+    torch::Tensor run(const torch::Tensor& q_, const torch::Tensor& k_, const torch::Tensor& v_, torch::Tensor& kc,
+                      torch::Tensor& vc, double softmax_scale, int64_t t, const torch::Tensor* seq_lengths,
+                      bool right_or_no_padding, double p, c10::optional<torch::Tensor> out_opt)
+    {
+        const int64_t n = B * H * Dh;
+        auto prep = [&](const torch::Tensor& x, const char* name) {
+            TORCH_CHECK(x.is_cuda() && x.device() == device, "FastForwardAttn: ", name, " is not on the engine's device");
+            TORCH_CHECK(dtype_code(x) == dtype, "FastForwardAttn: ", name, " has a different dtype than the cache");
+            TORCH_CHECK(x.numel() == n, "FastForwardAttn: ", name, " must hold batch*heads*head_dim = ", n, " elements, got ", x.numel());
+            return x.contiguous();
+        };
+        torch::Tensor q = prep(q_, "q"), k = prep(k_, "k"), v = prep(v_, "v");
+        for (const torch::Tensor* c : {&kc, &vc}) {
+            TORCH_CHECK(c->is_cuda() && c->device() == device && dtype_code(*c) == dtype && c->is_contiguous() &&
+                            c->dim() == 4 && c->size(0) == B && c->size(1) == H && c->size(2) == Lmax && c->size(3) == Dh,
+                        "FastForwardAttn: cache tensors must be the [batch, heads, max_len, head_dim] tensors returned by get_cache()");
+        }
+        TORCH_CHECK(t >= 0 && t < Lmax, "FastForwardAttn: curr_timestep ", t, " outside [0, ", Lmax, ")");
+        TORCH_CHECK(p >= 0.0 && p <= 1.0, "FastForwardAttn: prob_thresh ", p, " outside [0, 1]");
+        torch::Tensor sl;
+        if (seq_lengths != nullptr) {
+            TORCH_CHECK(seq_lengths->is_cuda() && seq_lengths->device() == device && seq_lengths->scalar_type() == torch::kInt &&
+                            seq_lengths->numel() == B,
+                        "FastForwardAttn: seq_lengths must be an int32 CUDA tensor with one entry per batch element");
+            sl = seq_lengths->contiguous();
+        }
+        c10::cuda::CUDAGuard guard(device);
+        const bool twopass = p > 0.0 || mode == FFA_MODE_ROUND_LIKE_TORCH;
+        if (twopass && !has_scores) bind_workspace(true);
+        torch::Tensor out;
+        if (out_opt.has_value()) {
+            out = *out_opt;
+            TORCH_CHECK(out.is_cuda() && out.device() == device && dtype_code(out) == dtype && out.is_contiguous() && out.numel() == n,
+                        "FastForwardAttn: out must be a contiguous tensor of batch*heads*head_dim elements on the engine's device");
+        } else {
+            out = torch::empty({B, H, Dh}, q.options());
+        }
+        uint32_t* mask_ptr = nullptr;
+        if (want_mask && p > 0.0) {
+            if (!kept_mask.defined()) kept_mask = torch::zeros({B, H, (Lmax + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
+            mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
+        }
+        check(ffa_attention(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                            (float)softmax_scale, (int)t, seq_lengths ? sl.data_ptr<int>() : nullptr, right_or_no_padding,
+                            (float)p, mask_ptr, at::cuda::getCurrentCUDAStream().stream()),
+              "attention");
+        return out;
+    }
+
+    // torch_ffa_api.cpp:189-192
+    torch::Tensor attention(torch::Tensor q, torch::Tensor k, torch::Tensor v, double softmax_scale, int64_t curr_timestep,
+                            double prob_thresh, c10::optional<torch::Tensor> out)
+    {
+        return run(q, k, v, k_cache, v_cache, softmax_scale, curr_timestep, nullptr, true, prob_thresh, out);
+    }
+    // torch_ffa_api.cpp:179-182
+    torch::Tensor attention_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor kc, torch::Tensor vc,
+                                  double softmax_scale, int64_t curr_timestep, double prob_thresh, c10::optional<torch::Tensor> out)
+    {
+        return run(q, k, v, kc, vc, softmax_scale, curr_timestep, nullptr, true, prob_thresh, out);
+    }
+    // torch_ffa_api.cpp:184-187: left padding, keys below seq_lengths[b] are masked
+    torch::Tensor attention_varlen(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor kc, torch::Tensor vc,
+                                   double softmax_scale, int64_t curr_timestep, torch::Tensor seq_lengths, double prob_thresh,
+                                   c10::optional<torch::Tensor> out)
+    {
+        return run(q, k, v, kc, vc, softmax_scale, curr_timestep, &seq_lengths, false, prob_thresh, out);
+    }
+    // c_ffa_api.h:17-20 semantics (per-sample lengths, right padding); not exported by the
+    // reference's Python class, exported here so the mode is reachable from Python
+    torch::Tensor attention_per_sample(torch::Tensor q, torch::Tensor k, torch::Tensor v, double softmax_scale,
+                                       torch::Tensor seq_lengths, double prob_thresh, c10::optional<torch::Tensor> out)
+    {
+        return run(q, k, v, k_cache, v_cache, softmax_scale, 0, &seq_lengths, true, prob_thresh, out);
+    }
+
+    std::pair<torch::Tensor, torch::Tensor> get_cache() { return std::make_pair(k_cache, v_cache); }
+
+    void set_mode(const std::string& m)
+    {
+        TORCH_CHECK(m == "exact" || m == "round_like_torch", "FastForwardAttn: mode must be 'exact' or 'round_like_torch'");
+        mode = m == "exact" ? FFA_MODE_EXACT : FFA_MODE_ROUND_LIKE_TORCH;
+        check(ffa_plan_set_mode(plan, mode), "mode");
+    }
+    void set_launch(int tile_rows, int stages, int consumer_warps, int ctas_per_sm, int grid)
+    {
+        ffa_launch_t l{tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0};
+        const bool any = tile_rows > 0 || stages > 0 || consumer_warps > 0 || ctas_per_sm > 0 || grid > 0;
+        check(ffa_plan_set_launch(plan, any ? &l : nullptr), "launch override");
+    }
+    py::dict launch_shape(int64_t t)
+    {
+        ffa_launch_t l;
+        check(ffa_plan_get_launch(plan, (int)t, &l), "launch shape");
+        py::dict d;
+        d["tile_rows"] = l.tile_rows, d["stages"] = l.stages, d["consumer_warps"] = l.consumer_warps;
+        d["ctas_per_sm"] = l.ctas_per_sm, d["grid"] = l.grid, d["smem_bytes"] = l.smem_bytes;
+        return d;
+    }
+    void record_kept_mask(bool on) { want_mask = on; }
+    torch::Tensor get_kept_mask()
+    {
+        TORCH_CHECK(kept_mask.defined(), "FastForwardAttn: no kept mask recorded (record_kept_mask(True), then a call with prob_thresh > 0)");
+        return kept_mask;
+    }
+    int device_status()
+    {
+        c10::cuda::CUDAGuard guard(device);
+        int s = 0;
+        const int rc = ffa_device_status(plan, at::cuda::getCurrentCUDAStream().stream(), &s);
+        TORCH_CHECK(rc == FFA_OK || rc == FFA_ERR_DEVICE, "FastForwardAttn: status: ", ffa_last_error());
+        return s;
+    }
+
+    ffa_plan_t* plan = nullptr;
+    torch::Tensor k_cache, v_cache, workspace, kept_mask;
+    c10::Device device{c10::kCUDA, 0};
+    int64_t B = 0, H = 0, Dh = 0, Lmax = 0;
+    int dtype = 0, mode = FFA_MODE_EXACT;
+    bool has_scores = false, want_mask = false;
+};
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
+{
+    m.doc() = "B200 decode masked multi-head attention behind the FastForwardAttention interface";
+    m.def("launch_count", []() { return ffa_launch_count(); }, "kernels launched by the engine since load");
+    py::class_<FastForwardAttn>(m, "FastForwardAttn")
+        .def(py::init<torch::Tensor, torch::Tensor, int64_t, bool>(), py::arg("K"), py::arg("V"), py::arg("max_timesteps"),
+             py::arg("use_default_kernel_launch") = false)
+        .def("get_cache", &FastForwardAttn::get_cache, "the live (k_cache, v_cache) tensors, [batch, heads, max_len, head_dim]")
+        .def("attention", &FastForwardAttn::attention, "decode step on the engine's own caches", py::arg("q"), py::arg("k"),
+             py::arg("v"), py::arg("softmax_scale"), py::arg("curr_timestep"), py::arg("prob_thresh") = 0.0,
+             py::arg("out") = py::none())
+        .def("attention", &FastForwardAttn::attention_cache, "decode step on caches passed back by the caller", py::arg("q"),
+             py::arg("k"), py::arg("v"), py::arg("k_cache"), py::arg("v_cache"), py::arg("softmax_scale"),
+             py::arg("curr_timestep"), py::arg("prob_thresh") = 0.0, py::arg("out") = py::none())
+        .def("attention", &FastForwardAttn::attention_varlen, "decode step with left padding: keys below seq_lengths[b] are masked",
+             py::arg("q"), py::arg("k"), py::arg("v"), py::arg("k_cache"), py::arg("v_cache"), py::arg("softmax_scale"),
+             py::arg("curr_timestep"), py::arg("seq_lengths"), py::arg("prob_thresh") = 0.0, py::arg("out") = py::none())
+        .def("attention_per_sample", &FastForwardAttn::attention_per_sample,
+             "decode step with per-sample cache lengths (right padding): sample b appends at row seq_lengths[b]", py::arg("q"),
+             py::arg("k"), py::arg("v"), py::arg("softmax_scale"), py::arg("seq_lengths"), py::arg("prob_thresh") = 0.0,
+             py::arg("out") = py::none())
+        .def("set_mode", &FastForwardAttn::set_mode, "'exact' (default) or 'round_like_torch'")
+        .def("set_launch", &FastForwardAttn::set_launch, py::arg("tile_rows") = 0, py::arg("stages") = 0,
+             py::arg("consumer_warps") = 0, py::arg("ctas_per_sm") = 0, py::arg("grid") = 0)
+        .def("launch_shape", &FastForwardAttn::launch_shape, py::arg("t"))
+        .def("record_kept_mask", &FastForwardAttn::record_kept_mask)
+        .def("get_kept_mask", &FastForwardAttn::get_kept_mask)
+        .def("device_status", &FastForwardAttn::device_status, "synchronises; 0 when the kernels recorded no error");
+}

@@ -1,0 +1,78 @@
+"""Head-sharded decode attention across the GPUs of one node.
+
+Every (batch, head) pair is an independent problem (the reference's grid is one CTA per
+pair, attention.cu:1303), so rank r of N owns heads [r*H/N, (r+1)*H/N) for the whole
+generation: its slice of the prompt K/V, its KV-cache shard, its slice of every q/k/v.  No
+cache row ever crosses NVLink.  The only collective is one all-gather of the [B, H/N, Dh]
+outputs, issued when the caller asks for the full [B, H, Dh] tensor.
+
+One process per GPU (torchrun); the process group decides the backend (NCCL on GPUs).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def head_range(num_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    """Heads [lo, hi) owned by `rank`."""
+    if num_heads % world != 0:
+        raise ValueError(f"{num_heads} heads do not divide over {world} ranks")
+    per = num_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_heads(x: torch.Tensor, rank: int, world: int, num_heads: int) -> torch.Tensor:
+    """Slice this rank's heads out of a full tensor.  Accepts [B, H, ...] (example.py:31-33) or
+    the HF forks' [B, 1, H*Dh] (modeling_opt.py:193-203)."""
+    lo, hi = head_range(num_heads, rank, world)
+    if x.dim() >= 3 and x.size(1) == num_heads:
+        return x[:, lo:hi].contiguous()
+    B = x.size(0)
+    return x.reshape(B, num_heads, -1)[:, lo:hi].contiguous()
+
+
+class ShardedFastForwardAttn:
+    """FastForwardAttn over a head shard, plus the optional output all-gather.
+
+    K_local / V_local: this rank's [B, H/N, prompt, Dh] slice.  `engine_factory` builds the
+    per-rank engine; it defaults to the CUDA extension and exists so that the host logic can
+    be exercised on CPU ranks with a stand-in engine.
+    """
+
+    def __init__(self, K_local: torch.Tensor, V_local: torch.Tensor, max_len: int,
+                 use_default_kernel_launch: bool = False, group: Optional[dist.ProcessGroup] = None,
+                 engine_factory: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if engine_factory is None:
+            from . import FastForwardAttn as engine_factory  # raises if the extension is missing
+        self.engine = engine_factory(K_local, V_local, max_len, use_default_kernel_launch)
+        self.B, self.H_local, _, self.Dh = K_local.shape
+        self.H = self.H_local * self.world
+        self._gathered = None
+
+    def get_cache(self):
+        return self.engine.get_cache()
+
+    def attention(self, q_local, k_local, v_local, softmax_scale: float, curr_timestep: int,
+                  prob_thresh: float = 0.0, gather: bool = False) -> torch.Tensor:
+        """One decode step on this rank's heads; q/k/v hold B*(H/N)*Dh elements.  Returns the
+        local [B, H/N, Dh] output, or the full [B, H, Dh] tensor when gather=True."""
+        out = self.engine.attention(q_local, k_local, v_local, softmax_scale, curr_timestep, prob_thresh)
+        return self.gather(out) if gather else out
+
+    def gather(self, out_local: torch.Tensor) -> torch.Tensor:
+        """All-gather of the per-rank outputs into [B, H, Dh] (rank-major heads)."""
+        if self.world == 1:
+            return out_local
+        out_local = out_local.contiguous()
+        if self._gathered is None or self._gathered.dtype != out_local.dtype or self._gathered.device != out_local.device:
+            self._gathered = torch.empty(self.world, self.B, self.H_local, self.Dh, dtype=out_local.dtype,
+                                         device=out_local.device)
+        dist.all_gather_into_tensor(self._gathered.view(-1), out_local.view(-1), group=self.group)
+        # [N, B, H/N, Dh] -> [B, N, H/N, Dh] -> [B, H, Dh]
+        return self._gathered.permute(1, 0, 2, 3).reshape(self.B, self.H, self.Dh)

@@ -1,0 +1,131 @@
+/*
+ * C ABI of the B200 decode-attention engine (libffa_b200.so).
+ *
+ * One decode step of masked multi-head attention for a single new token per (batch, head):
+ * append k/v at row t of the KV cache, attend over rows 0..t, optional probability pruning.
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless stated otherwise.
+ * All calls are asynchronous on the given stream (a cudaStream_t passed as void*; NULL is the
+ * legacy default stream) and return an int status: 0 on success, a negative FFA_ERR_* code
+ * otherwise, with a human-readable reason available from ffa_last_error().
+ *
+ * Each entry point cites the reference interface it replaces (paths inside the
+ * FastForwardAttention checkout).
+ */
+#ifndef FFA_C_API_H
+#define FFA_C_API_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element type of q/k/v, the caches and the output.  The reference dispatches on
+ * sizeof(T) with T in {float, uint16_t-as-half} (attention.cu:1512-1554); bf16 is new. */
+enum { FFA_DTYPE_F32 = 0, FFA_DTYPE_F16 = 1, FFA_DTYPE_BF16 = 2 };
+
+enum {
+    FFA_OK = 0,
+    FFA_ERR_DTYPE = -1,     /* unknown dtype code */
+    FFA_ERR_HEAD_DIM = -2,  /* head_dim not in {64, 80, 128, 256} (attention.cu:1515-1531) */
+    FFA_ERR_RANGE = -3,     /* t outside [0, max_len), sizes <= 0, p outside [0, 1] */
+    FFA_ERR_ARG = -4,       /* null or misaligned pointer, bad flag combination */
+    FFA_ERR_CUDA = -5,      /* a CUDA runtime call failed; ffa_last_error() has its text */
+    FFA_ERR_WORKSPACE = -6, /* no workspace bound, or bound workspace too small */
+    FFA_ERR_DEVICE = -7     /* the kernel recorded an error in the device status word */
+};
+
+/* Arithmetic modes (ffa_plan_set_mode). */
+enum {
+    /* fp32 arithmetic throughout, one rounding to the storage type at the end.  Default. */
+    FFA_MODE_EXACT = 0,
+    /* Re-applies the four roundings of torch's same-dtype softmax(QK^T*scale)V on fp16/bf16
+     * operands (scores, scaled scores, probabilities, output), so results track the
+     * reference's torch path (example.py:6-7) rather than the exact value.  Two kernels. */
+    FFA_MODE_ROUND_LIKE_TORCH = 1
+};
+
+/* Bits of the device status word (ffa_device_status). */
+enum {
+    FFA_STATUS_WAIT_TIMEOUT = 1, /* a bounded wait on a copy barrier ran out */
+    FFA_STATUS_BAD_LENGTH = 2    /* a per-sample length was outside [0, max_len) */
+};
+
+typedef struct ffa_plan ffa_plan_t;
+
+/* Launch shape of the streaming kernels, chosen by the planner per (dtype, sizes, t). */
+typedef struct ffa_launch {
+    int tile_rows;      /* cache rows per pipeline stage (K rows and V rows each) */
+    int stages;         /* depth of the shared-memory ring */
+    int consumer_warps; /* compute warps per CTA (one more warp issues the bulk copies) */
+    int ctas_per_sm;    /* resident CTAs per SM the grid is sized for */
+    int grid;           /* number of CTAs; the (batch*head, tile) work list is cut evenly */
+    int smem_bytes;     /* dynamic shared memory per CTA */
+} ffa_launch_t;
+
+/* Bytes of the two cache slabs, each laid out [batch, heads, max_len, head_dim] (row t of
+ * one (batch, head) is head_dim contiguous elements; rows are 16-byte aligned).
+ * Replaces the torch::empty shapes in init_attention_cache (torch_ffa_api.cpp:65-66, 85-86). */
+int ffa_cache_bytes(int dtype, int batch, int heads, int max_len, int head_dim, size_t* k_bytes,
+                    size_t* v_bytes);
+
+/* Copies prompt K and V, each [batch, heads, prompt_len, head_dim] contiguous, into rows
+ * [0, prompt_len) of the caches; rows >= prompt_len are left untouched.
+ * Replaces invokeTranspose4dBatchMajor<T> (attention.cu:1611-1689). */
+int ffa_cache_init(int dtype, int batch, int heads, int prompt_len, int max_len, int head_dim,
+                   const void* k_src, const void* v_src, void* k_cache, void* v_cache, void* stream);
+
+/* Creates the per-engine plan: validates the shape, queries the device once, prepares the
+ * kernels.  use_default_launch != 0 selects the fixed analytic launch rule, 0 the table
+ * measured on B200.  Host memory only; no device allocation.
+ * Replaces get_launch_params (kernel_launch_utils.h:135-180) and the launch members kept by
+ * the FastForwardAttn constructor (torch_ffa_api.cpp:162-177, 196-201). */
+int ffa_plan_create(int dtype, int batch, int heads, int head_dim, int max_len, int use_default_launch,
+                    int device, ffa_plan_t** plan);
+void ffa_plan_destroy(ffa_plan_t* plan);
+
+/* The launch shape the planner picks for step t (after any override). */
+int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch);
+/* Forces a launch shape (fields <= 0 keep the planner's choice); NULL removes the override.
+ * Used by the tuning sweep; the reference exposes tpb/tpv/tpk the same way
+ * (c_ffa_api.h:17-20). */
+int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch);
+int ffa_plan_set_mode(ffa_plan_t* plan, int mode);
+
+/* Scratch the engine needs in device memory: split partials, arrival counters, the status
+ * word and, when with_scores != 0 (needed for p > 0 and FFA_MODE_ROUND_LIKE_TORCH), one fp32
+ * score per cache row.  The caller allocates it (256-byte aligned) and binds it once;
+ * binding clears the counters on the stream.  One workspace serves one stream at a time. */
+size_t ffa_workspace_bytes(const ffa_plan_t* plan, int with_scores);
+int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* stream);
+
+/* One decode step.  q, k, v: batch*heads*head_dim contiguous elements in (batch, head, dim)
+ * order.  Writes k and v into row `row` of the caches and out[batch, heads, head_dim], where
+ *   seq_lengths == NULL                      : row = t for every sample, all keys visible;
+ *   seq_lengths != NULL, right_or_no_padding : row = seq_lengths[b] (per-sample lengths);
+ *   seq_lengths != NULL, !right_or_no_padding: row = t, keys < seq_lengths[b] are masked
+ *                                              (left padding).
+ * p is the pruning threshold as a fraction of the largest probability; p == 0 is exact
+ * attention.  kept_mask, if not NULL and p > 0, receives one bit per cache row,
+ * [batch*heads, ceil(max_len/32)] words, bit set = row contributed to the output.
+ * Replaces call_attention<T> (attention.cu:1512-1554) / do_attention<T> (c_ffa_api.h:17-20);
+ * the tpv/tpk/tpb arguments of those live in the plan. */
+int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_cache, void* v_cache,
+                  void* out, float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding,
+                  float p, uint32_t* kept_mask, void* stream);
+
+/* Synchronises the stream and returns the device status word (0 = clean) in *status, then
+ * clears it.  The reference only printf()s cudaGetLastError (attention.cu:1444-1451). */
+int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
+
+/* Kernels launched by this library since it was loaded (for launch accounting in benchmarks). */
+unsigned long long ffa_launch_count(void);
+
+/* Reason for the most recent non-zero return on this thread. */
+const char* ffa_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FFA_C_API_H */

@@ -159,9 +159,10 @@ def pruned_attention(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, softmax_
     out = torch.einsum("nl,nld->nd", Pk, V.to(torch.float32)).to(T)
 
     # Borderline census: positions whose decision flips if P_i moves by one unit in the last
-    # place of T (fp32: by a relative 1e-6, the size of the kernel's exp/division shortcuts).
-    if T == torch.float32:
-        lo, hi = (e * inv) * (1 - 1e-6), (e * inv) * (1 + 1e-6)
+    # place of T (fp32: by a relative 1e-5, the size of the kernel's exp shortcut plus the
+    # summation-order noise of a 64..256-term fp32 dot product in the exponent).
+    if T in (torch.float32, torch.float64):
+        lo, hi = (e * inv) * (1 - 1e-5), (e * inv) * (1 + 1e-5)
         flips = (lo <= theta) != (hi <= theta)
     else:
         bits = P.contiguous().view(torch.int16).to(torch.int32)

@@ -1,0 +1,68 @@
+"""CPU-side checks of the boundary: the library loads, exports every symbol the header
+declares, and rejects bad arguments without touching a GPU."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from fastforwardattention_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ffa_c_api.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ffa_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = capi.lib()
+    names = declared_symbols()
+    assert len(names) >= 13
+    for n in names:
+        assert hasattr(L, n), n
+    assert sorted(capi.SYMBOLS) == [n for n in names if n in capi.SYMBOLS]
+    assert set(names) >= set(capi.SYMBOLS)
+
+
+def test_argument_validation_without_gpu():
+    L = capi.lib()
+    kb, vb = C.c_size_t(), C.c_size_t()
+    assert L.ffa_cache_bytes(capi.BF16, 32, 32, 32768, 128, C.byref(kb), C.byref(vb)) == 0
+    assert kb.value == vb.value == 32 * 32 * 32768 * 128 * 2
+    assert L.ffa_cache_bytes(capi.F32, 1, 32, 1000, 64, C.byref(kb), C.byref(vb)) == 0
+    assert kb.value == 32 * 1000 * 64 * 4
+    assert L.ffa_cache_bytes(7, 1, 1, 8, 64, C.byref(kb), C.byref(vb)) == -1
+    assert L.ffa_cache_bytes(capi.F16, 1, 1, 8, 96, C.byref(kb), C.byref(vb)) == -2
+    assert b"head_dim" in L.ffa_last_error()
+    assert L.ffa_cache_bytes(capi.F16, 0, 1, 8, 64, C.byref(kb), C.byref(vb)) == -3
+    assert L.ffa_cache_init(capi.F16, 1, 1, 9, 8, 64, None, None, None, None, None) == -3
+    assert L.ffa_attention(None, None, None, None, None, None, None, 1.0, 0, None, 1, 0.0, None, None) == -4
+    assert L.ffa_workspace_bytes(None, 0) == 0
+    assert L.ffa_launch_count() == 0
+
+
+def test_python_module_fails_loudly_when_extension_is_missing(monkeypatch):
+    import importlib
+
+    import fastforwardattention_b200 as pkg
+
+    def boom(name, package=None):
+        raise ImportError("no module")
+
+    monkeypatch.setattr(importlib, "import_module", boom)
+    with pytest.raises(ImportError, match="compiled extension is missing"):
+        pkg.FastForwardAttn
+
+
+def test_extension_class_surface():
+    from ff_attention import FastForwardAttn
+
+    for name in ("attention", "get_cache", "set_mode", "launch_shape", "device_status"):
+        assert hasattr(FastForwardAttn, name)
+    import torch
+
+    with pytest.raises(RuntimeError, match="CUDA tensors"):
+        FastForwardAttn(torch.zeros(1, 1, 4, 64), torch.zeros(1, 1, 4, 64), 8, False)

@@ -1,0 +1,119 @@
+"""The Python class, driven the way the reference's example.py and HF forks drive it."""
+import math
+
+import pytest
+import torch
+
+from oracle import ffa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_example_py_loop():
+    """example.py:9-46 with a seed: fp16, batch 10, 32 heads, head_dim 64, prompt 1024, 128
+    steps, U[0,1) inputs, optimized launch, p = 0, max relative difference < 1e-2."""
+    from ff_attention import FastForwardAttn as FFA
+
+    torch.manual_seed(0)
+    B, H, Dh, Lp, n = 10, 32, 64, 1024, 128
+    dt = torch.float16
+    temp = 1 / math.sqrt(Dh)
+    K = torch.rand(B, H, Lp, Dh, dtype=dt).cuda()
+    V = torch.rand(B, H, Lp, Dh, dtype=dt).cuda()
+    ffa = FFA(K, V, Lp + n, False)
+    for i in range(n):
+        k = torch.rand(B, H, 1, Dh, dtype=dt).cuda()
+        v = torch.rand(B, H, 1, Dh, dtype=dt).cuda()
+        q = torch.rand(B, H, 1, Dh, dtype=dt).cuda()
+        t = Lp + i
+        out = ffa.attention(q, k, v, temp, t, 0)
+        K = torch.cat([K, k], axis=-2)
+        V = torch.cat([V, v], axis=-2)
+        if i % 16 == 0 or i == n - 1:
+            ref = O.torch_attn_func(q.view(B * H, 1, Dh).cpu(), K.view(B * H, t + 1, Dh).cpu(),
+                                    V.view(B * H, t + 1, Dh).cpu(), temp)
+            rel = ((ref.view(B, H, 1, Dh) - out.view(B, H, 1, Dh).cpu()).abs() / ref.view(B, H, 1, Dh)).max()
+            assert rel < 1e-2
+            assert (ref.view(B, H, Dh).float() - out.cpu().float()).abs().max() <= 2e-3
+    assert out.shape == (B, H, Dh) and out.dtype == dt
+    assert ffa.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
+def test_overloads_and_get_cache(dt):
+    """modeling_opt.py:201-226 / modeling_gptj.py:259-279 call convention: q/k/v as
+    [B, 1, H*Dh], caches fetched with get_cache() and passed back, left-padding lengths."""
+    from fastforwardattention_b200 import FastForwardAttn
+
+    g = torch.Generator().manual_seed(3)
+    B, H, Dh, Lp, Lmax = 3, 4, 64, 40, 44
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    ffa = FastForwardAttn(K.cuda(), V.cuda(), Lmax, True)
+    kc, vc = ffa.get_cache()
+    assert kc.shape == (B, H, Lmax, Dh) and vc.shape == (B, H, Lmax, Dh)
+    pads = torch.tensor([0, 7, 39], dtype=torch.int32)
+    orc = O.DecodeOracle(K, V, Lmax, compute_dtype=torch.float64)
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dt]
+    for i in range(3):
+        t = Lp + i
+        q, k, v = (torch.randn(B, 1, H * Dh, generator=g).to(dt) for _ in range(3))
+        orc.append(k, v, t)
+        if i == 0:
+            out = ffa.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, t)            # p defaults to 0
+        elif i == 1:
+            out = ffa.attention(q.cuda(), k.cuda(), v.cuda(), kc, vc, 0.125, t, 0)
+        else:
+            out = ffa.attention(q.cuda(), k.cuda(), v.cuda(), kc, vc, 0.125, t, pads.cuda(), 0)
+        fk = pads.repeat_interleave(H) if i == 2 else None
+        want, _, _ = O.pruned_attention(q.view(B * H, Dh).double(), orc.K[:, : t + 1], orc.V[:, : t + 1], 0.125, 0.0,
+                                        first_key=fk, eps=0.0)
+        assert (out.view(B * H, Dh).cpu().double() - want.double()).abs().max() <= tol
+        assert torch.equal(kc[:, :, t].cpu().view(B, 1, H * Dh), k)
+    buf = torch.empty(B, H, Dh, dtype=dt, device="cuda")
+    assert ffa.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, Lmax - 1, 0.0, out=buf).data_ptr() == buf.data_ptr()
+    assert ffa.device_status() == 0
+    shape = ffa.launch_shape(Lp)
+    assert shape["grid"] >= 1 and shape["tile_rows"] % 8 == 0
+
+
+def test_errors_raise():
+    from fastforwardattention_b200 import FastForwardAttn
+
+    K = torch.zeros(1, 2, 8, 64, dtype=torch.float16, device="cuda")
+    ffa = FastForwardAttn(K, K.clone(), 16, False)
+    q = torch.zeros(1, 2, 1, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="curr_timestep"):
+        ffa.attention(q, q, q, 0.125, 16, 0)
+    with pytest.raises(RuntimeError, match="dtype"):
+        ffa.attention(q.float(), q, q, 0.125, 8, 0)
+    with pytest.raises(RuntimeError, match="elements"):
+        ffa.attention(q[:, :1], q, q, 0.125, 8, 0)
+    with pytest.raises(RuntimeError, match="max_timesteps"):
+        FastForwardAttn(K, K.clone(), 4, False)
+    with pytest.raises(RuntimeError, match="unsupported tensor type"):
+        FastForwardAttn(K.double(), K.double(), 16, False)
+    with pytest.raises(RuntimeError, match="head_dim"):
+        FastForwardAttn(K[..., :48].contiguous(), K[..., :48].contiguous(), 16, False)
+
+
+def test_pruning_through_python_class():
+    from fastforwardattention_b200 import FastForwardAttn
+    from fastforwardattention_b200.workloads import CONFIGS, prompt_kv, step_qkv
+    from dataclasses import replace
+
+    w = replace(CONFIGS["prune-fp16-b10-p1e-3"], B=2, steps=4)
+    K, V = prompt_kv(w)
+    ffa = FastForwardAttn(K.cuda(), V.cuda(), w.max_len, False)
+    ffa.record_kept_mask(True)
+    orc = O.DecodeOracle(K, V, w.max_len)
+    N = w.B * w.H
+    for t, q, k, v in step_qkv(w):
+        out = ffa.attention(q.cuda(), k.cuda(), v.cuda(), w.scale, t, w.p)
+        orc.append(k, v, t)
+        want, kept, info = O.pruned_attention(q.view(N, w.Dh), orc.K[:, : t + 1], orc.V[:, : t + 1], w.scale, w.p)
+        m = ffa.get_kept_mask().cpu().view(N, -1).to(torch.int64) & 0xFFFFFFFF
+        bits = ((m[:, :, None] >> torch.arange(32)[None, None, :]) & 1).reshape(N, -1)[:, : t + 1].bool()
+        assert torch.equal(bits, kept)
+        assert (out.view(N, w.Dh).cpu().float() - want.float()).abs().max() <= 2e-3
+    assert ffa.device_status() == 0

@@ -1,0 +1,86 @@
+"""Host logic of the head-sharded path on two CPU ranks (gloo).  The per-rank engine is a
+stand-in built on the oracle: what is tested here is the partition arithmetic and the
+gather layout, not the kernel."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class OracleEngine:
+    def __init__(self, K, V, max_len, use_default):
+        from oracle.ffa_oracle import DecodeOracle
+
+        self.o = DecodeOracle(K, V, max_len)
+
+    def attention(self, q, k, v, scale, t, p=0.0):
+        return self.o.step(q, k, v, scale, t)
+
+    def get_cache(self):
+        return self.o.K, self.o.V
+
+
+def _worker(rank, world, port, q_out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fastforwardattention_b200.sharded import ShardedFastForwardAttn, head_range, shard_heads
+        from oracle.ffa_oracle import DecodeOracle
+
+        g = torch.Generator().manual_seed(0)
+        B, H, Dh, Lp, steps = 2, 4, 64, 9, 3
+        K = torch.randn(B, H, Lp, Dh, generator=g)
+        V = torch.randn(B, H, Lp, Dh, generator=g)
+        full = DecodeOracle(K, V, Lp + steps)
+        eng = ShardedFastForwardAttn(shard_heads(K, rank, world, H), shard_heads(V, rank, world, H), Lp + steps,
+                                     False, engine_factory=OracleEngine)
+        assert head_range(H, rank, world) == (rank * H // world, (rank + 1) * H // world)
+        worst = 0.0
+        for i in range(steps):
+            q, k, v = (torch.randn(B, 1, H * Dh, generator=g) for _ in range(3))   # HF layout
+            want = full.step(q, k, v, 0.125, Lp + i)
+            ql, kl, vl = (shard_heads(x, rank, world, H) for x in (q, k, v))
+            local = eng.attention(ql, kl, vl, 0.125, Lp + i)
+            lo, hi = head_range(H, rank, world)
+            worst = max(worst, (local - want[:, lo:hi]).abs().max().item())
+            got = eng.attention(ql, kl, vl, 0.125, Lp + i, gather=True)
+            assert got.shape == (B, H, Dh)
+            worst = max(worst, (got - want).abs().max().item())
+        q_out.put((rank, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharding_and_gather_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert sorted(r for r, _ in res) == [0, 1]
+    assert all(w < 1e-6 for _, w in res)
+
+
+def test_head_range_rejects_uneven_split():
+    from fastforwardattention_b200.sharded import head_range
+
+    with pytest.raises(ValueError):
+        head_range(6, 0, 4)
