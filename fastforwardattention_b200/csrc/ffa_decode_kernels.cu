@@ -768,12 +768,18 @@ int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes)
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
-        cudaError_t e;
-        e = cudaFuncSetAttribute(ffa_stream_kernel<T, DH, kPassOne>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes);
+        // the opt-in limit covers static + dynamic shared memory of a kernel
+        auto raise_limit = [&](const void* fn) -> cudaError_t {
+            cudaFuncAttributes a;
+            cudaError_t err = cudaFuncGetAttributes(&a, fn);
+            if (err != cudaSuccess) return err;
+            return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes - (int)a.sharedSizeBytes);
+        };
+        cudaError_t e = raise_limit(reinterpret_cast<const void*>(ffa_stream_kernel<T, DH, kPassOne>));
         if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(ffa_stream_kernel<T, DH, kPassScore>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes);
+        e = raise_limit(reinterpret_cast<const void*>(ffa_stream_kernel<T, DH, kPassScore>));
         if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(ffa_value_gather_kernel<T, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes);
+        e = raise_limit(reinterpret_cast<const void*>(ffa_value_gather_kernel<T, DH>));
         return (int)e;
     });
 }
