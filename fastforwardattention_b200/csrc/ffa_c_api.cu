@@ -109,13 +109,6 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
 Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int tensors)
 {
     Shape s = default_shape(p, row_bytes, rows_total, tensors);
-    const double bytes = (double)rows_total * row_bytes * tensors;
-    if (bytes >= 512e6) {
-        // long sequences: one CTA per SM with a deep ring keeps ~100 KB per SM in flight
-        s.cps = 1;
-        s.stages = tensors == 2 ? 6 : 8;
-        s.warps = 8;
-    }
     return s;
 }
 
