@@ -36,8 +36,8 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the streaming kernel divided by
 # the launch's algorithmic bytes, from the ncu capture summarised under profiles/ (captured on
 # the 2048-token case and scaled by bytes streamed, which is what the kernel's traffic is
-# proportional to).  None until a capture exists.
-TRAFFIC_RATIO = None
+# proportional to).
+TRAFFIC_RATIO = 1.004
 
 
 def algorithmic_bytes(es, B, H, Dh, t):
