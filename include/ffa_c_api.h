@@ -115,6 +115,32 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
                   void* out, float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding,
                   float p, uint32_t* kept_mask, void* stream);
 
+/* The exact (p == 0, no per-sample lengths) decode step with NO caller-provided workspace and
+ * no allocation of any kind inside the call.  It has no counterpart in the reference; it
+ * exists for hosts that cannot allocate device memory when they call the engine: a server
+ * whose own pool allocator took the whole GPU at start-up (a cudaMalloc from a plug-in then
+ * fails or is against policy), a latency-critical decode thread that must not pay the
+ * device-wide synchronisation of cudaMalloc / cudaFree, or a bare C host that owns only the
+ * six tensors of the call.  The scratch (split partials, arrival counters, status word)
+ * lives in a 4 MiB static device array that every GPU loading this library holds until
+ * process exit.  Limits and rules:
+ *   - sizes whose scratch need exceeds 4 MiB are rejected with FFA_ERR_RANGE (need =
+ *     256 + 4*batch*heads + 4*(grid + batch*heads)*(head_dim + 2) bytes, grid <= 2 CTAs per SM;
+ *     e.g. batch*heads = 1024 at head_dim 128 needs 0.7 MiB); use ffa_attention beyond that;
+ *   - the array is shared by every call on that GPU and keeps the previous call's contents;
+ *     each call clears the counters and status word on `stream` before launching, and calls
+ *     whose kernels overlap on one GPU (other streams, other host threads) race -- keep them
+ *     stream-ordered;
+ *   - the first call on each device performs a one-time set-up (device address of the array,
+ *     device queries, kernel attributes); make that first call outside any stream capture.
+ * Arguments as for ffa_attention.  device_status: optional DEVICE int the kernel ORs its
+ * FFA_STATUS_* bits into (caller-owned, caller-cleared); NULL keeps them in the static
+ * array.  error_text: optional HOST buffer that receives the reason for a non-zero return. */
+int ffa_attention_static_scratch(int dtype, int batch, int heads, int head_dim, int max_len, const void* q,
+                                 const void* k, const void* v, void* k_cache, void* v_cache, void* out,
+                                 float softmax_scale, int t, int* device_status, void* stream, char* error_text,
+                                 size_t error_text_len);
+
 /* Synchronises the stream and returns the device status word (0 = clean) in *status, then
  * clears it.  The reference only printf()s cudaGetLastError (attention.cu:1444-1451). */
 int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
