@@ -13,9 +13,13 @@ Two things are restated here, each from the reference file and lines it follows:
 * the pruning rule of the reference's CUDA kernel (attention.cu:1108-1126 softmax incl. the
   left-padding mask, :1184-1191 threshold and skip, :461-469 ``leq``, :1227-1256 new token is
   always kept).  The reference has no test that passes p > 0 and no CPU implementation of the
-  rule, so the restated rule is "parity unpinned" by the reference's tests; the fp16
-  comparison quirk inside it IS pinned, exhaustively, against the CUDA toolkit's own host
-  implementation of the same expression (see oracle/half_leq_host.cu and tests/test_oracle.py).
+  rule, so no reference TEST pins it.  It is pinned instead against the reference itself:
+  (a) the fp16 comparison quirk, exhaustively, against the CUDA toolkit's own host
+  implementation of the same expression (oracle/half_leq_host.cu, tests/test_oracle.py);
+  (b) the whole rule against the reference's own CUDA kernel, compiled unmodified into
+  oracle/_ref and run on a GPU, whose kept set is read off its output with one-hot value rows
+  (tests/test_reference_kernel_gpu.py): identical in fp32, identical in fp16 outside a band
+  of the reference's own fp16 score noise around the threshold.
 """
 from __future__ import annotations
 
