@@ -32,7 +32,8 @@ namespace {
 
 constexpr int kPassOne = 0;
 constexpr int kPassScore = 1;
-constexpr uint32_t kWaitLimit = 1u << 22;  // bounded barrier wait: ~1 s, then give up
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bounded barrier wait: 2 s, then give up
+constexpr uint32_t kDrainPolls = 1u << 20;
 constexpr int kStatusWaitTimeout = 1;
 constexpr int kStatusBadLength = 2;
 constexpr int kGatherThreads = 256;
@@ -66,17 +67,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity.  Never spins for ever: after kWaitLimit polls
-// (or as soon as another thread of the CTA gave up) it raises the CTA's `dead` flag and
+// same, but the hardware may park the thread for up to `hint_ns` before answering
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the phase with the given parity.  Never spins for ever: after kWaitLimitNs of wall
+// time (or as soon as another thread of the CTA gave up) it raises the CTA's `dead` flag and
 // returns false; callers then skip the data but keep walking the same control flow so every
 // CTA-level barrier is still reached by everyone.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* dead)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
         if (*dead) return false;
-        if (i > 32) __nanosleep(128);
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
     }
     *dead = 1;
     return false;
@@ -111,6 +132,11 @@ struct Elem<float> {
         f[0] = __uint_as_float(r.x), f[1] = __uint_as_float(r.y), f[2] = __uint_as_float(r.z),
         f[3] = __uint_as_float(r.w);
     }
+    static __device__ __forceinline__ void unpack2(const uint4& r, float2* f)
+    {
+        f[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+        f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+    }
     static __device__ __forceinline__ float round(float x) { return x; }
     static __device__ __forceinline__ void store(float* p, float x) { *p = x; }
     // attention.cu:461-464
@@ -127,6 +153,12 @@ struct Elem<__half> {
             float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
             f[2 * i] = t.x, f[2 * i + 1] = t.y;
         }
+    }
+    static __device__ __forceinline__ void unpack2(const uint4& r, float2* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
     }
     static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
     static __device__ __forceinline__ void store(__half* p, float x) { *p = __float2half_rn(x); }
@@ -151,6 +183,12 @@ struct Elem<__nv_bfloat16> {
             f[2 * i] = __uint_as_float(w[i] << 16);
             f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
+    }
+    static __device__ __forceinline__ void unpack2(const uint4& r, float2* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
     }
     static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
     static __device__ __forceinline__ void store(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
@@ -280,32 +318,34 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
     if (threadIdx.x < 32) {
         // ---------------- producer ----------------
         if (threadIdx.x == 0) {
-            uint32_t it = 0;
+            uint32_t issued = 0, stage = 0, use = 0;  // ring position: buffer index and how often it was used
             int cur_b = -1;
             SampleRange sr{0, 0, false};
-            for (long long u = u0; u < u1; ++u) {
-                const int bh = (int)(u / upb), j = (int)(u - (long long)bh * upb);
+            long long u = u0;
+            int bh = (int)(u0 / upb), j = (int)(u0 - (long long)bh * upb);
+            for (; u < u1; ++u, ++j) {
+                if (j == upb) j = 0, ++bh;
                 const int b = bh / P.H;
                 if (b != cur_b) sr = sample_range(P, b), cur_b = b;
                 if (!sr.ok) continue;
                 const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
                 if (hi <= lo) continue;
-                const uint32_t s = it % S, use = it / S;
-                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * s, (use - 1) & 1, flags)) break;
+                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
                 const uint32_t bytes = (uint32_t)(hi - lo) * ROWB;
                 const size_t off = ((size_t)bh * P.Lmax + lo) * ROWB;
-                mbar_expect_tx(bar_full + 8 * s, bytes * TENSORS);
-                bulk_copy_g2s(ring + s * stage_bytes, kc + off, bytes, bar_full + 8 * s);
-                if (TENSORS == 2) bulk_copy_g2s(ring + s * stage_bytes + tile_bytes, vc + off, bytes, bar_full + 8 * s);
-                ++it;
+                mbar_expect_tx(bar_full + 8 * stage, bytes * TENSORS);
+                bulk_copy_g2s(ring + stage * stage_bytes, kc + off, bytes, bar_full + 8 * stage);
+                if (TENSORS == 2) bulk_copy_g2s(ring + stage * stage_bytes + tile_bytes, vc + off, bytes, bar_full + 8 * stage);
+                ++issued;
+                if (++stage == (uint32_t)S) stage = 0, ++use;
             }
             if (flags[0]) {
                 // gave up: let the copies already issued land before the CTA releases its
                 // shared memory (bounded again)
-                const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
+                const uint32_t pending = issued < (uint32_t)S ? issued : (uint32_t)S;
                 for (uint32_t k = 0; k < pending; ++k) {
-                    const uint32_t id = it - 1 - k, s = id % S, use = id / S;
-                    for (uint32_t n = 0; n < kWaitLimit && !mbar_try_wait(bar_full + 8 * s, use & 1); ++n) __nanosleep(256);
+                    const uint32_t id = issued - 1 - k, st = id % S, us = id / S;
+                    for (uint32_t n = 0; n < kDrainPolls && !mbar_try_wait(bar_full + 8 * st, us & 1); ++n) __nanosleep(256);
                 }
             }
         }
@@ -314,7 +354,9 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
         const int ctid = threadIdx.x - 32;
         const int lane = ctid & 31;
         const int g = ctid / LPR, li = ctid % LPR;
-        uint32_t it = 0;
+        constexpr int E2 = EPV / 2;
+        constexpr bool kAllLanes = (VPR == LPR * VPL);  // false only for head_dim 80
+        uint32_t stage = 0, phase = 0;
         long long u = u0;
         while (u < u1) {
             const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
@@ -328,17 +370,21 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
             float qf[VPL][EPV];
             load_row_f32<T, DH>(static_cast<const unsigned char*>(P.q) + (size_t)bh * ROWB, li, qf);
             const float qmul = kPrecise ? 1.f : P.scale * kLog2e;
+            float2 q2[VPL][E2];
 #pragma unroll
             for (int x = 0; x < VPL; ++x)
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) qf[x][e] *= qmul;
+                for (int e = 0; e < EPV; ++e) {
+                    qf[x][e] *= qmul;
+                    if (e & 1) q2[x][e >> 1] = make_float2(qf[x][e - 1], qf[x][e]);
+                }
 
             float m = -CUDART_INF_F, l = 0.f;
-            float acc[VPL][EPV];
+            float2 acc2[VPL][E2];
 #pragma unroll
             for (int x = 0; x < VPL; ++x)
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) acc[x][e] = 0.f;
+                for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
 
             auto score_of = [&](float dot) -> float {
                 if (!kPrecise) return dot;
@@ -347,70 +393,99 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
             };
             auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
 
-            for (int j = j0; j < j1; ++j) {
-                const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
-                if (!sr.ok || hi <= lo) continue;
-                const int nrows = hi - lo;
-                const uint32_t s = it % S, use = it / S;
-                ++it;
-                if (!mbar_wait_bounded(bar_full + 8 * s, use & 1, flags)) continue;
-                const unsigned char* ks = smem + (size_t)s * stage_bytes;
-                const unsigned char* vs = ks + tile_bytes;
-                for (int base = 0; base < nrows; base += 4 * NG) {
-                    float sc[4];
-                    int rr[4];
+            // Four rows per lane group at a time: all shared-memory loads first, then the
+            // packed fp32 FMAs (fma.rn.f32x2), four interleaved butterfly sums, one softmax
+            // update.  FULL: every row of the batch exists (no predicates, no clamping).
+            auto batch = [&](auto full_tag, const unsigned char* ks, const unsigned char* vs, int base, int nrows, int row0) {
+                constexpr bool FULL = decltype(full_tag)::value;
+                int rc[4];
+                uint4 kraw[4][VPL];
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu) {
-                        const int r = base + uu * NG + g;
-                        const bool okr = r < nrows;
-                        rr[uu] = okr ? r : 0;
-                        float dot = 0.f;
+                for (int uu = 0; uu < 4; ++uu) {
+                    const int r = base + uu * NG + g;
+                    rc[uu] = FULL ? r : min(r, nrows - 1);
 #pragma unroll
-                        for (int x = 0; x < VPL; ++x) {
-                            const int vec = li + x * LPR;
-                            if (vec < VPR && okr) {
-                                float kf[EPV];
-                                Elem<T>::unpack(*reinterpret_cast<const uint4*>(ks + (size_t)r * ROWB + vec * 16), kf);
+                    for (int x = 0; x < VPL; ++x)
+                        if (kAllLanes || li + x * LPR < VPR)
+                            kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc[uu] * ROWB + (li + x * LPR) * 16);
+                }
+                float sc[4];
 #pragma unroll
-                                for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[e], dot);
-                            }
+                for (int uu = 0; uu < 4; ++uu) {
+                    float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x)
+                        if (kAllLanes || li + x * LPR < VPR) {
+                            float2 k2[E2];
+                            Elem<T>::unpack2(kraw[uu][x], k2);
+#pragma unroll
+                            for (int e = 0; e < E2; ++e) a = __ffma2_rn(q2[x][e], k2[e], a);
                         }
-                        dot = group_sum<LPR>(dot);
-                        sc[uu] = okr ? score_of(dot) : -CUDART_INF_F;
-                    }
-                    const float m_new = fmaxf(fmaxf(fmaxf(m, sc[0]), fmaxf(sc[1], sc[2])), sc[3]);
-                    if (m_new == -CUDART_INF_F) continue;  // this group has no row in this batch of rows
-                    const float corr = expo(m - m_new);
-                    m = m_new;
-                    l *= corr;
-                    if (PASS == kPassOne) {
+                    sc[uu] = a.x + a.y;
+                }
+#pragma unroll
+                for (int off = LPR / 2; off >= 1; off >>= 1)
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu) sc[uu] += __shfl_xor_sync(0xffffffffu, sc[uu], off);
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) sc[uu] = (FULL || base + uu * NG + g < nrows) ? score_of(sc[uu]) : -CUDART_INF_F;
+                const float m_new = fmaxf(fmaxf(fmaxf(m, sc[0]), fmaxf(sc[1], sc[2])), sc[3]);
+                if (!FULL && m_new == -CUDART_INF_F) return;  // this group has no row in this batch
+                const float corr = expo(m - m_new);
+                m = m_new;
+                float pr[4];
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) pr[uu] = expo(sc[uu] - m);
+                l = fmaf(l, corr, (pr[0] + pr[1]) + (pr[2] + pr[3]));
+                if (PASS == kPassOne) {
+                    uint4 vraw[4][VPL];
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu)
 #pragma unroll
                         for (int x = 0; x < VPL; ++x)
+                            if (kAllLanes || li + x * LPR < VPR)
+                                vraw[uu][x] = *reinterpret_cast<const uint4*>(vs + (size_t)rc[uu] * ROWB + (li + x * LPR) * 16);
+                    const float2 c2 = make_float2(corr, corr);
 #pragma unroll
-                            for (int e = 0; e < EPV; ++e) acc[x][e] *= corr;
-                    }
+                    for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                        for (int e = 0; e < E2; ++e) acc2[x][e] = __fmul2_rn(acc2[x][e], c2);
 #pragma unroll
                     for (int uu = 0; uu < 4; ++uu) {
-                        const float pr = expo(sc[uu] - m);
-                        l += pr;
-                        if (PASS == kPassOne) {
+                        const float2 p2 = make_float2(pr[uu], pr[uu]);
 #pragma unroll
-                            for (int x = 0; x < VPL; ++x) {
-                                const int vec = li + x * LPR;
-                                if (vec < VPR && pr != 0.f) {
-                                    float vf[EPV];
-                                    Elem<T>::unpack(*reinterpret_cast<const uint4*>(vs + (size_t)rr[uu] * ROWB + vec * 16), vf);
+                        for (int x = 0; x < VPL; ++x)
+                            if (kAllLanes || li + x * LPR < VPR) {
+                                float2 v2[E2];
+                                Elem<T>::unpack2(vraw[uu][x], v2);
 #pragma unroll
-                                    for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr, vf[e], acc[x][e]);
-                                }
+                                for (int e = 0; e < E2; ++e) acc2[x][e] = __ffma2_rn(p2, v2[e], acc2[x][e]);
                             }
-                        } else if (li == 0 && sc[uu] != -CUDART_INF_F) {
-                            P.scores[(size_t)bh * P.Lmax + lo + base + uu * NG + g] = sc[uu];
-                        }
                     }
+                } else if (li == 0) {
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu)
+                        if (FULL || base + uu * NG + g < nrows) P.scores[(size_t)bh * P.Lmax + row0 + base + uu * NG + g] = sc[uu];
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            };
+
+            if (sr.ok) {
+                for (int j = j0; j < j1; ++j) {
+                    const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
+                    if (hi <= lo) continue;
+                    const int nrows = hi - lo;
+                    const bool ready = mbar_wait_bounded(bar_full + 8 * stage, phase, flags);
+                    const unsigned char* ks = smem + (size_t)stage * stage_bytes;
+                    const unsigned char* vs = ks + tile_bytes;
+                    if (ready) {
+                        int base = 0;
+                        for (; base + 4 * NG <= nrows; base += 4 * NG) batch(std::true_type{}, ks, vs, base, nrows, lo);
+                        if (base < nrows) batch(std::false_type{}, ks, vs, base, nrows, lo);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+                    if (++stage == (uint32_t)S) stage = 0, phase ^= 1;
+                }
             }
 
             // ---- the new token: score against k, append k (and v) at row sr.row ----
@@ -440,10 +515,13 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                             if (PASS == kPassOne) {
                                 const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + src);
                                 *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
-                                float vf[EPV];
-                                Elem<T>::unpack(vraw, vf);
+                                float2 v2[E2];
+                                Elem<T>::unpack2(vraw, v2);
 #pragma unroll
-                                for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr, vf[e], acc[x][e] * corr);
+                                for (int e = 0; e < E2; ++e) {
+                                    acc2[x][e].x = fmaf(pr, v2[e].x, acc2[x][e].x * corr);
+                                    acc2[x][e].y = fmaf(pr, v2[e].y, acc2[x][e].y * corr);
+                                }
                             }
                         }
                     }
@@ -459,9 +537,9 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                     const int vec = li + x * LPR;
                     if (vec < VPR) {
 #pragma unroll
-                        for (int e = 0; e < EPV; e += 4)
-                            *reinterpret_cast<float4*>(mine + vec * EPV + e) =
-                                make_float4(acc[x][e], acc[x][e + 1], acc[x][e + 2], acc[x][e + 3]);
+                        for (int e = 0; e < E2; e += 2)
+                            *reinterpret_cast<float4*>(mine + vec * EPV + 2 * e) =
+                                make_float4(acc2[x][e].x, acc2[x][e].y, acc2[x][e + 1].x, acc2[x][e + 1].y);
                     }
                 }
             }
