@@ -83,32 +83,48 @@ Carve carve(const ffa_plan* p, bool with_scores)
 
 // ---- planner -------------------------------------------------------------------------------
 // The streaming kernels take (tile_rows, stages, consumer_warps, ctas_per_sm).  The flat unit
-// list is cut evenly over the grid, so the only shape questions are: enough bytes in flight
-// per SM to cover HBM latency (ring depth x tile size x resident CTAs), tiles small enough
-// that every CTA gets several units when batch*heads*t is small, and the shared-memory
-// budget.  The default rule below fixes 2 resident CTAs with a 3-deep ring of 16 KB tiles
-// per tensor; the measured table refines that per (row bytes, work size).
+// list is cut evenly over the grid, so the shape questions are: enough bytes in flight per SM
+// to cover HBM latency (ring depth x tile size x resident CTAs) but not many more (sweeps on
+// B200 lose 4-7 % of bandwidth with a third stage: more concurrent streams, worse DRAM page
+// locality), compute warps enough to keep up with the ring, tiles small enough that every CTA
+// gets several units when batch*heads*t is small, and the shared-memory budget.
 struct Shape {
     int tile_rows, stages, warps, cps;
 };
 
+// Fixed analytic rule: 16 KB tiles per tensor (4 rows per lane group and batch at 8 compute
+// warps... 8 at 4 warps), a 2-deep ring, 4 compute warps, 2 CTAs per SM.
 Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int tensors)
 {
-    (void)p;
+    (void)p, (void)rows_total;
     Shape s;
-    s.warps = 8;
+    s.warps = 4;
     s.cps = 2;
-    s.stages = tensors == 2 ? 3 : 4;
+    s.stages = tensors == 2 ? 2 : 3;
     s.tile_rows = 16384 / row_bytes;
-    (void)rows_total;
     return s;
 }
 
-// Winners of the sweep on B200 (see the tuning script beside the package); keyed by the
-// bytes one decode step streams.  Falls back to the default rule for shapes it has not seen.
+// Refinements measured with `python -m fastforwardattention_b200.tune` on B200 (CUDA-graph
+// timing, replicas rotating so that every launch streams from HBM), keyed by row bytes and by
+// the bytes one decode step streams:
+//   < 48 MB  (OPT-1.3B fp32 batch 1, 16 MB: 12.9 us vs 17.3 us)  one CTA per SM: fewer split
+//            partials and arrival counters to merge than bytes to stream
+//   48-600 MB, 256-byte rows (bf16 x 128, 270 MB: 5.43 vs 5.14 TB/s)  8 KB tiles, 4 CTAs per SM:
+//            the ring fills sooner and the tail is shorter
+//   48-600 MB, >= 512-byte rows (GPT-J fp16 x 256, 269 MB: 5.53 vs 5.36 TB/s)  8 compute warps
+//   otherwise the rule above (bf16 x 128: 7.35 TB/s at 32 K tokens, 7.22 at 8 K, 6.67 at 2 K;
+//            fp16 x 64, 103 MB: 4.20 TB/s)
 Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int tensors)
 {
     Shape s = default_shape(p, row_bytes, rows_total, tensors);
+    const double bytes = (double)rows_total * row_bytes * tensors;
+    if (bytes < 48e6) {
+        s.cps = 1;
+    } else if (bytes < 600e6) {
+        if (row_bytes >= 512) s.warps = 8;
+        else if (row_bytes == 256) s.tile_rows /= 2, s.cps = 4;
+    }
     return s;
 }
 
