@@ -64,44 +64,56 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region (read-only query)."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """nvidia-smi clocks and throttle reasons (read-only query), sampled every 50 ms from before
+    the timed region until after it; only samples whose timestamp falls inside the window given
+    to summary() are reported."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc = index, None   # an nvidia-smi id: index or GPU-<uuid>
+        self.index, self.proc, self.rows = index, None, []   # an nvidia-smi id: index or GPU-<uuid>
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            time.sleep(0.4)   # let it start producing before the timed region begins
         except Exception:
             self.proc = None
         return self
 
-    def __exit__(self, *a):
-        self.rows = []
+    def stop(self):
         if self.proc is None:
             return
+        time.sleep(0.06)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             out = ""
+        import datetime
+
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) >= 7:
-                self.rows.append(f)
+            if len(f) >= 8:
+                try:
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                except ValueError:
+                    continue
+                self.rows.append((ts, f[1:]))
 
-    def summary(self):
-        if not getattr(self, "rows", None):
+    def summary(self, t0, t1):
+        rows = [r for ts, r in self.rows if t0 <= ts <= t1]
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[3 + i] == "Active" for r in self.rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self.rows[0][1]),
-                "power_w_max": max(float(r[2]) for r in self.rows), "reasons": reasons, "samples": len(self.rows)}
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i] == "Active" for r in rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(rows[0][1]),
+                "power_w_max": max(float(r[2]) for r in rows), "reasons": reasons, "samples": len(rows),
+                "window": "timed steps, continued untimed with the same steps up to 0.5 s when shorter"}
 
 
 class CpuReferenceSample:
@@ -164,8 +176,9 @@ def workload_config(w, n):
             "decode_steps": w.steps, "final_len": w.max_len, "p": w.p,
             "parallelism": f"heads sharded over {n} GPU(s), {w.H // n} heads each" if n > 1 else "single GPU",
             "l2": "inputs larger than L2: every step streams the whole KV cache shard from HBM"
-                  if 2 * w.B * (w.H // n) * w.max_len * w.Dh * w.dtype.itemsize > 2 * 126e6 else
-                  "KV shard smaller than L2; an L2 flush (256 MB write) runs between timed steps"}
+                  if 2 * w.B * (w.H // n) * w.max_len * w.Dh * w.dtype.itemsize >= 600e6 else
+                  "KV shard below 600 MB: steps rotate over engine replicas (>= 600 MB of caches together), "
+                  "so every step streams from HBM; no flush kernel"}
 
 
 def main():
@@ -198,75 +211,96 @@ def main():
 
     w = full.shard(rank, world) if world > 1 else full
     es = w.dtype.itemsize
-    K, V = device_prompt_kv(w, dev)
-    eng = ShardedFastForwardAttn(K, V, w.max_len, False) if world > 1 else None
-    ffa = eng.engine if eng is not None else FastForwardAttn(K, V, w.max_len, False)
-    del K, V
+    # Engines: one for the default workload.  A workload whose KV shard is not several times the
+    # 126 MB L2 gets replicas with their own caches, used round-robin, so that every timed step
+    # streams from HBM without a flush kernel in between (a zero-fill flush leaves dirty lines
+    # whose write-back then competes with the step being timed).
+    kv_bytes = 2 * w.B * w.H * w.max_len * w.Dh * es
+    nrep = 1 if kv_bytes >= 600e6 else min(16, -(-int(600e6) // kv_bytes))
+    from dataclasses import replace
+
+    sharded, engines = [], []
+    for r in range(nrep):
+        K, V = device_prompt_kv(replace(w, seed=w.seed + 17 * r), dev)
+        if world > 1:
+            sharded.append(ShardedFastForwardAttn(K, V, w.max_len, False))
+            engines.append(sharded[-1].engine)
+        else:
+            engines.append(FastForwardAttn(K, V, w.max_len, False))
+        del K, V
     torch.cuda.empty_cache()
     if args.launch:
-        ffa.set_launch(*[int(x) for x in args.launch.split(",")])
-    shape = ffa.launch_shape(w.max_len - 1)
+        for e in engines:
+            e.set_launch(*[int(x) for x in args.launch.split(",")])
+    shape = engines[0].launch_shape(w.max_len - 1)
 
     total = args.warmup + args.steps
     g = torch.Generator(device=dev).manual_seed(w.seed + 1)
     qkv_d = torch.randn(total, 3, w.B, w.H, 1, w.Dh, generator=g, device=dev, dtype=torch.float32).to(w.dtype)
     qkv_h = qkv_d.cpu().pin_memory()
     out_d = torch.empty(w.B, w.H, w.Dh, dtype=w.dtype, device=dev)
-    out_h = torch.empty(w.B, w.H, w.Dh, dtype=w.dtype).pin_memory()
     stage = torch.empty(3, w.B, w.H, 1, w.Dh, dtype=w.dtype, device=dev)
-    small = 2 * w.B * w.H * w.max_len * w.Dh * es <= 2 * 126e6
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
-    t_of = lambda s: w.prompt + (s % w.steps)
+    out_h = torch.empty(w.B, w.H * world, w.Dh, dtype=w.dtype).pin_memory()
+    t_of = lambda s: w.prompt + ((s // nrep) % w.steps)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def resident_step(s):
+        engines[s % nrep].attention(qkv_d[s, 0], qkv_d[s, 1], qkv_d[s, 2], w.scale, t_of(s), 0.0, out=out_d)
+
+    def e2e_step(s):
+        stage.copy_(qkv_h[s], non_blocking=True)
+        if world > 1:
+            o = sharded[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0, gather=True)
+        else:
+            o = engines[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0)
+        out_h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller consumes the result every step
+
+    clocks = ClockSampler(gpu_id(dev)).start()
+
     # ---- leg 1: inputs resident in HBM; per-launch events give the kernel's own duration ----
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     for s in range(args.warmup):
-        ffa.attention(qkv_d[s, 0], qkv_d[s, 1], qkv_d[s, 2], w.scale, t_of(s), 0.0, out=out_d)
+        resident_step(s)
     barrier()
     launches0 = launch_count()
-    with ClockSampler(gpu_id(dev)) as clocks:
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(args.steps):
-            s = args.warmup + i
-            if flush is not None:
-                flush.zero_()
-            ev[i][0].record()
-            ffa.attention(qkv_d[s, 0], qkv_d[s, 1], qkv_d[s, 2], w.scale, t_of(s), 0.0, out=out_d)
-            ev[i][1].record()
-        stop.record()
-        barrier()
+    wall0 = time.time()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        ev[i][0].record()
+        resident_step(args.warmup + i)
+        ev[i][1].record()
+    stop.record()
+    barrier()
     launches = launch_count() - launches0
+    loop_ms = start.elapsed_time(stop)
     kernel_ms = [a.elapsed_time(b) for a, b in ev]
-    loop_ms = sum(kernel_ms) if flush is not None else start.elapsed_time(stop)
     alg = [algorithmic_bytes(es, w.B, w.H, w.Dh, t_of(args.warmup + i)) for i in range(args.steps)]
+    # keep the same load running (untimed) until the clock sampler has seen it for half a second
+    while time.time() - wall0 < 0.5:
+        for i in range(args.steps):
+            resident_step(args.warmup + i)
+        torch.cuda.synchronize()
+    wall1 = time.time()
+    clocks.stop()
 
     # ---- leg 2: end to end through the Python class with host buffers ----
     for s in range(min(3, args.warmup)):
-        stage.copy_(qkv_h[s], non_blocking=True)
-        o = (eng.attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0, gather=True) if eng is not None
-             else ffa.attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0))
-        out_h_full = torch.empty(o.shape, dtype=o.dtype).pin_memory()
-        out_h_full.copy_(o, non_blocking=True)
+        e2e_step(s)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        s = args.warmup + i
-        stage.copy_(qkv_h[s], non_blocking=True)
-        o = (eng.attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0, gather=True) if eng is not None
-             else ffa.attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0))
-        out_h_full.copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the caller consumes the result every step
+        e2e_step(args.warmup + i)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
-    status = ffa.device_status()
+    status = max(e.device_status() for e in engines)
 
     # ---- max over ranks ----
     times = torch.tensor([loop_ms, e2e_ms, sum(kernel_ms)], dtype=torch.float64, device=dev)
@@ -289,10 +323,10 @@ def main():
                              "avg_launch_ms": ksum_ms / args.steps,
                              "traffic": TRAFFIC_RATIO * per_launch_alg if TRAFFIC_RATIO else None},
                 "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "steps/s",
-                        "h2d_bytes_per_step": 3 * w.B * w.H * w.Dh * es, "d2h_bytes_per_step": out_h_full.numel() * es,
+                        "h2d_bytes_per_step": 3 * w.B * w.H * w.Dh * es, "d2h_bytes_per_step": out_h.numel() * es,
                         "includes": "pinned-host q/k/v upload, attention, output all-gather (N>1), output download, sync"},
                 "gpu_launches": int(launches), "launch_shape": dict(shape), "device_status": status,
-                "clocks": clocks.summary()}
+                "clocks": clocks.summary(wall0, wall1), "replicas": nrep}
         if world == 1 and not args.no_cpu_baseline:
             smp = CpuReferenceSample(full)
             probe = smp.step()

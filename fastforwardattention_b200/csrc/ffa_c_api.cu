@@ -372,6 +372,17 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     return FFA_OK;
 }
 
+int ffa_selftest_wait_timeout(ffa_plan_t* plan, unsigned int limit_ms, void* stream)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound");
+    if (limit_ms == 0 || limit_ms > 2000) return fail(FFA_ERR_RANGE, "limit_ms must be in [1, 2000]");
+    const int r = ffa_k_wait_selftest(plan->status, (unsigned long long)limit_ms * 1000000ull, nullptr, static_cast<cudaStream_t>(stream));
+    if (r != 0) return cuda_fail(r, "self-test launch");
+    g_launches.fetch_add(1);
+    return FFA_OK;
+}
+
 int ffa_device_status(ffa_plan_t* plan, void* stream, int* status)
 {
     if (plan == nullptr || status == nullptr) return fail(FFA_ERR_ARG, "null pointer");

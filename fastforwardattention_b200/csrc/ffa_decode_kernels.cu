@@ -90,14 +90,15 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
 // time (or as soon as another thread of the CTA gave up) it raises the CTA's `dead` flag and
 // returns false; callers then skip the data but keep walking the same control flow so every
 // CTA-level barrier is still reached by everyone.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* dead)
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* dead,
+                                                  unsigned long long limit_ns = kWaitLimitNs)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     for (;;) {
         if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
         if (*dead) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        if (global_timer_ns() - t0 > limit_ns) break;
     }
     *dead = 1;
     return false;
@@ -798,6 +799,31 @@ __global__ void __launch_bounds__(256) ffa_cache_init_kernel(const uint4* __rest
 }
 
 // ------------------------------------------------------------------------------------------
+// Diagnostic: the bounded wait on a barrier that nothing ever completes
+// ------------------------------------------------------------------------------------------
+// One warp waits, with the given limit, for a copy barrier no copy was issued against.  The
+// wait must run out, raise the flag and let the kernel return normally with the time-out bit
+// in the status word -- the behaviour the streaming kernels rely on if a copy never lands.
+__global__ void __launch_bounds__(32) ffa_wait_selftest_kernel(int* status, unsigned long long limit_ns, unsigned long long* waited_ns)
+{
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int dead;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        dead = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const unsigned long long t0 = global_timer_ns();
+    const bool ok = mbar_wait_bounded(smem_u32(&bar), 0, &dead, limit_ns);
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        if (!ok || dead) atomicOr(status, kStatusWaitTimeout);
+        if (waited_ns != nullptr) *waited_ns = global_timer_ns() - t0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Host-side dispatch
 // ------------------------------------------------------------------------------------------
 template <typename F>
@@ -874,6 +900,12 @@ int ffa_k_cache_init(int dtype, int BH, int prompt_len, int max_len, int head_di
     ffa_cache_init_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(k_src), static_cast<const uint4*>(v_src),
                                                                 static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
                                                                 src_per, dst_per, total);
+    return (int)cudaGetLastError();
+}
+
+int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, cudaStream_t stream)
+{
+    ffa_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_ns, waited_ns);
     return (int)cudaGetLastError();
 }
 

@@ -43,3 +43,5 @@ int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const
 // shared-memory bytes a launch shape needs
 int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage);
 int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows);
+// diagnostic: a bounded wait that must time out (see ffa_selftest_wait_timeout)
+int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, cudaStream_t stream);

@@ -145,6 +145,12 @@ int ffa_attention_static_scratch(int dtype, int batch, int heads, int head_dim, 
  * clears it.  The reference only printf()s cudaGetLastError (attention.cu:1444-1451). */
 int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
 
+/* Diagnostic, no counterpart in the reference: launches one warp that waits, for at most
+ * limit_ms (1..2000), on a copy barrier nothing completes.  The wait must give up, the kernel
+ * must return normally, and the next ffa_device_status() must report FFA_STATUS_WAIT_TIMEOUT
+ * -- the path the streaming kernels take if a bulk copy never lands.  Nothing faults or hangs. */
+int ffa_selftest_wait_timeout(ffa_plan_t* plan, unsigned int limit_ms, void* stream);
+
 /* Kernels launched by this library since it was loaded (for launch accounting in benchmarks). */
 unsigned long long ffa_launch_count(void);
 

@@ -380,3 +380,26 @@ def test_pruning_straddling_scores(dt):
         assert max_err(got.view(B * H, Dh), want) <= tol + 0.05 * diff
     print(f"\n[prune straddle] {dt}: differing={total_diff} borderline={total_border}")
     assert eng.status() == 0
+
+
+def test_bounded_wait_times_out_and_reports():
+    """Failure detection on the device: a wait on a barrier that nothing completes runs out
+    after its limit, the kernel returns, the status word carries the time-out bit, and the
+    context stays usable (the next decode step is correct)."""
+    import ctypes as C
+    import time
+
+    dt, B, H, Dh, Lp = torch.float16, 1, 2, 64, 20
+    g, K, V = small_case(dt, B, H, Dh, Lp, Lp + 1, 5)
+    eng = CAbiEngine(K, V, Lp + 1)
+    t0 = time.time()
+    capi.check(eng.L.ffa_selftest_wait_timeout(eng.plan, 50, None))
+    torch.cuda.synchronize()
+    assert 0.04 < time.time() - t0 < 1.5
+    assert eng.status() == 1          # FFA_STATUS_WAIT_TIMEOUT, and reading clears it
+    assert eng.status() == 0
+    q, k, v = qkv(g, B, H, Dh, dt)
+    got = eng.attention(q, k, v, 0.125, Lp)
+    ref = O.DecodeOracle(K, V, Lp + 1, compute_dtype=torch.float64).step(q, k, v, 0.125, Lp)
+    assert_close_ulp(got, ref, dt, "step after the timed-out wait")
+    assert eng.status() == 0

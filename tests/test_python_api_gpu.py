@@ -117,3 +117,43 @@ def test_pruning_through_python_class():
         assert torch.equal(bits, kept)
         assert (out.view(N, w.Dh).cpu().float() - want.float()).abs().max() <= 2e-3
     assert ffa.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.float32])
+def test_cuda_graph_replay_with_device_side_step(dt):
+    """A decode step captured ONCE in a CUDA graph and replayed for every token: the row index
+    lives in device memory (per-sample lengths, the c_ffa_api.h:17-20 mode), so the captured
+    launch parameters never change.  Removes the per-step host work that dominates the small
+    configurations."""
+    from fastforwardattention_b200 import FastForwardAttn
+
+    g = torch.Generator().manual_seed(11)
+    B, H, Dh, Lp, n = 2, 8, 64, 150, 6
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    ffa = FastForwardAttn(K.cuda(), V.cuda(), Lp + n, False)
+    orc = O.DecodeOracle(K, V, Lp + n, compute_dtype=torch.float64)
+    q_s, k_s, v_s = (torch.zeros(B, H, 1, Dh, dtype=dt, device="cuda") for _ in range(3))
+    out_s = torch.zeros(B, H, Dh, dtype=dt, device="cuda")
+    rows = torch.full((B,), Lp, dtype=torch.int32, device="cuda")
+    # warm-up outside capture (first call binds nothing new, but keeps capture free of lazy init)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ffa.attention_per_sample(q_s, k_s, v_s, 0.125, rows, 0.0, out=out_s)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ffa.attention_per_sample(q_s, k_s, v_s, 0.125, rows, 0.0, out=out_s)
+        rows.add_(1)
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3}[dt]
+    for i in range(n):
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        q_s.copy_(q), k_s.copy_(k), v_s.copy_(v)
+        graph.replay()
+        ref = orc.step(q, k, v, 0.125, Lp + i)
+        assert (out_s.cpu().double() - ref).abs().max().item() <= tol, i
+    assert int(rows[0]) == Lp + n and ffa.device_status() == 0
+    kc, _ = ffa.get_cache()
+    assert torch.equal(kc[:, :, Lp + n - 1].cpu(), k[:, :, 0])
