@@ -15,7 +15,7 @@ MODE_EXACT, MODE_ROUND_LIKE_TORCH = 0, 1
 
 SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_destroy", "ffa_plan_get_launch",
            "ffa_plan_set_launch", "ffa_plan_set_mode", "ffa_workspace_bytes", "ffa_workspace_bind", "ffa_attention",
-           "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout"]
+           "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path"]
 
 
 class Launch(C.Structure):
@@ -46,6 +46,7 @@ def lib() -> C.CDLL:
         L.ffa_plan_get_launch.argtypes = [vp, i, C.POINTER(Launch)]
         L.ffa_plan_set_launch.argtypes = [vp, C.POINTER(Launch)]
         L.ffa_plan_set_mode.argtypes = [vp, i]
+        L.ffa_plan_set_prune_path.argtypes = [vp, i]
         L.ffa_workspace_bytes.argtypes = [vp, i]
         L.ffa_workspace_bytes.restype = sz
         L.ffa_workspace_bind.argtypes = [vp, vp, sz, vp]

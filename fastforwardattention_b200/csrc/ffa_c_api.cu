@@ -47,6 +47,7 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 
 struct ffa_plan {
     int dtype, B, H, Dh, Lmax, use_default, device, mode;
+    int prune_path;  // 0 = choose, 1 = fused cluster kernel only, 2 = two kernels only
     int sms, smem_per_cta, smem_per_sm;
     bool forced;
     ffa_launch_t force;
@@ -180,6 +181,43 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
     return FFA_OK;
 }
 
+// Fused pruning kernel: a cluster of C CTAs per (batch, head), C in {1, 2, 4, 8}; each CTA keeps
+// the scores of its slice (chunk rows, a multiple of 32 so mask words never straddle slices) in
+// shared memory.  The kernel has a score phase and a value phase separated by a cluster
+// barrier, so a second wave of CTAs costs a whole extra latency chain: take the largest C whose
+// B*H*C CTAs are all resident at once (slices of at least 128 rows); when even C = 1 needs
+// several waves, the smallest C that fits in shared memory.  False when 8 slices do not fit
+// (then the two-kernel path runs).
+bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out)
+{
+    const int rowb = p->Dh * elem_size(p->dtype);
+    const long long BH = (long long)p->B * p->H;
+    int best_c = 0, best_chunk = 0, best_r = 0, best_smem = 0, best_resident = 0;
+    bool have_single_wave = false;
+    for (int c = 1; c <= 8; c *= 2) {
+        const int chunk = (int)(((long long)cap_rows + 1 + c - 1) / c + 31) / 32 * 32;
+        if (c > 1 && chunk < 128) break;
+        int r = 8192 / rowb;
+        if (r > chunk) r = (chunk + 7) / 8 * 8;
+        const int smem = ffa_k_fused_smem_bytes(p->dtype, p->Dh, r, 3, chunk);
+        if (smem > p->smem_per_cta) continue;
+        int resident = p->smem_per_sm / (smem + kSmemReservePerCta);
+        if (resident > 7) resident = 7;  // 160 threads x 56 registers
+        const bool single_wave = BH * c <= (long long)p->sms * resident;
+        // single wave: the more slices the better; several waves: stop slicing once three CTAs
+        // per SM can overlap one another's phases
+        const bool take = single_wave || (!have_single_wave && (best_c == 0 || best_resident < 3));
+        if (take) best_c = c, best_chunk = chunk, best_r = r, best_smem = smem, best_resident = resident;
+        have_single_wave = have_single_wave || single_wave;
+        if (have_single_wave && !single_wave) break;
+    }
+    if (best_c == 0) return false;
+    P->cluster = best_c, P->chunk_rows = best_chunk, P->tile_rows = best_r, P->stages = 3;
+    P->grid = (int)(BH * best_c);
+    *smem_out = best_smem;
+    return true;
+}
+
 // rows the unit list must cover for this call: t when every sample is at row t, max_len - 1
 // when rows come from per-sample lengths the host cannot see
 int cap_rows_for(const ffa_plan* p, int t, const int* seq_lengths, int right_or_no_padding)
@@ -277,6 +315,14 @@ int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch)
     return FFA_OK;
 }
 
+int ffa_plan_set_prune_path(ffa_plan_t* plan, int path)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (path < 0 || path > 2) return fail(FFA_ERR_ARG, "prune path must be 0 (choose), 1 (fused) or 2 (two kernels)");
+    plan->prune_path = path;
+    return FFA_OK;
+}
+
 int ffa_plan_set_mode(ffa_plan_t* plan, int mode)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
@@ -324,9 +370,6 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
         return fail(FFA_ERR_ARG, "left padding (right_or_no_padding = 0) needs seq_lengths");
     if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
     const bool twopass = p > 0.f || plan->mode == FFA_MODE_ROUND_LIKE_TORCH;
-    if (twopass && plan->scores == nullptr)
-        return fail(FFA_ERR_WORKSPACE, "p > 0 and the torch-rounding mode need a workspace sized with with_scores = 1");
-
     const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
     const long long BH = (long long)plan->B * plan->H;
     FfaStepParams P;
@@ -340,6 +383,20 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     P.stats = plan->stats, P.scores = plan->scores;
     P.kept_mask = kept_mask, P.mask_words = (plan->Lmax + 31) / 32;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    if (twopass && plan->prune_path != 2) {
+        FfaStepParams F = P;
+        int smem_f = 0;
+        if (plan_fused(plan, cap, &F, &smem_f)) {
+            const int rf = ffa_k_decode_fused_prune(plan->dtype, plan->Dh, F, smem_f, st);
+            if (rf != 0) return cuda_fail(rf, "fused pruning launch");
+            g_launches.fetch_add(1);
+            return FFA_OK;
+        }
+        if (plan->prune_path == 1) return fail(FFA_ERR_ARG, "the fused pruning kernel does not fit this shape in shared memory");
+    }
+    if (twopass && plan->scores == nullptr)
+        return fail(FFA_ERR_WORKSPACE, "this shape needs the two-kernel pruning path: bind a workspace sized with with_scores = 1");
 
     ffa_launch_t L;
     int r = fit_launch(plan, cap, twopass ? 1 : 2, &L);

@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <cstring>
 #include <type_traits>
 
 #include "ffa_internal.h"
@@ -781,6 +782,339 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
 }
 
 // ------------------------------------------------------------------------------------------
+// Fused pruning step: one thread-block cluster per (batch, head), scores never leave the SMs
+// ------------------------------------------------------------------------------------------
+// The pruning rule needs the global max and sum of a (batch, head) before any V row may be
+// touched (attention.cu:1184-1191), so the score pass and the value pass cannot be one
+// streaming sweep.  Here both live in one kernel: a cluster of C CTAs owns a (batch, head);
+// CTA r scores its slice of rows from a K-only bulk-copy ring into its OWN shared memory,
+// the C pairs (max, sum) are exchanged through distributed shared memory behind a cluster
+// barrier, every CTA prunes and gathers the V rows of its slice, and CTA 0 adds the C partial
+// outputs (again through distributed shared memory).  No score scratch in HBM, no second
+// launch, no arrival counters.  Used when a slice's scores fit in shared memory; the two
+// kernels above remain for everything else.
+//
+// Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (index, probability)
+// | group reduction area [NG][DH + 4] | partial output [DH] | (max, sum) | barriers | flags.
+constexpr int kFusedThreads = 160;   // 1 copy warp + 4 compute warps
+constexpr int kFusedListCap = 512;   // rows pruned and gathered per round (multiple of 32)
+
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_smem_f32(const void* own_smem_ptr, uint32_t peer_rank)
+{
+    uint32_t peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_smem_ptr)), "r"(peer_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const FfaStepParams P)
+{
+    using G = RowGeom<T, DH>;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL;
+    constexpr int NCW = 4, NCT = NCW * 32, NG = NCT / LPR, RS = DH + 4, E2 = EPV / 2;
+    constexpr bool kAllLanes = (VPR == LPR * VPL);
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int R = P.tile_rows, S = P.stages, C = P.cluster, chunk = P.chunk_rows;
+    const uint32_t tile_bytes = (uint32_t)R * ROWB;
+    float* sc = reinterpret_cast<float*>(smem + (size_t)S * tile_bytes);
+    int* list_idx = reinterpret_cast<int*>(sc + chunk);
+    float* list_p = reinterpret_cast<float*>(list_idx + kFusedListCap);
+    float* red = list_p + kFusedListCap;
+    float* accs = red + NG * RS;
+    float* stat = accs + DH;                       // [0] max, [1] sum of this CTA's slice
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4);
+    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead, [1] list length
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S), ring = smem_u32(smem);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t rank = cluster_rank();
+    const int bh = blockIdx.x / C;
+    const SampleRange sr = sample_range(P, bh / P.H);
+    const int c0 = (int)rank * chunk;                                   // first absolute row of this slice
+    const int lo = sr.ok ? max(c0, sr.first) : 0;
+    const int hi = sr.ok ? min(c0 + chunk, sr.row) : 0;                 // cached rows [lo, hi)
+    const bool owns_new = sr.ok && sr.row >= c0 && sr.row < c0 + chunk; // the new token's row is in this slice
+    const int nrows = max(hi - lo, 0), ntiles = (nrows + R - 1) / R;
+    const bool prune = P.p > 0.f;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, NCW);
+        }
+        flags[0] = 0, flags[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int ctid = tid - 32, g = ctid / LPR, li = ctid % LPR;   // meaningful for compute warps only
+    float2 q2[VPL][E2];
+    float qf[VPL][EPV];
+    float m = -CUDART_INF_F, l = 0.f;
+
+    auto score_of = [&](float dot) -> float {
+        if (P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
+        return dot * P.scale;
+    };
+
+    // ---------------- phase 1: scores of this slice into shared memory ----------------
+    if (warp == 0) {
+        if (tid == 0) {
+            const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache) + ((size_t)bh * P.Lmax + lo) * ROWB;
+            uint32_t stage = 0, use = 0;
+            for (int j = 0; j < ntiles; ++j) {
+                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
+                const uint32_t bytes = (uint32_t)min(R, nrows - j * R) * ROWB;
+                mbar_expect_tx(bar_full + 8 * stage, bytes);
+                bulk_copy_g2s(ring + stage * tile_bytes, kc + (size_t)j * tile_bytes, bytes, bar_full + 8 * stage);
+                if (++stage == (uint32_t)S) stage = 0, ++use;
+            }
+        }
+    } else {
+        load_row_f32<T, DH>(static_cast<const unsigned char*>(P.q) + (size_t)bh * ROWB, li, qf);
+#pragma unroll
+        for (int x = 0; x < VPL; ++x)
+#pragma unroll
+            for (int e = 1; e < EPV; e += 2) q2[x][e >> 1] = make_float2(qf[x][e - 1], qf[x][e]);
+
+        uint32_t stage = 0, phase = 0;
+        for (int j = 0; j < ntiles; ++j) {
+            const int n = min(R, nrows - j * R);
+            const bool ready = mbar_wait_bounded(bar_full + 8 * stage, phase, flags);
+            const unsigned char* ks = smem + (size_t)stage * tile_bytes;
+            float* sc_tile = sc + (lo - c0) + j * R;
+            if (ready) {
+                for (int base = 0; base < n; base += 4 * NG) {
+                    uint4 kraw[4][VPL];
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu) {
+                        const int rc = min(base + uu * NG + g, n - 1);
+#pragma unroll
+                        for (int x = 0; x < VPL; ++x)
+                            if (kAllLanes || li + x * LPR < VPR)
+                                kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc * ROWB + (li + x * LPR) * 16);
+                    }
+                    float s4[4];
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu) {
+                        float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int x = 0; x < VPL; ++x)
+                            if (kAllLanes || li + x * LPR < VPR) {
+                                float2 k2[E2];
+                                Elem<T>::unpack2(kraw[uu][x], k2);
+#pragma unroll
+                                for (int e = 0; e < E2; ++e) a = __ffma2_rn(q2[x][e], k2[e], a);
+                            }
+                        s4[uu] = a.x + a.y;
+                    }
+#pragma unroll
+                    for (int off = LPR / 2; off >= 1; off >>= 1)
+#pragma unroll
+                        for (int uu = 0; uu < 4; ++uu) s4[uu] += __shfl_xor_sync(0xffffffffu, s4[uu], off);
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu) {
+                        const int r = base + uu * NG + g;
+                        s4[uu] = r < n ? score_of(s4[uu]) : -CUDART_INF_F;
+                        if (r < n && li == 0) sc_tile[r] = s4[uu];
+                    }
+                    const float m_new = fmaxf(fmaxf(fmaxf(m, s4[0]), fmaxf(s4[1], s4[2])), s4[3]);
+                    if (m_new != -CUDART_INF_F) {
+                        l = l * expf(m - m_new) + ((expf(s4[0] - m_new) + expf(s4[1] - m_new)) + (expf(s4[2] - m_new) + expf(s4[3] - m_new)));
+                        m = m_new;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+            if (++stage == (uint32_t)S) stage = 0, phase ^= 1;
+        }
+        // the new token: score against k, append k at row sr.row (attention.cu:900-958)
+        if (owns_new) {
+            float kf[VPL][EPV];
+            load_row_f32<T, DH>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB, li, kf);
+            float dot = 0.f;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[x][e], dot);
+            dot = group_sum<LPR>(dot);
+            if (g == 0) {
+                const float st = score_of(dot);
+                const float m_new = fmaxf(m, st);
+                l = l * expf(m - m_new) + expf(st - m_new);
+                m = m_new;
+                if (li == 0) sc[sr.row - c0] = st;
+                const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+                for (int x = 0; x < VPL; ++x) {
+                    const int vec = li + x * LPR;
+                    if (vec < VPR)
+                        *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + vec * 16) =
+                            *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB + vec * 16);
+                }
+            }
+        }
+        if (li == 0) red[g * RS] = m, red[g * RS + 1] = l;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float Mc = -CUDART_INF_F, Lc = 0.f;
+        for (int gg = 0; gg < NG; ++gg) Mc = fmaxf(Mc, red[gg * RS]);
+        for (int gg = 0; gg < NG; ++gg)
+            if (red[gg * RS] != -CUDART_INF_F) Lc += red[gg * RS + 1] * expf(red[gg * RS] - Mc);
+        stat[0] = Mc, stat[1] = Lc;
+    }
+    cluster_sync_all();   // every slice's (max, sum) is visible cluster-wide; also a CTA barrier
+
+    // ---------------- global statistics of the (batch, head) ----------------
+    float M = -CUDART_INF_F, Lsum = 0.f;
+    for (int c = 0; c < C; ++c) M = fmaxf(M, ld_peer_smem_f32(stat, c));
+    for (int c = 0; c < C; ++c) {
+        const float mc = ld_peer_smem_f32(stat, c);
+        if (mc != -CUDART_INF_F) Lsum += ld_peer_smem_f32(stat + 1, c) * expf(mc - M);
+    }
+    // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
+    // the torch-rounding mode divides exactly like torch's softmax does
+    const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
+    const float theta = Elem<T>::round(P.p * inv);
+    auto prob_of = [&](float s) -> float {
+        if (prune) return Elem<T>::round(__expf(s - M) * inv);
+        return Elem<T>::round(expf(s - M) / Lsum);
+    };
+
+    // ---------------- phase 2: prune, gather the surviving V rows ----------------
+    float2 acc2[VPL][E2];
+#pragma unroll
+    for (int x = 0; x < VPL; ++x)
+#pragma unroll
+        for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
+    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache) + (size_t)bh * P.Lmax * ROWB;
+    const int hi_mask = sr.ok ? min(c0 + chunk, sr.row + 1) : c0;   // rows whose mask bit this slice writes
+    for (int sub = c0; sub < hi_mask; sub += kFusedListCap) {
+        __syncthreads();
+        if (tid == 0) flags[1] = 0;
+        __syncthreads();
+        const int sub_hi = min(sub + kFusedListCap, hi_mask);
+        for (int base = sub + warp * 32; base < sub_hi; base += kFusedThreads) {
+            const int i = base + lane;
+            const bool cached = i >= lo && i < hi;
+            float pr = 0.f;
+            bool keep = false;
+            if (cached) {
+                pr = prob_of(sc[i - c0]);
+                keep = prune ? !Elem<T>::leq(pr, theta) : true;
+            }
+            const unsigned bal = __ballot_sync(0xffffffffu, keep);
+            if (P.kept_mask != nullptr && lane == 0)
+                P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
+                    bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+            int pos = 0;
+            if (lane == 0 && bal) pos = atomicAdd(const_cast<int*>(&flags[1]), __popc(bal));
+            pos = __shfl_sync(0xffffffffu, pos, 0) + __popc(bal & ((1u << lane) - 1u));
+            if (keep) list_idx[pos] = i, list_p[pos] = pr;
+        }
+        __syncthreads();
+        const int n = flags[1];
+        if (warp > 0) {
+            for (int base = 0; base < n; base += 4 * NG) {
+                uint4 raw[4][VPL];
+                float pr[4];
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) {
+                    const int idx = base + uu * NG + g;
+                    const bool okr = idx < n;
+                    pr[uu] = okr ? list_p[idx] : 0.f;
+                    const int row = okr ? list_idx[idx] : lo;
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        raw[uu][x] = make_uint4(0, 0, 0, 0);
+                        if (okr && (kAllLanes || li + x * LPR < VPR))
+                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + (size_t)row * ROWB + (li + x * LPR) * 16));
+                    }
+                }
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) {
+                    const float2 p2 = make_float2(pr[uu], pr[uu]);
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        float2 v2[E2];
+                        Elem<T>::unpack2(raw[uu][x], v2);
+#pragma unroll
+                        for (int e = 0; e < E2; ++e) acc2[x][e] = __ffma2_rn(p2, v2[e], acc2[x][e]);
+                    }
+                }
+            }
+        }
+    }
+    // the new token is never pruned (attention.cu:1227-1256): append v, add P_t * v
+    if (warp > 0) {
+        if (owns_new && g == 0) {
+            const float pt = prob_of(sc[sr.row - c0]);
+            const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                const int vec = li + x * LPR;
+                if (vec < VPR) {
+                    const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + (size_t)bh * ROWB + vec * 16);
+                    *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
+                    float2 v2[E2];
+                    Elem<T>::unpack2(vraw, v2);
+#pragma unroll
+                    for (int e = 0; e < E2; ++e) {
+                        acc2[x][e].x = fmaf(pt, v2[e].x, acc2[x][e].x);
+                        acc2[x][e].y = fmaf(pt, v2[e].y, acc2[x][e].y);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) {
+            const int vec = li + x * LPR;
+            if (vec < VPR) {
+#pragma unroll
+                for (int e = 0; e < E2; e += 2)
+                    *reinterpret_cast<float4*>(red + g * RS + vec * EPV + 2 * e) =
+                        make_float4(acc2[x][e].x, acc2[x][e].y, acc2[x][e + 1].x, acc2[x][e + 1].y);
+            }
+        }
+    }
+    __syncthreads();
+    for (int d = tid; d < DH; d += kFusedThreads) {
+        float A = 0.f;
+        for (int gg = 0; gg < NG; ++gg) A += red[gg * RS + d];
+        accs[d] = A;
+    }
+    cluster_sync_all();   // every slice's partial output is visible cluster-wide
+    if (rank == 0) {
+        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+        for (int d = tid; d < DH; d += kFusedThreads) {
+            float A = 0.f;
+            for (int c = 0; c < C; ++c) A += ld_peer_smem_f32(accs + d, c);   // slice order: deterministic
+            Elem<T>::store(outp + d, sr.ok ? A : 0.f);
+        }
+    }
+    cluster_sync_all();   // peers keep their shared memory alive until CTA 0 has read it
+    if (tid == 0) {
+        if (flags[0]) atomicOr(P.status, kStatusWaitTimeout);
+        if (!sr.ok && rank == 0) atomicOr(P.status, kStatusBadLength);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Cache build: prompt [BH, Lp, Dh] -> rows [0, Lp) of [BH, Lmax, Dh], K and V in one launch
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) ffa_cache_init_kernel(const uint4* __restrict__ k_src, const uint4* __restrict__ v_src,
@@ -867,6 +1201,16 @@ int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows)
     return tile_rows * 8 + (kGatherThreads / lpr) * head_dim * 4;
 }
 
+int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows)
+{
+    const int rowb = head_dim * elem_size(dtype);
+    const int vpr = rowb / 16;
+    const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
+    const int ng = 128 / lpr;
+    return stages * tile_rows * rowb + chunk_rows * 4 + kFusedListCap * 8 + ng * (head_dim + 4) * 4 + head_dim * 4 + 16 +
+           2 * stages * 8 + 16;
+}
+
 int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes)
 {
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
@@ -884,6 +1228,8 @@ int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes)
         e = raise_limit(reinterpret_cast<const void*>(ffa_stream_kernel<T, DH, kPassScore>));
         if (e != cudaSuccess) return (int)e;
         e = raise_limit(reinterpret_cast<const void*>(ffa_value_gather_kernel<T, DH>));
+        if (e != cudaSuccess) return (int)e;
+        e = raise_limit(reinterpret_cast<const void*>(ffa_prune_cluster_kernel<T, DH>));
         return (int)e;
     });
 }
@@ -916,6 +1262,28 @@ int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int th
         constexpr int DH = decltype(dh)::value;
         ffa_stream_kernel<T, DH, kPassOne><<<P.grid, threads, smem, stream>>>(P);
         return (int)cudaGetLastError();
+    });
+}
+
+int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, int smem, cudaStream_t stream)
+{
+    return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
+        using T = decltype(t);
+        constexpr int DH = decltype(dh)::value;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)P.grid, 1, 1);
+        cfg.blockDim = dim3(kFusedThreads, 1, 1);
+        cfg.dynamicSmemBytes = (size_t)smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)P.cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return (int)cudaLaunchKernelEx(&cfg, ffa_prune_cluster_kernel<T, DH>, P);
     });
 }
 

@@ -29,6 +29,8 @@ struct FfaStepParams {
     float* scores;     // [B*H, Lmax] fp32 scores (two-pass modes)
     uint32_t* kept_mask;  // [B*H, mask_words] or null
     int mask_words;
+    // fused pruning kernel: CTAs per (batch, head) cluster, cache rows per CTA (multiple of 32)
+    int cluster, chunk_rows;
 };
 
 // dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.
@@ -43,5 +45,8 @@ int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const
 // shared-memory bytes a launch shape needs
 int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage);
 int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows);
+// p > 0 or round-like-torch when a slice's scores fit in shared memory: one cluster launch.
+int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, int smem, cudaStream_t stream);
+int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows);
 // diagnostic: a bounded wait that must time out (see ffa_selftest_wait_timeout)
 int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, cudaStream_t stream);

@@ -97,8 +97,6 @@ struct FastForwardAttn {
             sl = seq_lengths->contiguous();
         }
         c10::cuda::CUDAGuard guard(device);
-        const bool twopass = p > 0.0 || mode == FFA_MODE_ROUND_LIKE_TORCH;
-        if (twopass && !has_scores) bind_workspace(true);
         torch::Tensor out;
         if (out_opt.has_value()) {
             out = *out_opt;
@@ -112,10 +110,18 @@ struct FastForwardAttn {
             if (!kept_mask.defined()) kept_mask = torch::zeros({B, H, (Lmax + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
             mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
         }
-        check(ffa_attention(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
-                            (float)softmax_scale, (int)t, seq_lengths ? sl.data_ptr<int>() : nullptr, right_or_no_padding,
-                            (float)p, mask_ptr, at::cuda::getCurrentCUDAStream().stream()),
-              "attention");
+        auto call = [&]() {
+            return ffa_attention(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                                 (float)softmax_scale, (int)t, seq_lengths ? sl.data_ptr<int>() : nullptr, right_or_no_padding,
+                                 (float)p, mask_ptr, at::cuda::getCurrentCUDAStream().stream());
+        };
+        int rc = call();
+        if (rc == FFA_ERR_WORKSPACE && !has_scores) {
+            // a shape the fused pruning kernel cannot hold: grow the workspace by the score scratch, once
+            bind_workspace(true);
+            rc = call();
+        }
+        check(rc, "attention");
         return out;
     }
 
@@ -154,6 +160,7 @@ struct FastForwardAttn {
         mode = m == "exact" ? FFA_MODE_EXACT : FFA_MODE_ROUND_LIKE_TORCH;
         check(ffa_plan_set_mode(plan, mode), "mode");
     }
+    void set_prune_path(int path) { check(ffa_plan_set_prune_path(plan, path), "prune path"); }
     void set_launch(int tile_rows, int stages, int consumer_warps, int ctas_per_sm, int grid)
     {
         ffa_launch_t l{tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0};
@@ -216,6 +223,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
              py::arg("k"), py::arg("v"), py::arg("softmax_scale"), py::arg("seq_lengths"), py::arg("prob_thresh") = 0.0,
              py::arg("out") = py::none())
         .def("set_mode", &FastForwardAttn::set_mode, "'exact' (default) or 'round_like_torch'")
+        .def("set_prune_path", &FastForwardAttn::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
         .def("set_launch", &FastForwardAttn::set_launch, py::arg("tile_rows") = 0, py::arg("stages") = 0,
              py::arg("consumer_warps") = 0, py::arg("ctas_per_sm") = 0, py::arg("grid") = 0)
         .def("launch_shape", &FastForwardAttn::launch_shape, py::arg("t"))

@@ -92,10 +92,18 @@ int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch);
  * (c_ffa_api.h:17-20). */
 int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch);
 int ffa_plan_set_mode(ffa_plan_t* plan, int mode);
+/* p > 0 and the torch-rounding mode need the global softmax statistics before any V row is
+ * read.  Two implementations: 1 = one launch, a thread-block cluster per (batch, head) with the
+ * scores in shared memory (needs no score scratch); 2 = two launches through an fp32 score
+ * scratch in the workspace (any size).  0 (default) picks 1 whenever a slice fits in shared
+ * memory.  The reference does both phases in one CTA per (batch, head) (attention.cu:1077-1257),
+ * which is what caps its sequence length. */
+int ffa_plan_set_prune_path(ffa_plan_t* plan, int path);
 
 /* Scratch the engine needs in device memory: split partials, arrival counters, the status
  * word and, when with_scores != 0 (needed for p > 0 and FFA_MODE_ROUND_LIKE_TORCH), one fp32
- * score per cache row.  The caller allocates it (256-byte aligned) and binds it once;
+ * score per cache row (only the two-launch pruning path reads it; ffa_attention returns
+ * FFA_ERR_WORKSPACE if a call needs it and it is missing).  The caller allocates it (256-byte aligned) and binds it once;
  * binding clears the counters on the stream.  One workspace serves one stream at a time. */
 size_t ffa_workspace_bytes(const ffa_plan_t* plan, int with_scores);
 int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* stream);

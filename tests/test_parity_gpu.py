@@ -94,10 +94,11 @@ def test_golden_vectors_torch_rounding_mode(name):
 # ------------------------------------------------------------------------------------------
 # the benchmark configurations, driven step by step like example.py:30-46
 # ------------------------------------------------------------------------------------------
-def run_config(w: Workload, step_filter, mode=capi.MODE_EXACT, use_default=False):
+def run_config(w: Workload, step_filter, mode=capi.MODE_EXACT, use_default=False, prune_path=0):
     K, V = prompt_kv(w)
     eng = CAbiEngine(K, V, w.max_len, use_default=use_default)
     eng.set_mode(mode)
+    eng.set_prune_path(prune_path)
     orc = O.DecodeOracle(K, V, w.max_len)
     N = w.B * w.H
     worst = {"same": 0.0, "noise": 0.0, "f64": 0.0}
@@ -149,10 +150,11 @@ def test_config_long_bf16(x):
     run_config(w, lambda i: i in (0, 1, 64, 127))
 
 
+@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
 @pytest.mark.parametrize("x", [512, 2048])
-def test_config_long_bf16_torch_rounding_mode(x):
+def test_config_long_bf16_torch_rounding_mode(x, path):
     w = CONFIGS[f"long-{x}"]
-    run_config(w, lambda i: i in (0, 127), mode=capi.MODE_ROUND_LIKE_TORCH)
+    run_config(w, lambda i: i in (0, 127), mode=capi.MODE_ROUND_LIKE_TORCH, prune_path=path)
 
 
 def test_config_fp16_torch_rounding_mode():
@@ -275,13 +277,15 @@ def test_canary_rows_are_untouched():
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("p", [0.0, 1e-3])
-def test_left_padding_mask(dt, p):
+@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+def test_left_padding_mask(dt, p, path):
     """The 9-argument overload of the reference: keys below seq_lengths[b] are masked
     (attention.cu:814-817, 1054, 1112-1113)."""
     B, H, Dh, Lp, Lmax = 4, 3, 64, 70, 75
     g, K, V = small_case(dt, B, H, Dh, Lp, Lmax, 21)
     first = torch.tensor([0, 13, 69, 70], dtype=torch.int32)
     eng = CAbiEngine(K, V, Lmax)
+    eng.set_prune_path(path)
     eng.set_launch(tile_rows=16)
     orc = O.DecodeOracle(K, V, Lmax)
     for i in range(3):
@@ -332,11 +336,13 @@ def test_per_sample_lengths_right_padding(dt):
 # ------------------------------------------------------------------------------------------
 # pruning: the kept set must equal the reference rule's
 # ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
 @pytest.mark.parametrize("name", ["prune-fp16-b10-p1e-4", "prune-fp16-b10-p1e-3"])
-def test_pruning_workload_kept_set(name):
+def test_pruning_workload_kept_set(name, path):
     w = CONFIGS[name]
     K, V = prompt_kv(w)
     eng = CAbiEngine(K, V, w.max_len)
+    eng.set_prune_path(path)
     orc = O.DecodeOracle(K, V, w.max_len)
     N = w.B * w.H
     checked = 0
@@ -353,6 +359,32 @@ def test_pruning_workload_kept_set(name):
         assert 0.03 < info["kept_fraction"] < 0.08    # the 5 % peaks survive, nothing else
         checked += 1
     assert checked >= 6 and eng.status() == 0
+
+
+@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+@pytest.mark.parametrize("dt,Dh,B,H,Lp", [(torch.float32, 80, 1, 3, 333), (torch.float16, 80, 2, 2, 1500),
+                                          (torch.bfloat16, 256, 1, 2, 2100), (torch.float32, 256, 1, 1, 40),
+                                          (torch.float16, 128, 40, 8, 95), (torch.bfloat16, 64, 1, 1, 9000)])
+def test_pruning_all_head_dims_both_paths(dt, Dh, B, H, Lp, path):
+    """Slices per (batch, head) from 1 to 8, slices shorter than a tile, rounds of more than
+    1024 rows, head_dim 80: kept set and output against the restated rule on both paths."""
+    g, K, V = small_case(dt, B, H, Dh, Lp, Lp + 2, 900 + Dh + Lp)
+    eng = CAbiEngine(K, V, Lp + 2)
+    eng.set_prune_path(path)
+    orc = O.DecodeOracle(K, V, Lp + 2)
+    for i, p in enumerate((1e-3, 0.05)):
+        t = Lp + i
+        q, k, v = qkv(g, B, H, Dh, dt)
+        q = 2.0 * q
+        got = eng.attention(q, k, v, Dh ** -0.5, t, p=p, want_mask=True)
+        orc.append(k, v, t)
+        want, kept, info = O.pruned_attention(q.view(B * H, Dh), orc.K[:, : t + 1], orc.V[:, : t + 1], Dh ** -0.5, p)
+        diff = int((eng.kept(t) != kept).sum())
+        assert diff <= info["borderline"], (p, diff, info)
+        tol = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 8e-3}[dt]
+        assert max_err(got.view(B * H, Dh), want) <= tol + 0.05 * diff
+        assert torch.equal(eng.v_cache[:, :, t].cpu(), v[:, :, 0]) and torch.equal(eng.k_cache[:, :, t].cpu(), k[:, :, 0])
+    assert eng.status() == 0
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
