@@ -630,6 +630,7 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
     float* list_p = reinterpret_cast<float*>(list_idx + R);
     float* red = list_p + R;  // [NG][DH]
     __shared__ int s_n, s_last;
+    __shared__ unsigned s_words[16];   // one ballot per 32 rows of a 512-row unit
 
     const long long U = P.total_units;
     const int upb = P.units_per_bh;
@@ -665,10 +666,14 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
         for (int j = j0; j < j1 && sr.ok; ++j) {
             const int lo = j * R, hi = min((j + 1) * R, sr.row + 1);  // includes the new token's bit
             if (hi <= lo) break;
+            // survivors are listed in row order: ballots first, then a prefix over the words
             __syncthreads();
-            if (tid == 0) s_n = 0;
-            __syncthreads();
-            for (int base = lo + warp * 32; base < hi; base += NT) {
+            float my_p[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int base = lo + (warp + 8 * k) * 32;
+                my_p[k] = -1.f;
+                if (base >= hi) continue;   // warp-uniform
                 const int i = base + lane;
                 const bool cached = i < sr.row && i >= sr.first;
                 float pr = 0.f;
@@ -681,10 +686,23 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
                 if (P.kept_mask != nullptr && lane == 0)
                     P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
                         bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
-                int pos = 0;
-                if (lane == 0 && bal) pos = atomicAdd(&s_n, __popc(bal));
-                pos = __shfl_sync(0xffffffffu, pos, 0) + __popc(bal & ((1u << lane) - 1u));
-                if (keep) list_idx[pos] = i, list_p[pos] = pr;
+                if (lane == 0) s_words[warp + 8 * k] = bal;
+                if (keep) my_p[k] = pr;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                if (my_p[k] >= 0.f) {
+                    const int w = warp + 8 * k;
+                    int pos = __popc(s_words[w] & ((1u << lane) - 1u));
+                    for (int ww = 0; ww < w; ++ww) pos += __popc(s_words[ww]);
+                    list_idx[pos] = lo + w * 32 + lane, list_p[pos] = my_p[k];
+                }
+            }
+            if (tid == 0) {
+                int tot = 0;
+                for (int w = 0; w < ((hi - lo + 31) >> 5); ++w) tot += __popc(s_words[w]);
+                s_n = tot;
             }
             __syncthreads();
             const int n = s_n;
@@ -795,7 +813,7 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
 // kernels above remain for everything else.
 //
 // Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (index, probability)
-// | group reduction area [NG][DH + 4] | partial output [DH] | (max, sum) | barriers | flags.
+// | ballot words | group reduction area [NG][DH + 4] | partial output [DH] | (max, sum) | barriers | flags.
 constexpr int kFusedThreads = 160;   // 1 copy warp + 4 compute warps
 constexpr int kFusedListCap = 512;   // rows pruned and gathered per round (multiple of 32)
 
@@ -832,7 +850,8 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     float* sc = reinterpret_cast<float*>(smem + (size_t)S * tile_bytes);
     int* list_idx = reinterpret_cast<int*>(sc + chunk);
     float* list_p = reinterpret_cast<float*>(list_idx + kFusedListCap);
-    float* red = list_p + kFusedListCap;
+    unsigned* words = reinterpret_cast<unsigned*>(list_p + kFusedListCap);   // one ballot per 32 rows of a round
+    float* red = reinterpret_cast<float*>(words + kFusedListCap / 32);
     float* accs = red + NG * RS;
     float* stat = accs + DH;                       // [0] max, [1] sum of this CTA's slice
     uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4);
@@ -1005,11 +1024,17 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache) + (size_t)bh * P.Lmax * ROWB;
     const int hi_mask = sr.ok ? min(c0 + chunk, sr.row + 1) : c0;   // rows whose mask bit this slice writes
     for (int sub = c0; sub < hi_mask; sub += kFusedListCap) {
-        __syncthreads();
-        if (tid == 0) flags[1] = 0;
+        // Survivors are listed in row order (ballots first, then a prefix over the 32-row
+        // words), so the order of the floating-point sums below never depends on timing.
         __syncthreads();
         const int sub_hi = min(sub + kFusedListCap, hi_mask);
-        for (int base = sub + warp * 32; base < sub_hi; base += kFusedThreads) {
+        constexpr int kMine = (kFusedListCap / 32 + 4) / 5;   // 32-row words per warp and round
+        float my_p[kMine];
+#pragma unroll
+        for (int k = 0; k < kMine; ++k) {
+            const int base = sub + (warp + 5 * k) * 32;
+            my_p[k] = -1.f;
+            if (base >= sub_hi) continue;   // warp-uniform
             const int i = base + lane;
             const bool cached = i >= lo && i < hi;
             float pr = 0.f;
@@ -1022,10 +1047,24 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
             if (P.kept_mask != nullptr && lane == 0)
                 P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
                     bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
-            int pos = 0;
-            if (lane == 0 && bal) pos = atomicAdd(const_cast<int*>(&flags[1]), __popc(bal));
-            pos = __shfl_sync(0xffffffffu, pos, 0) + __popc(bal & ((1u << lane) - 1u));
-            if (keep) list_idx[pos] = i, list_p[pos] = pr;
+            if (lane == 0) words[warp + 5 * k] = bal;
+            if (keep) my_p[k] = pr;
+        }
+        __syncthreads();
+        const int nwords = (sub_hi - sub + 31) >> 5;
+#pragma unroll
+        for (int k = 0; k < kMine; ++k) {
+            if (my_p[k] >= 0.f) {
+                const int w = warp + 5 * k;
+                int pos = __popc(words[w] & ((1u << lane) - 1u));
+                for (int ww = 0; ww < w; ++ww) pos += __popc(words[ww]);
+                list_idx[pos] = sub + w * 32 + lane, list_p[pos] = my_p[k];
+            }
+        }
+        if (tid == 0) {
+            int tot = 0;
+            for (int w = 0; w < nwords; ++w) tot += __popc(words[w]);
+            flags[1] = tot;
         }
         __syncthreads();
         const int n = flags[1];
@@ -1207,7 +1246,7 @@ int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, i
     const int vpr = rowb / 16;
     const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
     const int ng = 128 / lpr;
-    return stages * tile_rows * rowb + chunk_rows * 4 + kFusedListCap * 8 + ng * (head_dim + 4) * 4 + head_dim * 4 + 16 +
+    return stages * tile_rows * rowb + chunk_rows * 4 + kFusedListCap * 8 + kFusedListCap / 32 * 4 + ng * (head_dim + 4) * 4 + head_dim * 4 + 16 +
            2 * stages * 8 + 16;
 }
 

@@ -435,3 +435,20 @@ def test_bounded_wait_times_out_and_reports():
     ref = O.DecodeOracle(K, V, Lp + 1, compute_dtype=torch.float64).step(q, k, v, 0.125, Lp)
     assert_close_ulp(got, ref, dt, "step after the timed-out wait")
     assert eng.status() == 0
+
+
+@pytest.mark.parametrize("p,path", [(0.0, 0), (1e-2, 1), (1e-2, 2)], ids=["exact", "prune-fused", "prune-two-kernels"])
+def test_results_are_bitwise_reproducible(p, path):
+    """Split partials are merged in slot order and pruning survivors are listed in row order, so
+    two runs on the same inputs give the same bits whatever the CTA timing."""
+    dt, B, H, Dh, Lp = torch.float16, 3, 8, 128, 3000
+    g, K, V = small_case(dt, B, H, Dh, Lp, Lp + 1, 31)
+    q, k, v = qkv(g, B, H, Dh, dt)
+    outs = []
+    for rep in range(3):
+        eng = CAbiEngine(K, V, Lp + 1)
+        eng.set_prune_path(path)
+        eng.set_launch(tile_rows=16, ctas_per_sm=4)     # many splits per (batch, head)
+        outs.append(eng.attention(2 * q, k, v, Dh ** -0.5, Lp, p=p).cpu())
+        assert eng.status() == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
