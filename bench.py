@@ -122,7 +122,7 @@ class CpuReferenceSample:
     length.  One call of step() is one evaluation over the sample; the full-workload step
     time is extrapolated by the pair count ((batch, head) pairs are independent)."""
 
-    def __init__(self, w, pairs=32):
+    def __init__(self, w, pairs=128):
         from oracle.ffa_oracle import torch_attn_func
 
         self.fn, self.w = torch_attn_func, w

@@ -109,8 +109,9 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
 // Refinements measured with `python -m fastforwardattention_b200.tune` on B200 (CUDA-graph
 // timing, replicas rotating so that every launch streams from HBM), keyed by row bytes and by
 // the bytes one decode step streams:
-//   < 48 MB  (OPT-1.3B fp32 batch 1, 16 MB: 12.9 us vs 17.3 us)  one CTA per SM: fewer split
-//            partials and arrival counters to merge than bytes to stream
+//   < 48 MB  (OPT-1.3B fp32 batch 1, 16 MB: 12.9 us vs 17.3 us)  one CTA per SM when there are few
+//            (batch, head) pairs: fewer split partials and arrival counters to merge than bytes
+//            to stream; more CTAs only to keep it at <= 2 pairs per CTA
 //   48-600 MB, 256-byte rows (bf16 x 128, 270 MB: 5.43 vs 5.14 TB/s)  8 KB tiles, 4 CTAs per SM:
 //            the ring fills sooner and the tail is shorter
 //   48-600 MB, >= 512-byte rows (GPT-J fp16 x 256, 269 MB: 5.53 vs 5.36 TB/s)  8 compute warps
@@ -121,7 +122,11 @@ Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int
     Shape s = default_shape(p, row_bytes, rows_total, tensors);
     const double bytes = (double)rows_total * row_bytes * tensors;
     if (bytes < 48e6) {
-        s.cps = 1;
+        // every (batch, head) a CTA walks costs a serial latency chain (merge, store); with many
+        // pairs and short sequences let resident CTAs overlap those chains: <= 2 pairs per CTA
+        const long long BH = (long long)p->B * p->H;
+        const long long want = (BH + 2LL * p->sms - 1) / (2LL * p->sms);
+        s.cps = (int)(want < 1 ? 1 : want > 4 ? 4 : want);
     } else if (bytes < 600e6) {
         if (row_bytes >= 512) s.warps = 8;
         else if (row_bytes == 256) s.tile_rows /= 2, s.cps = 4;

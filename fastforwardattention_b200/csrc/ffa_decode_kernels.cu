@@ -360,6 +360,16 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
         constexpr bool kAllLanes = (VPR == LPR * VPL);  // false only for head_dim 80
         uint32_t stage = 0, phase = 0;
         long long u = u0;
+        // q of the first (batch, head) of this CTA's run; the next one is fetched while the
+        // current one is being processed, so its global-memory latency is never exposed
+        const unsigned char* qbase = static_cast<const unsigned char*>(P.q);
+        uint4 qraw[VPL];
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) {
+            qraw[x] = make_uint4(0, 0, 0, 0);
+            if (u0 < u1 && li + x * LPR < VPR)
+                qraw[x] = *reinterpret_cast<const uint4*>(qbase + (size_t)(u0 / upb) * ROWB + (li + x * LPR) * 16);
+        }
         while (u < u1) {
             const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
             const int j1 = (int)min((long long)upb, j0 + (u1 - u));
@@ -370,7 +380,26 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
             // q for this (batch, head), pre-multiplied so that scores come out of the FMAs
             // ready for the exponential (exact mode: scale only, natural-log domain)
             float qf[VPL][EPV];
-            load_row_f32<T, DH>(static_cast<const unsigned char*>(P.q) + (size_t)bh * ROWB, li, qf);
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) Elem<T>::unpack(qraw[x], qf[x]);
+            if (u + (j1 - j0) < u1) {   // this CTA goes on with the next (batch, head)
+#pragma unroll
+                for (int x = 0; x < VPL; ++x)
+                    if (li + x * LPR < VPR)
+                        qraw[x] = *reinterpret_cast<const uint4*>(qbase + (size_t)(bh + 1) * ROWB + (li + x * LPR) * 16);
+            }
+            // the new token's k and v are needed only at the end of the segment: fetch them now
+            const bool owns_new = sr.ok && j0 <= jt && jt < j1;
+            uint4 knew[VPL], vnew[VPL];
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                knew[x] = vnew[x] = make_uint4(0, 0, 0, 0);
+                if (owns_new && li + x * LPR < VPR) {
+                    const size_t src = (size_t)bh * ROWB + (li + x * LPR) * 16;
+                    knew[x] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + src);
+                    if (PASS == kPassOne) vnew[x] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + src);
+                }
+            }
             const float qmul = kPrecise ? 1.f : P.scale * kLog2e;
             float2 q2[VPL][E2];
 #pragma unroll
@@ -491,14 +520,15 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
             }
 
             // ---- the new token: score against k, append k (and v) at row sr.row ----
-            if (sr.ok && j0 <= jt && jt < j1) {
-                float kf[VPL][EPV];
-                load_row_f32<T, DH>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB, li, kf);
+            if (owns_new) {
                 float dot = 0.f;
 #pragma unroll
-                for (int x = 0; x < VPL; ++x)
+                for (int x = 0; x < VPL; ++x) {
+                    float kf[EPV];
+                    Elem<T>::unpack(knew[x], kf);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[x][e], dot);
+                    for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[e], dot);
+                }
                 dot = group_sum<LPR>(dot);  // every group computes it; group 0 uses it
                 if (g == 0) {
                     const float st = score_of(dot);
@@ -511,14 +541,11 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                     for (int x = 0; x < VPL; ++x) {
                         const int vec = li + x * LPR;
                         if (vec < VPR) {
-                            const size_t src = (size_t)bh * ROWB + vec * 16;
-                            const uint4 kraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + src);
-                            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + vec * 16) = kraw;
+                            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + vec * 16) = knew[x];
                             if (PASS == kPassOne) {
-                                const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + src);
-                                *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
+                                *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vnew[x];
                                 float2 v2[E2];
-                                Elem<T>::unpack2(vraw, v2);
+                                Elem<T>::unpack2(vnew[x], v2);
 #pragma unroll
                                 for (int e = 0; e < E2; ++e) {
                                     acc2[x][e].x = fmaf(pr, v2[e].x, acc2[x][e].x * corr);
