@@ -29,7 +29,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from fastforwardattention_b200.workloads import CONFIGS, device_prompt_kv  # noqa: E402
+from fastforwardattention_b200.workloads import CONFIGS, device_prompt_kv, device_step_qkv  # noqa: E402
 
 METRIC = "decode_attention_steps_per_sec"
 FALLBACK_HBM_GBS = 6650.0
@@ -40,9 +40,12 @@ FALLBACK_HBM_GBS = 6650.0
 TRAFFIC_RATIO = 1.004
 
 
-def algorithmic_bytes(es, B, H, Dh, t):
-    """K and V rows 0..t-1 read once, q/k/v read, rows t written, out written."""
-    return es * B * H * Dh * (2 * t + 6)
+def algorithmic_bytes(es, B, H, Dh, t, kept_frac=None):
+    """K and V rows 0..t-1 read once, q/k/v read, rows t written, out written.  With pruning
+    only the surviving share of the V rows is read."""
+    if kept_frac is None:
+        return es * B * H * Dh * (2 * t + 6)
+    return es * B * H * Dh * (t + 6) + int(es * B * H * Dh * t * kept_frac)
 
 
 def gpu_id(dev):
@@ -221,7 +224,8 @@ def main():
 
     sharded, engines = [], []
     for r in range(nrep):
-        K, V = device_prompt_kv(replace(w, seed=w.seed + 17 * r), dev)
+        # (the pruning workload keeps one seed: its step queries must stay aligned with the peaked keys)
+        K, V = device_prompt_kv(w if w.peaked else replace(w, seed=w.seed + 17 * r), dev)
         if world > 1:
             sharded.append(ShardedFastForwardAttn(K, V, w.max_len, False))
             engines.append(sharded[-1].engine)
@@ -235,8 +239,7 @@ def main():
     shape = engines[0].launch_shape(w.max_len - 1)
 
     total = args.warmup + args.steps
-    g = torch.Generator(device=dev).manual_seed(w.seed + 1)
-    qkv_d = torch.randn(total, 3, w.B, w.H, 1, w.Dh, generator=g, device=dev, dtype=torch.float32).to(w.dtype)
+    qkv_d = device_step_qkv(w, total, dev)
     qkv_h = qkv_d.cpu().pin_memory()
     out_d = torch.empty(w.B, w.H, w.Dh, dtype=w.dtype, device=dev)
     stage = torch.empty(3, w.B, w.H, 1, w.Dh, dtype=w.dtype, device=dev)
@@ -249,14 +252,14 @@ def main():
         torch.cuda.synchronize()
 
     def resident_step(s):
-        engines[s % nrep].attention(qkv_d[s, 0], qkv_d[s, 1], qkv_d[s, 2], w.scale, t_of(s), 0.0, out=out_d)
+        engines[s % nrep].attention(qkv_d[s, 0], qkv_d[s, 1], qkv_d[s, 2], w.scale, t_of(s), w.p, out=out_d)
 
     def e2e_step(s):
         stage.copy_(qkv_h[s], non_blocking=True)
         if world > 1:
-            o = sharded[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0, gather=True)
+            o = sharded[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), w.p, gather=True)
         else:
-            o = engines[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), 0.0)
+            o = engines[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), w.p)
         out_h.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the caller consumes the result every step
 
@@ -280,7 +283,17 @@ def main():
     launches = launch_count() - launches0
     loop_ms = start.elapsed_time(stop)
     kernel_ms = [a.elapsed_time(b) for a, b in ev]
-    alg = [algorithmic_bytes(es, w.B, w.H, w.Dh, t_of(args.warmup + i)) for i in range(args.steps)]
+    kept_frac = None
+    if w.p > 0:
+        # share of cached V rows that survive the threshold, counted from the kept mask of one step
+        s_last = args.warmup + args.steps - 1
+        engines[s_last % nrep].record_kept_mask(True)
+        resident_step(s_last)
+        m = engines[s_last % nrep].get_kept_mask().view(-1)
+        bits = sum(int(((m >> i) & 1).sum()) for i in range(32))
+        kept_frac = bits / (w.B * w.H * (t_of(s_last) + 1))
+        engines[s_last % nrep].record_kept_mask(False)
+    alg = [algorithmic_bytes(es, w.B, w.H, w.Dh, t_of(args.warmup + i), kept_frac) for i in range(args.steps)]
     # keep the same load running (untimed) until the clock sampler has seen it for half a second
     while time.time() - wall0 < 0.5:
         for i in range(args.steps):
@@ -319,9 +332,10 @@ def main():
                 "hbm_gbs_all_gpus": world * sum(alg) / (loop_ms * 1e-3) / 1e9,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
-                             "kernel": "ffa_stream_kernel (one-pass)", "bytes_per_launch": per_launch_alg,
+                             "kernel": "ffa_stream_kernel (one-pass)" if w.p == 0 else "ffa_prune_cluster_kernel",
+                             "kept_v_rows": kept_frac, "bytes_per_launch": per_launch_alg,
                              "avg_launch_ms": ksum_ms / args.steps,
-                             "traffic": TRAFFIC_RATIO * per_launch_alg if TRAFFIC_RATIO else None},
+                             "traffic": TRAFFIC_RATIO * per_launch_alg if (TRAFFIC_RATIO and w.p == 0) else None},
                 "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "steps/s",
                         "h2d_bytes_per_step": 3 * w.B * w.H * w.Dh * es, "d2h_bytes_per_step": out_h.numel() * es,
                         "includes": "pinned-host q/k/v upload, attention, output all-gather (N>1), output download, sync"},

@@ -103,12 +103,30 @@ def step_qkv(w: Workload) -> Iterator[Tuple[int, torch.Tensor, torch.Tensor, tor
 
 def device_prompt_kv(w: Workload, device) -> Tuple[torch.Tensor, torch.Tensor]:
     """Prompt K and V generated directly in device memory (benchmark sizes: 8.6 GB per tensor
-    at 32 K tokens would take minutes through the host generator).  Values are N(0,1)."""
+    at 32 K tokens would take minutes through the host generator).  Values are N(0,1); the
+    pruning workload puts 4*q0 on a seeded 5 % of the positions and N(0, 0.5) elsewhere."""
     g = torch.Generator(device=device).manual_seed(w.seed)
     shape = (w.B, w.H, w.prompt, w.Dh)
     K = torch.empty(shape, dtype=w.dtype, device=device)
     V = torch.empty(shape, dtype=w.dtype, device=device)
+    q0 = _base_query(w).to(device).view(w.B, w.H, 1, w.Dh) if w.peaked else None
     for b in range(w.B):
         K[b].normal_(generator=g)
         V[b].normal_(generator=g)
+        if w.peaked:
+            peak = torch.rand(w.H, w.prompt, 1, generator=g, device=device) < 0.05
+            K[b] = torch.where(peak, (4.0 * q0[b]).to(w.dtype), (0.5 * K[b].float()).to(w.dtype))
     return K, V
+
+
+def device_step_qkv(w: Workload, steps: int, device) -> torch.Tensor:
+    """[steps, 3, B, H, 1, Dh] of q, k, v for `steps` decode steps, generated on the device
+    with the same distributions as step_qkv (not the same values)."""
+    g = torch.Generator(device=device).manual_seed(w.seed + 1)
+    x = torch.randn(steps, 3, w.B, w.H, 1, w.Dh, generator=g, device=device, dtype=torch.float32)
+    if w.peaked:
+        q0 = _base_query(w).to(device).view(1, w.B, w.H, 1, w.Dh)
+        x[:, 0] = q0 + 0.25 * x[:, 0]
+        peak = torch.rand(steps, w.B, w.H, 1, 1, generator=g, device=device) < 0.05
+        x[:, 1] = torch.where(peak, 4.0 * q0, 0.5 * x[:, 1])
+    return x.to(w.dtype)
