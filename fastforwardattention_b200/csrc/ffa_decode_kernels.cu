@@ -15,6 +15,9 @@
 //   ffa_value_gather_kernel<T, DH>        second half: tests every cached row with the
 //                                         reference's pruning rule (attention.cu:1184-1191,
 //                                         461-469) and loads only the V rows that survive
+//   ffa_prune_cluster_kernel<T, DH>       both halves in one launch: a thread-block cluster per
+//                                         (batch, head), scores in shared memory, statistics
+//                                         and partial outputs over distributed shared memory
 //   ffa_cache_init_kernel                 prompt K/V -> rows [0, prompt) of the caches
 //
 // One query row per head is a matrix-vector product (2 flops per cache element read), so the

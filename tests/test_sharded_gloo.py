@@ -84,3 +84,52 @@ def test_head_range_rejects_uneven_split():
 
     with pytest.raises(ValueError):
         head_range(6, 0, 4)
+
+
+def _worker_peer_leaves(rank, world, port, q_out):
+    """Rank 1 leaves between steps; rank 0 must get an error from the next gather, not a hang."""
+    import datetime
+    import time
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from fastforwardattention_b200.sharded import ShardedFastForwardAttn, shard_heads
+
+    g = torch.Generator().manual_seed(1)
+    B, H, Dh, Lp = 1, 4, 64, 5
+    K = torch.randn(B, H, Lp, Dh, generator=g)
+    V = torch.randn(B, H, Lp, Dh, generator=g)
+    eng = ShardedFastForwardAttn(shard_heads(K, rank, world, H), shard_heads(V, rank, world, H), Lp + 2, False,
+                                 engine_factory=OracleEngine)
+    q, k, v = (shard_heads(torch.randn(B, H, 1, Dh, generator=g), rank, world, H) for _ in range(3))
+    full = eng.attention(q, k, v, 0.125, Lp, gather=True)          # step 0: everybody is there
+    assert full.shape == (B, H, Dh)
+    def report(msg):
+        q_out.put((rank, msg))
+        q_out.close()
+        q_out.join_thread()                                        # flushed before the process goes away
+        os._exit(0)
+
+    if rank == 1:
+        report("left")                                             # leaves between steps, nothing in flight
+    t0 = time.time()
+    try:
+        eng.attention(q, k, v, 0.125, Lp + 1, gather=True)         # step 1: the peer is gone
+        report("no error")
+    except Exception as e:                                         # noqa: BLE001 - any backend error type
+        report(f"error after {time.time() - t0:.1f}s: {type(e).__name__}")
+
+
+def test_gather_fails_instead_of_hanging_when_a_rank_leaves():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_peer_leaves, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in procs)
+    for p in procs:
+        p.join(30)
+    assert res[1] == "left"
+    assert res[0].startswith("error after"), res
