@@ -51,7 +51,7 @@ def to_np(x: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "..", "..", "..", "reference")
     fn = load_reference_function(ref_root)
     torch.set_num_threads(1)
     for name, dt, B, H, Dh, Lp, steps, seed in CASES:
