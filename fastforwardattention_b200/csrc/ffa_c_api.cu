@@ -48,6 +48,7 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 struct ffa_plan {
     int dtype, B, H, Dh, Lmax, use_default, device, mode;
     int prune_path;  // 0 = choose, 1 = fused cluster kernel only, 2 = two kernels only
+    bool offline;    // planning only: created from given device properties, never launches
     int sms, smem_per_cta, smem_per_sm;
     bool forced;
     ffa_launch_t force;
@@ -158,7 +159,7 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
     if (!tile_forced) {
         // small problems: shrink tiles until every CTA slot has a few units to stream
         const long long slots = (long long)p->sms * s.cps;
-        while (s.tile_rows > 8 && BH * (cap_rows / s.tile_rows + 1) < 4 * slots) s.tile_rows /= 2;
+        while (s.tile_rows > 8 && BH * (cap_rows / s.tile_rows + 1) < 4 * slots) s.tile_rows = (s.tile_rows / 2 + 7) / 8 * 8;
     }
     // shared-memory budget: per CTA and per SM
     for (;;) {
@@ -202,7 +203,8 @@ bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out
     for (int c = 1; c <= 8; c *= 2) {
         const int chunk = (int)(((long long)cap_rows + 1 + c - 1) / c + 31) / 32 * 32;
         if (c > 1 && chunk < 128) break;
-        int r = 8192 / rowb;
+        int r = 8192 / rowb / 8 * 8;
+        if (r < 8) r = 8;
         if (r > chunk) r = (chunk + 7) / 8 * 8;
         const int smem = ffa_k_fused_smem_bytes(p->dtype, p->Dh, r, 3, chunk);
         if (smem > p->smem_per_cta) continue;
@@ -303,6 +305,43 @@ int ffa_plan_create(int dtype, int batch, int heads, int head_dim, int max_len, 
     return FFA_OK;
 }
 
+int ffa_plan_create_offline(int dtype, int batch, int heads, int head_dim, int max_len, int use_default_launch, int sms,
+                            int smem_per_cta, int smem_per_sm, ffa_plan_t** plan)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan pointer");
+    *plan = nullptr;
+    if (!dtype_ok(dtype)) return fail(FFA_ERR_DTYPE, "unsupported dtype code %d", dtype);
+    if (!head_dim_ok(head_dim)) return fail(FFA_ERR_HEAD_DIM, "unsupported head_dim %d (64, 80, 128, 256)", head_dim);
+    if (batch <= 0 || heads <= 0 || max_len <= 0) return fail(FFA_ERR_RANGE, "batch, heads and max_len must be positive");
+    if (sms <= 0 || smem_per_cta <= 0 || smem_per_sm < smem_per_cta) return fail(FFA_ERR_RANGE, "implausible device properties");
+    ffa_plan* p = new (std::nothrow) ffa_plan();
+    if (p == nullptr) return fail(FFA_ERR_ARG, "out of host memory");
+    std::memset(p, 0, sizeof(*p));
+    p->dtype = dtype, p->B = batch, p->H = heads, p->Dh = head_dim, p->Lmax = max_len;
+    p->use_default = use_default_launch != 0, p->device = -1, p->mode = FFA_MODE_EXACT;
+    p->sms = sms, p->smem_per_cta = smem_per_cta, p->smem_per_sm = smem_per_sm;
+    p->max_grid = sms * kMaxCtasPerSm;
+    p->offline = true;
+    *plan = p;
+    return FFA_OK;
+}
+
+int ffa_plan_get_prune_launch(const ffa_plan_t* plan, int t, int* cluster, int* chunk_rows, int* tile_rows, int* grid,
+                              int* smem_bytes)
+{
+    if (plan == nullptr || !cluster || !chunk_rows || !tile_rows || !grid || !smem_bytes) return fail(FFA_ERR_ARG, "null pointer");
+    if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
+    FfaStepParams P;
+    std::memset(&P, 0, sizeof(P));
+    int smem = 0;
+    if (plan->prune_path == 2 || !plan_fused(plan, t, &P, &smem)) {
+        *cluster = 0, *chunk_rows = 0, *tile_rows = 0, *grid = 0, *smem_bytes = 0;   // two-kernel path
+        return FFA_OK;
+    }
+    *cluster = P.cluster, *chunk_rows = P.chunk_rows, *tile_rows = P.tile_rows, *grid = P.grid, *smem_bytes = smem;
+    return FFA_OK;
+}
+
 void ffa_plan_destroy(ffa_plan_t* plan) { delete plan; }
 
 int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch)
@@ -366,6 +405,7 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
                   uint32_t* kept_mask, void* stream)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (plan->offline) return fail(FFA_ERR_ARG, "this plan was created offline (planning only) and cannot launch");
     if (!q || !k || !v || !k_cache || !v_cache || !out) return fail(FFA_ERR_ARG, "null tensor pointer");
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
         return fail(FFA_ERR_ARG, "tensor pointers must be 16-byte aligned");

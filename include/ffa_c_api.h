@@ -83,6 +83,11 @@ int ffa_cache_init(int dtype, int batch, int heads, int prompt_len, int max_len,
  * the FastForwardAttn constructor (torch_ffa_api.cpp:162-177, 196-201). */
 int ffa_plan_create(int dtype, int batch, int heads, int head_dim, int max_len, int use_default_launch,
                     int device, ffa_plan_t** plan);
+/* The same planner without a device: the caller states the multiprocessor count and the
+ * shared-memory limits (per CTA opt-in, per SM).  For capacity planning and for testing the
+ * launch rules on hosts without a GPU; such a plan cannot be passed to ffa_attention. */
+int ffa_plan_create_offline(int dtype, int batch, int heads, int head_dim, int max_len, int use_default_launch, int sms,
+                            int smem_per_cta, int smem_per_sm, ffa_plan_t** plan);
 void ffa_plan_destroy(ffa_plan_t* plan);
 
 /* The launch shape the planner picks for step t (after any override). */
@@ -99,6 +104,11 @@ int ffa_plan_set_mode(ffa_plan_t* plan, int mode);
  * memory.  The reference does both phases in one CTA per (batch, head) (attention.cu:1077-1257),
  * which is what caps its sequence length. */
 int ffa_plan_set_prune_path(ffa_plan_t* plan, int path);
+/* The fused pruning launch the planner picks for step t: CTAs per (batch, head) cluster, cache
+ * rows per CTA, tile rows, grid and dynamic shared memory; all zero when the two-launch path
+ * would run instead. */
+int ffa_plan_get_prune_launch(const ffa_plan_t* plan, int t, int* cluster, int* chunk_rows, int* tile_rows, int* grid,
+                              int* smem_bytes);
 
 /* Scratch the engine needs in device memory: split partials, arrival counters, the status
  * word and, when with_scores != 0 (needed for p > 0 and FFA_MODE_ROUND_LIKE_TORCH), one fp32
