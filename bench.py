@@ -32,6 +32,7 @@ sys.path.insert(0, ROOT)
 from fastforwardattention_b200.workloads import CONFIGS, device_prompt_kv, device_step_qkv  # noqa: E402
 
 METRIC = "decode_attention_steps_per_sec"
+DTYPE_NAME = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}   # storage type; sums are fp32
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the streaming kernel divided by
 # the launch's algorithmic bytes, from the ncu capture summarised under profiles/ (captured on
@@ -166,7 +167,7 @@ def run_reference(args, w):
     value = smp.run(steps, min(args.warmup, 3))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "steps/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": 1e3 / value, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": str(w.dtype).split(".")[-1], "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_NAME[w.dtype], "data": "synthetic",
             "config": workload_config(w, args.gpus),
             "cpu_baseline": {"value": value, "unit": "steps/s", "cores": smp.cores, "kind": "port",
                              "sample": smp.describe(steps)},
@@ -328,7 +329,7 @@ def main():
         line = {"metric": METRIC, "value": args.steps / (loop_ms * 1e-3), "unit": "steps/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": loop_ms / args.steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": str(w.dtype).split(".")[-1], "data": "synthetic", "config": workload_config(full, world),
+                "dtype": DTYPE_NAME[w.dtype], "accumulate": "f32", "data": "synthetic", "config": workload_config(full, world),
                 "hbm_gbs_all_gpus": world * sum(alg) / (loop_ms * 1e-3) / 1e9,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
