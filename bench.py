@@ -266,8 +266,7 @@ def main():
 
     clocks = ClockSampler(gpu_id(dev)).start()
 
-    # ---- leg 1: inputs resident in HBM; per-launch events give the kernel's own duration ----
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # ---- leg 1: inputs resident in HBM ----
     for s in range(args.warmup):
         resident_step(s)
     barrier()
@@ -276,14 +275,39 @@ def main():
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for i in range(args.steps):
-        ev[i][0].record()
         resident_step(args.warmup + i)
-        ev[i][1].record()
     stop.record()
     barrier()
     launches = launch_count() - launches0
     loop_ms = start.elapsed_time(stop)
-    kernel_ms = [a.elapsed_time(b) for a, b in ev]
+    # keep the same load running (untimed) until the clock sampler has seen it for half a second
+    while time.time() - wall0 < 0.5:
+        for i in range(args.steps):
+            resident_step(args.warmup + i)
+        torch.cuda.synchronize()
+    wall1 = time.time()
+    clocks.stop()
+    # the kernel's own duration for the roofline: the same K launches recorded in a CUDA graph and
+    # replayed, so no host work sits between them (matters when a launch is shorter than the
+    # host's per-call time); CUDA events around the replay, on the replay's stream
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        resident_step(args.warmup)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):   # other threads (NCCL watchdog) keep running
+        for i in range(args.steps):
+            resident_step(args.warmup + i)
+    graph.replay()
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    graph.replay()
+    g1.record()
+    torch.cuda.synchronize()
+    kernel_ms = [g0.elapsed_time(g1) / args.steps] * args.steps
     kept_frac = None
     if w.p > 0:
         # share of cached V rows that survive the threshold, counted from the kept mask of one step
@@ -295,13 +319,6 @@ def main():
         kept_frac = bits / (w.B * w.H * (t_of(s_last) + 1))
         engines[s_last % nrep].record_kept_mask(False)
     alg = [algorithmic_bytes(es, w.B, w.H, w.Dh, t_of(args.warmup + i), kept_frac) for i in range(args.steps)]
-    # keep the same load running (untimed) until the clock sampler has seen it for half a second
-    while time.time() - wall0 < 0.5:
-        for i in range(args.steps):
-            resident_step(args.warmup + i)
-        torch.cuda.synchronize()
-    wall1 = time.time()
-    clocks.stop()
 
     # ---- leg 2: end to end through the Python class with host buffers ----
     for s in range(min(3, args.warmup)):
