@@ -20,7 +20,8 @@ SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_des
 
 
 class Launch(C.Structure):
-    _fields_ = [(n, C.c_int) for n in ("tile_rows", "stages", "consumer_warps", "ctas_per_sm", "grid", "smem_bytes")]
+    _fields_ = [(n, C.c_int) for n in ("tile_rows", "stages", "consumer_warps", "ctas_per_sm", "grid", "smem_bytes",
+                                        "parts_per_bh")]
 
 
 class FfaError(RuntimeError):

@@ -42,6 +42,10 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 constexpr int kMaxCtasPerSm = 8;
 constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident CTA
+// below this many tiles per CTA slot the work list is cut on (batch, head) boundaries (measured:
+// bf16 x 128, batch 32 x 32 heads: 2 K tokens 154.9 vs 159.3 us, 1 K 81.8 vs 88.3 us, 512 45.6 vs
+// 48.9 us in favour of the aligned cut; 8 K tokens 603 vs 594 us against it)
+constexpr long long kAlignedBelowUnitsPerSlot = 200;
 
 }  // namespace
 
@@ -122,15 +126,23 @@ Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int
 {
     Shape s = default_shape(p, row_bytes, rows_total, tensors);
     const double bytes = (double)rows_total * row_bytes * tensors;
+    const long long BH = (long long)p->B * p->H;
     if (bytes < 48e6) {
         // every (batch, head) a CTA walks costs a serial latency chain (merge, store); with many
         // pairs and short sequences let resident CTAs overlap those chains: <= 2 pairs per CTA
-        const long long BH = (long long)p->B * p->H;
         const long long want = (BH + 2LL * p->sms - 1) / (2LL * p->sms);
         s.cps = (int)(want < 1 ? 1 : want > 4 ? 4 : want);
+        if (tensors == 2) s.stages = 3;   // OPT-1.3B fp32 batch 1: 10.7 us vs 11.3 us
     } else if (bytes < 600e6) {
-        if (row_bytes >= 512) s.warps = 8;
-        else if (row_bytes == 256) s.tile_rows /= 2, s.cps = 4;
+        if (row_bytes >= 512 && BH <= p->sms) {
+            // GPT-J fp16 x 256, batch 8 (128 pairs, 269 MB): one CTA per pair and per SM with a deep
+            // ring of 32 KB tiles, no split to merge: 42.9 us vs 47.5 us for two CTAs per pair
+            s.cps = 1, s.warps = 8, s.stages = tensors == 2 ? 3 : 4, s.tile_rows = 32768 / row_bytes;
+        } else if (row_bytes >= 512) {
+            s.warps = 8;
+        } else if (row_bytes == 256) {
+            s.tile_rows /= 2, s.cps = 4;
+        }
     }
     return s;
 }
@@ -156,10 +168,21 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
     if (s.tile_rows < 8) s.tile_rows = 8;
     s.tile_rows = (s.tile_rows + 7) / 8 * 8;  // keeps every tile a multiple of 128 bytes
     const bool tile_forced = p->forced && p->force.tile_rows > 0;
+    const bool grid_forced = p->forced && p->force.grid > 0;
+    // fewer (batch, head) pairs than CTA slots: each pair will be cut into C aligned parts (below);
+    // size the tiles so that a part is about four of them (enough for the 2-stage ring to overlap)
+    const long long slots0 = (long long)p->sms * s.cps;
+    const bool few_pairs = !grid_forced && BH <= slots0 && BH * (cap_rows / s.tile_rows + 1) < kAlignedBelowUnitsPerSlot * slots0;
     if (!tile_forced) {
-        // small problems: shrink tiles until every CTA slot has a few units to stream
-        const long long slots = (long long)p->sms * s.cps;
-        while (s.tile_rows > 8 && BH * (cap_rows / s.tile_rows + 1) < 4 * slots) s.tile_rows = (s.tile_rows / 2 + 7) / 8 * 8;
+        if (few_pairs) {
+            const long long c = slots0 / BH;
+            long long rows = (cap_rows / c / 4 + 7) / 8 * 8;
+            if (rows < 8) rows = 8;
+            if (rows < s.tile_rows) s.tile_rows = (int)rows;
+        } else {
+            // small problems: shrink tiles until every CTA slot has a few units to stream
+            while (s.tile_rows > 8 && BH * (cap_rows / s.tile_rows + 1) < 4 * slots0) s.tile_rows = (s.tile_rows / 2 + 7) / 8 * 8;
+        }
     }
     // shared-memory budget: per CTA and per SM
     for (;;) {
@@ -174,11 +197,37 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
         else if (s.cps > 1) --s.cps;
         else return fail(FFA_ERR_ARG, "no launch shape fits in shared memory");
     }
-    const long long units = BH * (cap_rows / s.tile_rows + 1);
+    // How the work list is cut (see Partition in the kernels).  Large problems: an even cut of the
+    // unit list.  Small ones (fewer than 200 units per CTA slot): CTA boundaries on (batch, head)
+    // boundaries -- C CTAs per pair when there are fewer pairs than slots, one CTA per pair when
+    // a third or fourth resident CTA per SM makes room for all pairs -- because there the serial
+    // per-segment latency and the merge of split pairs cost more than imbalance does
+    // (OPT-1.3B batch 1: 10.5 us vs 13.1 us; fp16 batch 10: 21.2 us vs 23.1 us).
+    const int upb = cap_rows / s.tile_rows + 1;
+    const long long units = BH * upb;
     long long grid = (long long)p->sms * s.cps;
+    int parts = upb;
+    if (!grid_forced && units < kAlignedBelowUnitsPerSlot * grid) {
+        if (BH <= grid) {
+            long long c = grid / BH;
+            if (c > upb) c = upb;
+            parts = (int)c, grid = BH * c;
+        } else {
+            const int need = (int)((BH + p->sms - 1) / p->sms);
+            const int smem = out->smem_bytes;
+            if (need <= 4 && (long long)need * (smem + kSmemReservePerCta) <= p->smem_per_sm && !(p->forced && p->force.ctas_per_sm > 0)) {
+                s.cps = need, parts = 1, grid = BH;
+            } else {
+                // more pairs than slots: k whole pairs per CTA, nothing straddles
+                const long long k = (BH + grid - 1) / grid;
+                parts = 1, grid = (BH + k - 1) / k;
+            }
+        }
+    }
     if (grid > units) grid = units;
-    if (p->forced && p->force.grid > 0 && p->force.grid < grid) grid = p->force.grid;
+    if (grid_forced && p->force.grid < grid) grid = p->force.grid;
     if (grid > p->max_grid) grid = p->max_grid;
+    out->parts_per_bh = parts;
     out->tile_rows = s.tile_rows;
     out->stages = s.stages;
     out->consumer_warps = s.warps;
@@ -448,6 +497,7 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     if (r != FFA_OK) return r;
     P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
     P.units_per_bh = cap / L.tile_rows + 1;
+    P.parts_per_bh = L.parts_per_bh;
     P.total_units = BH * P.units_per_bh;
     const int threads = 32 * (L.consumer_warps + 1);
     if (!twopass) {
@@ -461,6 +511,7 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     V.tile_rows = 512;
     V.stages = 0;
     V.units_per_bh = cap / V.tile_rows + 1;
+    V.parts_per_bh = V.units_per_bh;
     V.total_units = BH * V.units_per_bh;
     long long vgrid = (long long)plan->sms * 4;
     if (vgrid > V.total_units) vgrid = V.total_units;

@@ -240,11 +240,33 @@ __device__ __forceinline__ SampleRange sample_range(const FfaStepParams& P, int 
     return r;
 }
 
-// CTA c of G owns units [c*U/G, (c+1)*U/G); the CTA that owns unit u:
-__device__ __forceinline__ long long unit_start(long long c, long long U, int G) { return c * U / G; }
-__device__ __forceinline__ int cta_of_unit(long long u, long long U, int G)
+// Work decomposition.  Every (batch, head) is cut into `parts_per_bh` parts of whole tiles
+// (part p of a pair covers its units [p*upb/C, (p+1)*upb/C)); the flat list of B*H*C parts is
+// cut into `grid` equal contiguous runs, one per CTA.  With C = units per pair this is a plain
+// even cut of the unit list (large problems: perfect balance); with a small C and grid = B*H*C
+// or B*H/k every CTA boundary falls on a part boundary, so a CTA owns exactly one segment and
+// a pair is merged from exactly C partials (small problems: the serial per-segment latency
+// and the merge traffic are what cost).  Requires C <= upb and grid <= B*H*C.
+struct Partition {
+    long long parts_total;
+    int upb, C, G;
+    __device__ __forceinline__ long long unit_of_part(long long p) const
+    {
+        const long long bh = p / C;
+        return bh * upb + ((p - bh * C) * upb) / C;
+    }
+    __device__ __forceinline__ long long first_unit(long long cta) const { return unit_of_part(cta * parts_total / G); }
+    // the CTA that owns part p
+    __device__ __forceinline__ int cta_of_part(long long p) const { return (int)(((p + 1) * G + parts_total - 1) / parts_total - 1); }
+    __device__ __forceinline__ int first_cta_of(int bh) const { return cta_of_part((long long)bh * C); }
+    __device__ __forceinline__ int last_cta_of(int bh) const { return cta_of_part((long long)(bh + 1) * C - 1); }
+};
+__device__ __forceinline__ Partition make_partition(const FfaStepParams& P)
 {
-    return (int)(((u + 1) * G + U - 1) / U - 1);
+    Partition q;
+    q.upb = P.units_per_bh, q.C = P.parts_per_bh, q.G = P.grid;
+    q.parts_total = (long long)P.B * P.H * P.parts_per_bh;
+    return q;
 }
 
 template <typename T, int DH>
@@ -314,9 +336,9 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
     }
     __syncthreads();
 
-    const long long U = P.total_units;
     const int upb = P.units_per_bh;
-    const long long u0 = unit_start(blockIdx.x, U, P.grid), u1 = unit_start(blockIdx.x + 1, U, P.grid);
+    const Partition cut = make_partition(P);
+    const long long u0 = cut.first_unit(blockIdx.x), u1 = cut.first_unit(blockIdx.x + 1);
     const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache);
     const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
 
@@ -604,8 +626,7 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                 // cross-CTA merge without waiting: whoever arrives last does it
                 __threadfence();
                 named_bar_sync(1, nct);
-                const int c_first = cta_of_unit((long long)bh * upb, U, P.grid);
-                const int c_last = cta_of_unit((long long)(bh + 1) * upb - 1, U, P.grid);
+                const int c_first = cut.first_cta_of(bh), c_last = cut.last_cta_of(bh);
                 const int count = c_last - c_first + 1;
                 if (ctid == 0) {
                     const int old = atomicAdd(P.tickets + bh, 1);
@@ -662,9 +683,9 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
     __shared__ int s_n, s_last;
     __shared__ unsigned s_words[16];   // one ballot per 32 rows of a 512-row unit
 
-    const long long U = P.total_units;
     const int upb = P.units_per_bh;
-    const long long u0 = unit_start(blockIdx.x, U, P.grid), u1 = unit_start(blockIdx.x + 1, U, P.grid);
+    const Partition cut = make_partition(P);
+    const long long u0 = cut.first_unit(blockIdx.x), u1 = cut.first_unit(blockIdx.x + 1);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = tid / LPR, li = tid % LPR;
     const bool prune = P.p > 0.f;
@@ -808,8 +829,7 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
         if (!whole) {
             __threadfence();
             __syncthreads();
-            const int c_first = cta_of_unit((long long)bh * upb, U, P.grid);
-            const int c_last = cta_of_unit((long long)(bh + 1) * upb - 1, U, P.grid);
+            const int c_first = cut.first_cta_of(bh), c_last = cut.last_cta_of(bh);
             const int count = c_last - c_first + 1;
             if (tid == 0) s_last = (atomicAdd(P.tickets + bh, 1) == count - 1);
             __syncthreads();

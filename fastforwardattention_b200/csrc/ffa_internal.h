@@ -14,9 +14,9 @@ struct FfaStepParams {
     const int* seq_lengths;  // [B] or null
     int right_or_no_padding;
     int B, H, Lmax, t;
-    // work decomposition: every (batch, head) owns units_per_bh tiles of tile_rows cache rows;
-    // the flat list of B*H*units_per_bh units is cut into `grid` equal contiguous runs
-    int tile_rows, stages, units_per_bh, grid;
+    // work decomposition: every (batch, head) owns units_per_bh tiles of tile_rows cache rows, grouped
+    // into parts_per_bh parts; the flat list of B*H*parts_per_bh parts is cut into `grid` equal runs
+    int tile_rows, stages, units_per_bh, parts_per_bh, grid;
     long long total_units;
     float scale;
     float p;

@@ -163,7 +163,7 @@ struct FastForwardAttn {
     void set_prune_path(int path) { check(ffa_plan_set_prune_path(plan, path), "prune path"); }
     void set_launch(int tile_rows, int stages, int consumer_warps, int ctas_per_sm, int grid)
     {
-        ffa_launch_t l{tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0};
+        ffa_launch_t l{tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0, 0};
         const bool any = tile_rows > 0 || stages > 0 || consumer_warps > 0 || ctas_per_sm > 0 || grid > 0;
         check(ffa_plan_set_launch(plan, any ? &l : nullptr), "launch override");
     }
@@ -173,7 +173,7 @@ struct FastForwardAttn {
         check(ffa_plan_get_launch(plan, (int)t, &l), "launch shape");
         py::dict d;
         d["tile_rows"] = l.tile_rows, d["stages"] = l.stages, d["consumer_warps"] = l.consumer_warps;
-        d["ctas_per_sm"] = l.ctas_per_sm, d["grid"] = l.grid, d["smem_bytes"] = l.smem_bytes;
+        d["ctas_per_sm"] = l.ctas_per_sm, d["grid"] = l.grid, d["smem_bytes"] = l.smem_bytes, d["parts_per_bh"] = l.parts_per_bh;
         return d;
     }
     void record_kept_mask(bool on) { want_mask = on; }

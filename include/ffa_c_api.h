@@ -60,8 +60,9 @@ typedef struct ffa_launch {
     int stages;         /* depth of the shared-memory ring */
     int consumer_warps; /* compute warps per CTA (one more warp issues the bulk copies) */
     int ctas_per_sm;    /* resident CTAs per SM the grid is sized for */
-    int grid;           /* number of CTAs; the (batch*head, tile) work list is cut evenly */
+    int grid;           /* number of CTAs; the work list is cut into this many contiguous runs */
     int smem_bytes;     /* dynamic shared memory per CTA */
+    int parts_per_bh;   /* parts a (batch, head) is cut into; CTA runs are whole parts (output only) */
 } ffa_launch_t;
 
 /* Bytes of the two cache slabs, each laid out [batch, heads, max_len, head_dim] (row t of

@@ -60,7 +60,7 @@ class CAbiEngine:
         capi.check(self.L.ffa_plan_set_prune_path(self.plan, path))
 
     def set_launch(self, tile_rows=0, stages=0, consumer_warps=0, ctas_per_sm=0, grid=0):
-        l = capi.Launch(tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0)
+        l = capi.Launch(tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0, 0)
         capi.check(self.L.ffa_plan_set_launch(self.plan, C.byref(l)))
 
     def launch_shape(self, t):

@@ -38,6 +38,8 @@ def test_every_shape_fits_and_covers_the_work(dtype, Dh):
             units = B * H * (t // l.tile_rows + 1)
             assert 1 <= l.grid <= min(units, SMS * 8)            # no CTA without a unit
             assert l.grid <= SMS * l.ctas_per_sm
+            upb = t // l.tile_rows + 1
+            assert 1 <= l.parts_per_bh <= upb and l.grid <= B * H * l.parts_per_bh   # every CTA owns whole parts
             # the ring really holds stages x (K tile + V tile)
             assert l.smem_bytes >= l.stages * 2 * l.tile_rows * Dh * ES[dtype]
         L.ffa_plan_destroy(p)
@@ -48,10 +50,15 @@ def test_benchmark_configurations_get_the_measured_shapes():
     L, p = offline(capi.BF16, 32, 32, 128, 32768)
     l = launch(L, p, 32767)
     assert (l.tile_rows, l.stages, l.consumer_warps, l.ctas_per_sm, l.grid) == (64, 2, 4, 2, 296)
-    # config 1 (16 MB per step): one CTA per SM
+    assert l.parts_per_bh == 32767 // 64 + 1           # large problem: even cut of the unit list
+    # config 1 (16 MB per step): one CTA per SM, 4 CTAs per (batch, head), boundaries aligned
     L, p = offline(capi.F32, 1, 32, 64, 1000)
     l = launch(L, p, 999)
-    assert l.ctas_per_sm == 1 and l.grid == 148
+    assert (l.ctas_per_sm, l.grid, l.parts_per_bh) == (1, 128, 4)
+    # config 2: a third resident CTA per SM makes room for one CTA per (batch, head)
+    L, p = offline(capi.F16, 10, 32, 64, 1256)
+    l = launch(L, p, 1255)
+    assert (l.ctas_per_sm, l.grid, l.parts_per_bh) == (3, 320, 1)
     # config 3 (GPT-J rows of 512 bytes, 269 MB): 8 compute warps
     L, p = offline(capi.F16, 8, 16, 256, 2048)
     assert launch(L, p, 2047).consumer_warps == 8
@@ -62,11 +69,11 @@ def test_benchmark_configurations_get_the_measured_shapes():
 
 def test_forced_shape_is_respected_and_clamped():
     L, p = offline(capi.F16, 2, 4, 64, 500)
-    f = capi.Launch(16, 3, 2, 4, 5, 0)
+    f = capi.Launch(16, 3, 2, 4, 5, 0, 0)
     capi.check(L.ffa_plan_set_launch(p, C.byref(f)))
     l = launch(L, p, 400)
     assert (l.tile_rows, l.stages, l.consumer_warps, l.ctas_per_sm, l.grid) == (16, 3, 2, 4, 5)
-    f = capi.Launch(100000, 99, 99, 99, 0, 0)        # absurd: clamped until it fits
+    f = capi.Launch(100000, 99, 99, 99, 0, 0, 0)        # absurd: clamped until it fits
     capi.check(L.ffa_plan_set_launch(p, C.byref(f)))
     l = launch(L, p, 400)
     assert l.smem_bytes <= SMEM_CTA and l.consumer_warps == 16 and l.stages >= 2
