@@ -108,6 +108,8 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
     s.cps = 2;
     s.stages = tensors == 2 ? 2 : 3;
     s.tile_rows = 16384 / row_bytes;
+    // head_dim 80 (160- and 320-byte rows): a batch of the row loop is 128 / 64 rows there
+    if ((row_bytes / 16) % 5 == 0) s.tile_rows = 20480 / row_bytes;
     return s;
 }
 
@@ -160,7 +162,7 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
         if (p->force.ctas_per_sm > 0) s.cps = p->force.ctas_per_sm;
     }
     if (s.warps < 1) s.warps = 1;
-    if (s.warps > 16) s.warps = 16;
+    if (s.warps > 8) s.warps = 8;   // the kernels are compiled for at most 1 + 8 warps
     if (s.cps < 1) s.cps = 1;
     if (s.cps > kMaxCtasPerSm) s.cps = kMaxCtasPerSm;
     if (s.stages < 2) s.stages = 2;

@@ -214,8 +214,14 @@ struct RowGeom {
     static constexpr int EPV = Elem<T>::EPV;
     static constexpr int ROWB = DH * (int)sizeof(T);   // bytes per row, multiple of 16
     static constexpr int VPR = ROWB / 16;               // 16-byte vectors per row
-    static constexpr int LPR = VPR >= 32 ? 32 : pow2_ceil(VPR);  // lanes per row group
-    static constexpr int VPL = (VPR + 31) / 32;         // vectors per lane
+    // Lanes per row group and vectors per lane.  Power-of-two rows: one vector per lane up to a
+    // full warp, two per lane for 1024-byte rows.  head_dim 80 (10 or 20 vectors): five vectors
+    // per lane and 2 or 4 lanes per row, so that no lane idles.
+    static constexpr bool kFiveWide = (VPR % 5) == 0;
+    static constexpr int LPR = kFiveWide ? VPR / 5 : (VPR >= 32 ? 32 : VPR);
+    static constexpr int VPL = kFiveWide ? 5 : (VPR + 31) / 32;
+    static constexpr int RB = VPL >= 4 ? 2 : 4;          // rows per lane group and batch (register budget)
+    static_assert(LPR * VPL == VPR && (LPR & (LPR - 1)) == 0, "every lane of a power-of-two group owns VPL vectors");
     static_assert(ROWB % 16 == 0, "rows must be 16-byte multiples");
 };
 
@@ -304,10 +310,12 @@ __device__ __forceinline__ float group_sum(float x)
 // owns a row: 16-byte shared-memory reads, fp32 FMAs, butterfly sum.  Each group keeps its
 // own online-softmax state, so the row loop has no CTA-level synchronisation at all.
 template <typename T, int DH, int PASS>
-__global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams P)
+// Register budget: 4 resident CTAs of 160 threads (or 2 of 288) need <= 96 registers per thread;
+// head_dim 80 keeps five vectors per lane in flight and is compiled for 2 CTAs of 160 threads.
+__global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_stream_kernel(const FfaStepParams P)
 {
     using G = RowGeom<T, DH>;
-    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
     constexpr bool kPrecise = sizeof(T) == 4 || PASS == kPassScore;  // natural-log domain, full-precision exp
     constexpr int TENSORS = PASS == kPassOne ? 2 : 1;
     constexpr float kLog2e = 1.4426950408889634f;
@@ -382,7 +390,7 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
         const int lane = ctid & 31;
         const int g = ctid / LPR, li = ctid % LPR;
         constexpr int E2 = EPV / 2;
-        constexpr bool kAllLanes = (VPR == LPR * VPL);  // false only for head_dim 80
+        constexpr bool kAllLanes = (VPR == LPR * VPL);  // every lane of a group owns VPL vectors
         uint32_t stage = 0, phase = 0;
         long long u = u0;
         // q of the first (batch, head) of this CTA's run; the next one is fetched while the
@@ -449,15 +457,15 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
             };
             auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
 
-            // Four rows per lane group at a time: all shared-memory loads first, then the
+            // RB (four; two for head_dim 80) rows per lane group at a time: all shared-memory loads first, then the
             // packed fp32 FMAs (fma.rn.f32x2), four interleaved butterfly sums, one softmax
             // update.  FULL: every row of the batch exists (no predicates, no clamping).
             auto batch = [&](auto full_tag, const unsigned char* ks, const unsigned char* vs, int base, int nrows, int row0) {
                 constexpr bool FULL = decltype(full_tag)::value;
-                int rc[4];
-                uint4 kraw[4][VPL];
+                int rc[RB];
+                uint4 kraw[RB][VPL];
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
+                for (int uu = 0; uu < RB; ++uu) {
                     const int r = base + uu * NG + g;
                     rc[uu] = FULL ? r : min(r, nrows - 1);
 #pragma unroll
@@ -465,9 +473,9 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                         if (kAllLanes || li + x * LPR < VPR)
                             kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc[uu] * ROWB + (li + x * LPR) * 16);
                 }
-                float sc[4];
+                float sc[RB];
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
+                for (int uu = 0; uu < RB; ++uu) {
                     float2 a = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int x = 0; x < VPL; ++x)
@@ -482,21 +490,26 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
 #pragma unroll
                 for (int off = LPR / 2; off >= 1; off >>= 1)
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu) sc[uu] += __shfl_xor_sync(0xffffffffu, sc[uu], off);
+                    for (int uu = 0; uu < RB; ++uu) sc[uu] += __shfl_xor_sync(0xffffffffu, sc[uu], off);
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) sc[uu] = (FULL || base + uu * NG + g < nrows) ? score_of(sc[uu]) : -CUDART_INF_F;
-                const float m_new = fmaxf(fmaxf(fmaxf(m, sc[0]), fmaxf(sc[1], sc[2])), sc[3]);
+                for (int uu = 0; uu < RB; ++uu) sc[uu] = (FULL || base + uu * NG + g < nrows) ? score_of(sc[uu]) : -CUDART_INF_F;
+                float m_new = m;
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) m_new = fmaxf(m_new, sc[uu]);
                 if (!FULL && m_new == -CUDART_INF_F) return;  // this group has no row in this batch
                 const float corr = expo(m - m_new);
                 m = m_new;
-                float pr[4];
+                float pr[RB];
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) pr[uu] = expo(sc[uu] - m);
-                l = fmaf(l, corr, (pr[0] + pr[1]) + (pr[2] + pr[3]));
+                for (int uu = 0; uu < RB; ++uu) pr[uu] = expo(sc[uu] - m);
+                float psum = 0.f;
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) psum += pr[uu];
+                l = fmaf(l, corr, psum);
                 if (PASS == kPassOne) {
-                    uint4 vraw[4][VPL];
+                    uint4 vraw[RB][VPL];
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu)
+                    for (int uu = 0; uu < RB; ++uu)
 #pragma unroll
                         for (int x = 0; x < VPL; ++x)
                             if (kAllLanes || li + x * LPR < VPR)
@@ -507,7 +520,7 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
 #pragma unroll
                         for (int e = 0; e < E2; ++e) acc2[x][e] = __fmul2_rn(acc2[x][e], c2);
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu) {
+                    for (int uu = 0; uu < RB; ++uu) {
                         const float2 p2 = make_float2(pr[uu], pr[uu]);
 #pragma unroll
                         for (int x = 0; x < VPL; ++x)
@@ -520,7 +533,7 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                     }
                 } else if (li == 0) {
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu)
+                    for (int uu = 0; uu < RB; ++uu)
                         if (FULL || base + uu * NG + g < nrows) P.scores[(size_t)bh * P.Lmax + row0 + base + uu * NG + g] = sc[uu];
                 }
             };
@@ -535,7 +548,7 @@ __global__ void __launch_bounds__(544, 1) ffa_stream_kernel(const FfaStepParams 
                     const unsigned char* vs = ks + tile_bytes;
                     if (ready) {
                         int base = 0;
-                        for (; base + 4 * NG <= nrows; base += 4 * NG) batch(std::true_type{}, ks, vs, base, nrows, lo);
+                        for (; base + RB * NG <= nrows; base += RB * NG) batch(std::true_type{}, ks, vs, base, nrows, lo);
                         if (base < nrows) batch(std::false_type{}, ks, vs, base, nrows, lo);
                     }
                     __syncwarp();
@@ -672,7 +685,7 @@ template <typename T, int DH>
 __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const FfaStepParams P)
 {
     using G = RowGeom<T, DH>;
-    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
     constexpr int NT = kGatherThreads, NG = NT / LPR;
 
     extern __shared__ __align__(128) unsigned char smem[];
@@ -757,11 +770,11 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
             }
             __syncthreads();
             const int n = s_n;
-            for (int base = 0; base < n; base += 4 * NG) {
-                uint4 raw[4][VPL];
-                float pr[4];
+            for (int base = 0; base < n; base += RB * NG) {
+                uint4 raw[RB][VPL];
+                float pr[RB];
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
+                for (int uu = 0; uu < RB; ++uu) {
                     const int idx = base + uu * NG + g;
                     const bool okr = idx < n;
                     pr[uu] = okr ? list_p[idx] : 0.f;
@@ -775,7 +788,7 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
                     }
                 }
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu)
+                for (int uu = 0; uu < RB; ++uu)
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
                         float vf[EPV];
@@ -890,7 +903,7 @@ template <typename T, int DH>
 __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const FfaStepParams P)
 {
     using G = RowGeom<T, DH>;
-    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
     constexpr int NCW = 4, NCT = NCW * 32, NG = NCT / LPR, RS = DH + 4, E2 = EPV / 2;
     constexpr bool kAllLanes = (VPR == LPR * VPL);
 
@@ -966,19 +979,19 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
             const unsigned char* ks = smem + (size_t)stage * tile_bytes;
             float* sc_tile = sc + (lo - c0) + j * R;
             if (ready) {
-                for (int base = 0; base < n; base += 4 * NG) {
-                    uint4 kraw[4][VPL];
+                for (int base = 0; base < n; base += RB * NG) {
+                    uint4 kraw[RB][VPL];
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu) {
+                    for (int uu = 0; uu < RB; ++uu) {
                         const int rc = min(base + uu * NG + g, n - 1);
 #pragma unroll
                         for (int x = 0; x < VPL; ++x)
                             if (kAllLanes || li + x * LPR < VPR)
                                 kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc * ROWB + (li + x * LPR) * 16);
                     }
-                    float s4[4];
+                    float s4[RB];
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu) {
+                    for (int uu = 0; uu < RB; ++uu) {
                         float2 a = make_float2(0.f, 0.f);
 #pragma unroll
                         for (int x = 0; x < VPL; ++x)
@@ -993,16 +1006,21 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
 #pragma unroll
                     for (int off = LPR / 2; off >= 1; off >>= 1)
 #pragma unroll
-                        for (int uu = 0; uu < 4; ++uu) s4[uu] += __shfl_xor_sync(0xffffffffu, s4[uu], off);
+                        for (int uu = 0; uu < RB; ++uu) s4[uu] += __shfl_xor_sync(0xffffffffu, s4[uu], off);
 #pragma unroll
-                    for (int uu = 0; uu < 4; ++uu) {
+                    for (int uu = 0; uu < RB; ++uu) {
                         const int r = base + uu * NG + g;
                         s4[uu] = r < n ? score_of(s4[uu]) : -CUDART_INF_F;
                         if (r < n && li == 0) sc_tile[r] = s4[uu];
                     }
-                    const float m_new = fmaxf(fmaxf(fmaxf(m, s4[0]), fmaxf(s4[1], s4[2])), s4[3]);
+                    float m_new = m;
+#pragma unroll
+                    for (int uu = 0; uu < RB; ++uu) m_new = fmaxf(m_new, s4[uu]);
                     if (m_new != -CUDART_INF_F) {
-                        l = l * expf(m - m_new) + ((expf(s4[0] - m_new) + expf(s4[1] - m_new)) + (expf(s4[2] - m_new) + expf(s4[3] - m_new)));
+                        float psum = 0.f;
+#pragma unroll
+                        for (int uu = 0; uu < RB; ++uu) psum += expf(s4[uu] - m_new);
+                        l = l * expf(m - m_new) + psum;
                         m = m_new;
                     }
                 }
@@ -1119,11 +1137,11 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
         __syncthreads();
         const int n = flags[1];
         if (warp > 0) {
-            for (int base = 0; base < n; base += 4 * NG) {
-                uint4 raw[4][VPL];
-                float pr[4];
+            for (int base = 0; base < n; base += RB * NG) {
+                uint4 raw[RB][VPL];
+                float pr[RB];
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
+                for (int uu = 0; uu < RB; ++uu) {
                     const int idx = base + uu * NG + g;
                     const bool okr = idx < n;
                     pr[uu] = okr ? list_p[idx] : 0.f;
@@ -1136,7 +1154,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
                     }
                 }
 #pragma unroll
-                for (int uu = 0; uu < 4; ++uu) {
+                for (int uu = 0; uu < RB; ++uu) {
                     const float2 p2 = make_float2(pr[uu], pr[uu]);
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
@@ -1270,14 +1288,19 @@ int dispatch(int dtype, int head_dim, F&& f)
 }
 
 int elem_size(int dtype) { return dtype == 0 ? 4 : 2; }
+// lanes per row group, as RowGeom computes it
+int lanes_per_row(int rowb)
+{
+    const int vpr = rowb / 16;
+    return vpr % 5 == 0 ? vpr / 5 : (vpr >= 32 ? 32 : vpr);
+}
 
 }  // namespace
 
 int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage)
 {
     const int rowb = head_dim * elem_size(dtype);
-    const int vpr = rowb / 16;
-    const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
+    const int lpr = lanes_per_row(rowb);
     const int ng = consumer_warps * 32 / lpr;
     return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16;
 }
@@ -1285,16 +1308,14 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
 int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows)
 {
     const int rowb = head_dim * elem_size(dtype);
-    const int vpr = rowb / 16;
-    const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
+    const int lpr = lanes_per_row(rowb);
     return tile_rows * 8 + (kGatherThreads / lpr) * head_dim * 4;
 }
 
 int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows)
 {
     const int rowb = head_dim * elem_size(dtype);
-    const int vpr = rowb / 16;
-    const int lpr = vpr >= 32 ? 32 : pow2_ceil(vpr);
+    const int lpr = lanes_per_row(rowb);
     const int ng = 128 / lpr;
     return stages * tile_rows * rowb + chunk_rows * 4 + kFusedListCap * 8 + kFusedListCap / 32 * 4 + ng * (head_dim + 4) * 4 + head_dim * 4 + 16 +
            2 * stages * 8 + 16;

@@ -103,7 +103,7 @@ extern "C" int ffa_attention_static_scratch(int dtype, int batch, int heads, int
     // ---- launch shape: the engine's fixed rule (16 KB tiles, 4 compute warps, 2 CTAs/SM, 2 stages) ----
     const int es = dtype == FFA_DTYPE_F32 ? 4 : 2, rowb = head_dim * es;
     const long long BH = (long long)batch * heads;
-    int tile_rows = 16384 / rowb, stages = 2, cps = 2;
+    int tile_rows = ((rowb / 16) % 5 == 0 ? 20480 : 16384) / rowb, stages = 2, cps = 2;
     const int warps = 4;
     tile_rows = (tile_rows + 7) / 8 * 8;
     while (tile_rows > 8 && BH * (t / tile_rows + 1) < 4LL * st.sms * cps) tile_rows = (tile_rows / 2 + 7) / 8 * 8;

@@ -58,7 +58,7 @@ typedef struct ffa_plan ffa_plan_t;
 typedef struct ffa_launch {
     int tile_rows;      /* cache rows per pipeline stage (K rows and V rows each) */
     int stages;         /* depth of the shared-memory ring */
-    int consumer_warps; /* compute warps per CTA (one more warp issues the bulk copies) */
+    int consumer_warps; /* compute warps per CTA, 1..8 (one more warp issues the bulk copies) */
     int ctas_per_sm;    /* resident CTAs per SM the grid is sized for */
     int grid;           /* number of CTAs; the work list is cut into this many contiguous runs */
     int smem_bytes;     /* dynamic shared memory per CTA */

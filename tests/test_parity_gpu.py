@@ -236,7 +236,7 @@ def qkv(g, B, H, Dh, dt):
 @pytest.mark.parametrize("shape", [dict(tile_rows=8, stages=2, consumer_warps=1, grid=1),
                                    dict(tile_rows=16, stages=3, consumer_warps=4),
                                    dict(tile_rows=64, stages=2, consumer_warps=8, ctas_per_sm=1),
-                                   dict(tile_rows=8, stages=5, consumer_warps=16, ctas_per_sm=4)])
+                                   dict(tile_rows=8, stages=5, consumer_warps=7, ctas_per_sm=4)])
 def test_tile_edges_and_forced_shapes(dt, Dh, shape):
     B, H = 2, 3
     R = shape["tile_rows"]

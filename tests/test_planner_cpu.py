@@ -33,7 +33,7 @@ def test_every_shape_fits_and_covers_the_work(dtype, Dh):
                 continue
             l = launch(L, p, t)
             assert l.tile_rows % 8 == 0 and l.tile_rows >= 8
-            assert 2 <= l.stages <= 16 and 1 <= l.consumer_warps <= 16
+            assert 2 <= l.stages <= 16 and 1 <= l.consumer_warps <= 8
             assert l.smem_bytes <= SMEM_CTA and l.ctas_per_sm * (l.smem_bytes + 1024) <= SMEM_SM
             units = B * H * (t // l.tile_rows + 1)
             assert 1 <= l.grid <= min(units, SMS * 8)            # no CTA without a unit
@@ -76,7 +76,7 @@ def test_forced_shape_is_respected_and_clamped():
     f = capi.Launch(100000, 99, 99, 99, 0, 0, 0)        # absurd: clamped until it fits
     capi.check(L.ffa_plan_set_launch(p, C.byref(f)))
     l = launch(L, p, 400)
-    assert l.smem_bytes <= SMEM_CTA and l.consumer_warps == 16 and l.stages >= 2
+    assert l.smem_bytes <= SMEM_CTA and l.consumer_warps == 8 and l.stages >= 2
     capi.check(L.ffa_plan_set_launch(p, None))
     assert launch(L, p, 400).consumer_warps == 4
 
