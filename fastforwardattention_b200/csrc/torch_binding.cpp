@@ -57,6 +57,9 @@ struct FastForwardAttn {
                              v_cache.data_ptr(), stream.stream()),
               "cache init");
         bind_workspace(false);
+        // one-time: the caches and the cleared workspace are complete before the constructor
+        // returns, so the first step may run on any stream
+        stream.synchronize();
     }
     ~FastForwardAttn() { ffa_plan_destroy(plan); }
     FastForwardAttn(const FastForwardAttn&) = delete;
