@@ -21,6 +21,7 @@
 // any stream capture.  Nothing here calls cudaMalloc, cudaFree or any allocating routine.
 #include <cuda_runtime.h>
 
+#include <cstdarg>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -45,6 +46,18 @@ struct DeviceState {
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
 
+// writes the reason for a non-zero return into the caller's (host) buffer, if one was given
+int report(char* buf, size_t len, int code, const char* fmt, ...)
+{
+    if (buf != nullptr && len > 0) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, len, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
 int head_dim_index(int d) { return d == 64 ? 0 : d == 80 ? 1 : d == 128 ? 2 : d == 256 ? 3 : -1; }
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -55,11 +68,7 @@ extern "C" int ffa_attention_static_scratch(int dtype, int batch, int heads, int
                                             float softmax_scale, int t, int* device_status, void* stream,
                                             char* error_text, size_t error_text_len)
 {
-    // the reason for a non-zero return goes into the caller's (host) buffer, if one was given
-    auto fail = [&](int code, const char* fmt, auto... a) {
-        if (error_text != nullptr && error_text_len > 0) snprintf(error_text, error_text_len, fmt, a...);
-        return code;
-    };
+    auto fail = [&](int code, const char* fmt, auto... a) { return report(error_text, error_text_len, code, fmt, a...); };
     if (error_text != nullptr && error_text_len > 0) error_text[0] = 0;
     if (dtype != FFA_DTYPE_F32 && dtype != FFA_DTYPE_F16 && dtype != FFA_DTYPE_BF16) return fail(FFA_ERR_DTYPE, "unsupported dtype code %d", dtype);
     const int dhi = head_dim_index(head_dim);
