@@ -240,37 +240,34 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
 
 // Fused pruning kernel: a cluster of C CTAs per (batch, head), C in {1, 2, 4, 8}; each CTA keeps
 // the scores of its slice (chunk rows, a multiple of 32 so mask words never straddle slices) in
-// shared memory.  The kernel has a score phase and a value phase separated by a cluster
-// barrier, so a second wave of CTAs costs a whole extra latency chain: take the largest C whose
-// B*H*C CTAs are all resident at once (slices of at least 128 rows); when even C = 1 needs
-// several waves, the smallest C that fits in shared memory.  False when 8 slices do not fit
-// (then the two-kernel path runs).
+// shared memory.  The kernel is a score phase and a value phase separated by cluster barriers,
+// and the grid is not persistent, so the time is (number of waves) x (one CTA's chain): C is
+// the candidate with the smallest  ceil(B*H*C / resident CTAs) x (chunk + fixed cost), the
+// fixed cost of a CTA (start, barriers, merge) taken as 512 rows' worth.  Slices stay >= 128
+// rows.  False when 8 slices do not fit in shared memory (then the two-kernel path runs).
 bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out)
 {
     const int rowb = p->Dh * elem_size(p->dtype);
     const long long BH = (long long)p->B * p->H;
-    int best_c = 0, best_chunk = 0, best_r = 0, best_smem = 0, best_resident = 0;
-    bool have_single_wave = false;
+    int best_c = 0, best_chunk = 0, best_r = 0, best_smem = 0;
+    long long best_cost = 0;
     for (int c = 1; c <= 8; c *= 2) {
         const int chunk = (int)(((long long)cap_rows + 1 + c - 1) / c + 31) / 32 * 32;
         if (c > 1 && chunk < 128) break;
-        int r = 8192 / rowb / 8 * 8;
+        int r = (((rowb / 16) % 5 == 0 ? 20480 : 16384) / rowb) / 8 * 8;   // one 16 KB K tile (20 KB for head_dim 80)
         if (r < 8) r = 8;
         if (r > chunk) r = (chunk + 7) / 8 * 8;
-        const int smem = ffa_k_fused_smem_bytes(p->dtype, p->Dh, r, 3, chunk);
+        const int smem = ffa_k_fused_smem_bytes(p->dtype, p->Dh, r, 2, chunk);
         if (smem > p->smem_per_cta) continue;
         int resident = p->smem_per_sm / (smem + kSmemReservePerCta);
-        if (resident > 7) resident = 7;  // 160 threads x 56 registers
-        const bool single_wave = BH * c <= (long long)p->sms * resident;
-        // single wave: the more slices the better; several waves: stop slicing once three CTAs
-        // per SM can overlap one another's phases
-        const bool take = single_wave || (!have_single_wave && (best_c == 0 || best_resident < 3));
-        if (take) best_c = c, best_chunk = chunk, best_r = r, best_smem = smem, best_resident = resident;
-        have_single_wave = have_single_wave || single_wave;
-        if (have_single_wave && !single_wave) break;
+        if (resident > 7) resident = 7;  // 160 threads x <= 72 registers
+        const long long slots = (long long)p->sms * resident;
+        const long long waves = (BH * c + slots - 1) / slots;
+        const long long cost = waves * (chunk + 512);
+        if (best_c == 0 || cost < best_cost) best_c = c, best_chunk = chunk, best_r = r, best_smem = smem, best_cost = cost;
     }
     if (best_c == 0) return false;
-    P->cluster = best_c, P->chunk_rows = best_chunk, P->tile_rows = best_r, P->stages = 3;
+    P->cluster = best_c, P->chunk_rows = best_chunk, P->tile_rows = best_r, P->stages = 2;
     P->grid = (int)(BH * best_c);
     *smem_out = best_smem;
     return true;

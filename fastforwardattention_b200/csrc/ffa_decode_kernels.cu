@@ -201,13 +201,6 @@ struct Elem<__nv_bfloat16> {
     static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
 };
 
-constexpr int pow2_ceil(int x)
-{
-    int p = 1;
-    while (p < x) p <<= 1;
-    return p;
-}
-
 // Geometry of one cache row of DH elements of T, and of the lane group that owns a row.
 template <typename T, int DH>
 struct RowGeom {
@@ -455,7 +448,8 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 if (PASS == kPassScore && P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
                 return dot * P.scale;
             };
-            auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
+            // the score pass only feeds the softmax denominator: __expf, like the reference (attention.cu:1113)
+            auto expo = [&](float x) -> float { return PASS == kPassScore ? __expf(x) : (kPrecise ? expf(x) : fast_exp2(x)); };
 
             // RB (four; two for head_dim 80) rows per lane group at a time: all shared-memory loads first, then the
             // packed fp32 FMAs (fma.rn.f32x2), four interleaved butterfly sums, one softmax
@@ -979,51 +973,55 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
             const unsigned char* ks = smem + (size_t)stage * tile_bytes;
             float* sc_tile = sc + (lo - c0) + j * R;
             if (ready) {
-                for (int base = 0; base < n; base += RB * NG) {
+                // RB rows per lane group at a time, loads first; FULL: every row of the batch exists
+                auto batch = [&](auto full_tag, int base) {
+                    constexpr bool FULL = decltype(full_tag)::value;
                     uint4 kraw[RB][VPL];
 #pragma unroll
                     for (int uu = 0; uu < RB; ++uu) {
-                        const int rc = min(base + uu * NG + g, n - 1);
+                        const int r = base + uu * NG + g;
+                        const int rc = FULL ? r : min(r, n - 1);
 #pragma unroll
                         for (int x = 0; x < VPL; ++x)
-                            if (kAllLanes || li + x * LPR < VPR)
-                                kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc * ROWB + (li + x * LPR) * 16);
+                            kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc * ROWB + (li + x * LPR) * 16);
                     }
                     float s4[RB];
 #pragma unroll
                     for (int uu = 0; uu < RB; ++uu) {
                         float2 a = make_float2(0.f, 0.f);
 #pragma unroll
-                        for (int x = 0; x < VPL; ++x)
-                            if (kAllLanes || li + x * LPR < VPR) {
-                                float2 k2[E2];
-                                Elem<T>::unpack2(kraw[uu][x], k2);
+                        for (int x = 0; x < VPL; ++x) {
+                            float2 k2[E2];
+                            Elem<T>::unpack2(kraw[uu][x], k2);
 #pragma unroll
-                                for (int e = 0; e < E2; ++e) a = __ffma2_rn(q2[x][e], k2[e], a);
-                            }
+                            for (int e = 0; e < E2; ++e) a = __ffma2_rn(q2[x][e], k2[e], a);
+                        }
                         s4[uu] = a.x + a.y;
                     }
 #pragma unroll
                     for (int off = LPR / 2; off >= 1; off >>= 1)
 #pragma unroll
                         for (int uu = 0; uu < RB; ++uu) s4[uu] += __shfl_xor_sync(0xffffffffu, s4[uu], off);
+                    float m_new = m;
 #pragma unroll
                     for (int uu = 0; uu < RB; ++uu) {
                         const int r = base + uu * NG + g;
-                        s4[uu] = r < n ? score_of(s4[uu]) : -CUDART_INF_F;
-                        if (r < n && li == 0) sc_tile[r] = s4[uu];
+                        const bool okr = FULL || r < n;
+                        s4[uu] = okr ? score_of(s4[uu]) : -CUDART_INF_F;
+                        if (okr && li == 0) sc_tile[r] = s4[uu];
+                        m_new = fmaxf(m_new, s4[uu]);
                     }
-                    float m_new = m;
-#pragma unroll
-                    for (int uu = 0; uu < RB; ++uu) m_new = fmaxf(m_new, s4[uu]);
-                    if (m_new != -CUDART_INF_F) {
+                    if (FULL || m_new != -CUDART_INF_F) {
                         float psum = 0.f;
 #pragma unroll
-                        for (int uu = 0; uu < RB; ++uu) psum += expf(s4[uu] - m_new);
-                        l = l * expf(m - m_new) + psum;
+                        for (int uu = 0; uu < RB; ++uu) psum += __expf(s4[uu] - m_new);   // as attention.cu:1113
+                        l = l * __expf(m - m_new) + psum;
                         m = m_new;
                     }
-                }
+                };
+                int base = 0;
+                for (; base + RB * NG <= n; base += RB * NG) batch(std::true_type{}, base);
+                if (base < n) batch(std::false_type{}, base);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
@@ -1042,7 +1040,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
             if (g == 0) {
                 const float st = score_of(dot);
                 const float m_new = fmaxf(m, st);
-                l = l * expf(m - m_new) + expf(st - m_new);
+                l = l * __expf(m - m_new) + __expf(st - m_new);
                 m = m_new;
                 if (li == 0) sc[sr.row - c0] = st;
                 const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
@@ -1062,7 +1060,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
         float Mc = -CUDART_INF_F, Lc = 0.f;
         for (int gg = 0; gg < NG; ++gg) Mc = fmaxf(Mc, red[gg * RS]);
         for (int gg = 0; gg < NG; ++gg)
-            if (red[gg * RS] != -CUDART_INF_F) Lc += red[gg * RS + 1] * expf(red[gg * RS] - Mc);
+            if (red[gg * RS] != -CUDART_INF_F) Lc += red[gg * RS + 1] * __expf(red[gg * RS] - Mc);
         stat[0] = Mc, stat[1] = Lc;
     }
     cluster_sync_all();   // every slice's (max, sum) is visible cluster-wide; also a CTA barrier
@@ -1072,7 +1070,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     for (int c = 0; c < C; ++c) M = fmaxf(M, ld_peer_smem_f32(stat, c));
     for (int c = 0; c < C; ++c) {
         const float mc = ld_peer_smem_f32(stat, c);
-        if (mc != -CUDART_INF_F) Lsum += ld_peer_smem_f32(stat + 1, c) * expf(mc - M);
+        if (mc != -CUDART_INF_F) Lsum += ld_peer_smem_f32(stat + 1, c) * __expf(mc - M);
     }
     // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
     // the torch-rounding mode divides exactly like torch's softmax does
