@@ -1,0 +1,54 @@
+"""A decode step recorded once in a CUDA graph and replayed for every token.
+
+The per-call host work of `FastForwardAttn.attention` (argument checks, planning, launch)
+is a few microseconds -- more than the kernel itself on small configurations.  The row
+index can live in device memory (`attention_per_sample`), which makes the launch parameters
+of a step independent of the token position, so the step can be captured once:
+
+    step = GraphedStep(ffa, softmax_scale, first_row=prompt_len)
+    for token in range(n):
+        out = step(q, k, v)          # [B, H, Dh]; a view of a static buffer, valid until the next call
+
+The graph holds: the attention launch on the engine's own caches and the increment of the
+row counter.  q, k and v are copied into static buffers before every replay.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class GraphedStep:
+    def __init__(self, ffa, softmax_scale: float, first_row: int, prob_thresh: float = 0.0):
+        kc, _ = ffa.get_cache()
+        B, H, Lmax, Dh = kc.shape
+        if not 0 <= first_row < Lmax:
+            raise ValueError(f"first_row {first_row} outside [0, {Lmax})")
+        self.ffa, self.max_len = ffa, Lmax
+        dev, dt = kc.device, kc.dtype
+        self.q = torch.zeros(B, H, 1, Dh, dtype=dt, device=dev)
+        self.k = torch.zeros_like(self.q)
+        self.v = torch.zeros_like(self.q)
+        self.out = torch.zeros(B, H, Dh, dtype=dt, device=dev)
+        self.rows = torch.full((B,), first_row, dtype=torch.int32, device=dev)
+        self.next_row = first_row
+        # warm-up on a side stream (lazy initialisation must not happen inside the capture);
+        # it writes row `first_row` with zeros, which the first real step overwrites
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            ffa.attention_per_sample(self.q, self.k, self.v, softmax_scale, self.rows, prob_thresh, out=self.out)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            ffa.attention_per_sample(self.q, self.k, self.v, softmax_scale, self.rows, prob_thresh, out=self.out)
+            self.rows.add_(1)
+
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        if self.next_row >= self.max_len:
+            raise RuntimeError(f"the cache is full ({self.max_len} rows)")
+        self.q.copy_(q.view_as(self.q), non_blocking=True)
+        self.k.copy_(k.view_as(self.k), non_blocking=True)
+        self.v.copy_(v.view_as(self.v), non_blocking=True)
+        self.graph.replay()
+        self.next_row += 1
+        return self.out

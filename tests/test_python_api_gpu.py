@@ -157,3 +157,24 @@ def test_cuda_graph_replay_with_device_side_step(dt):
     assert int(rows[0]) == Lp + n and ffa.device_status() == 0
     kc, _ = ffa.get_cache()
     assert torch.equal(kc[:, :, Lp + n - 1].cpu(), k[:, :, 0])
+
+
+def test_graphed_step_helper():
+    from fastforwardattention_b200 import FastForwardAttn, GraphedStep
+
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(12)
+    B, H, Dh, Lp, n = 2, 4, 128, 90, 5
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    ffa = FastForwardAttn(K.cuda(), V.cuda(), Lp + n, False)
+    step = GraphedStep(ffa, Dh ** -0.5, first_row=Lp)
+    orc = O.DecodeOracle(K, V, Lp + n, compute_dtype=torch.float64)
+    for i in range(n):
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        out = step(q.cuda(), k.cuda(), v.cuda())
+        ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
+        assert (out.cpu().double() - ref).abs().max().item() <= 8e-3
+    with pytest.raises(RuntimeError, match="full"):
+        step(q.cuda(), k.cuda(), v.cuda())
+    assert ffa.device_status() == 0
