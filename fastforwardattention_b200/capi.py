@@ -16,7 +16,7 @@ MODE_EXACT, MODE_ROUND_LIKE_TORCH = 0, 1
 SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_destroy", "ffa_plan_get_launch",
            "ffa_plan_set_launch", "ffa_plan_set_mode", "ffa_workspace_bytes", "ffa_workspace_bind", "ffa_attention",
            "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
-           "ffa_plan_get_prune_launch"]
+           "ffa_plan_get_prune_launch", "ffa_cache_copy"]
 
 
 class Launch(C.Structure):
@@ -42,6 +42,7 @@ def lib() -> C.CDLL:
         vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
         L.ffa_cache_bytes.argtypes = [i, i, i, i, i, C.POINTER(sz), C.POINTER(sz)]
         L.ffa_cache_init.argtypes = [i, i, i, i, i, i, vp, vp, vp, vp, vp]
+        L.ffa_cache_copy.argtypes = [i, i, i, i, i, i, i, vp, vp, vp, vp, vp]
         L.ffa_plan_create.argtypes = [i, i, i, i, i, i, i, C.POINTER(vp)]
         L.ffa_plan_create_offline.argtypes = [i, i, i, i, i, i, i, i, i, C.POINTER(vp)]
         L.ffa_plan_get_prune_launch.argtypes = [vp, i] + [C.POINTER(i)] * 5

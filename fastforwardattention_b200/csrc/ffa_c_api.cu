@@ -298,26 +298,34 @@ int ffa_cache_bytes(int dtype, int batch, int heads, int max_len, int head_dim, 
     return FFA_OK;
 }
 
-int ffa_cache_init(int dtype, int batch, int heads, int prompt_len, int max_len, int head_dim, const void* k_src,
-                   const void* v_src, void* k_cache, void* v_cache, void* stream)
+int ffa_cache_copy(int dtype, int batch, int heads, int rows, int src_max_len, int dst_max_len, int head_dim,
+                   const void* k_src, const void* v_src, void* k_dst, void* v_dst, void* stream)
 {
     if (!dtype_ok(dtype)) return fail(FFA_ERR_DTYPE, "unsupported dtype code %d", dtype);
     if (!head_dim_ok(head_dim)) return fail(FFA_ERR_HEAD_DIM, "unsupported head_dim %d (64, 80, 128, 256)", head_dim);
-    if (batch <= 0 || heads <= 0 || max_len <= 0 || prompt_len < 0 || prompt_len > max_len)
-        return fail(FFA_ERR_RANGE, "need 0 <= prompt_len (%d) <= max_len (%d) and positive batch, heads", prompt_len, max_len);
-    if (prompt_len == 0) return FFA_OK;
-    if (!k_src || !v_src || !k_cache || !v_cache) return fail(FFA_ERR_ARG, "null pointer");
-    if (!aligned16(k_src) || !aligned16(v_src) || !aligned16(k_cache) || !aligned16(v_cache))
+    if (batch <= 0 || heads <= 0 || dst_max_len <= 0 || rows < 0 || rows > dst_max_len || rows > src_max_len)
+        return fail(FFA_ERR_RANGE, "need 0 <= rows (%d) <= source length (%d) and destination length (%d), positive batch, heads",
+                    rows, src_max_len, dst_max_len);
+    if (rows == 0) return FFA_OK;
+    if (!k_src || !v_src || !k_dst || !v_dst) return fail(FFA_ERR_ARG, "null pointer");
+    if (!aligned16(k_src) || !aligned16(v_src) || !aligned16(k_dst) || !aligned16(v_dst))
         return fail(FFA_ERR_ARG, "pointers must be 16-byte aligned");
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return cuda_fail(e, "device query");
-    const int r = ffa_k_cache_init(dtype, batch * heads, prompt_len, max_len, head_dim, k_src, v_src, k_cache, v_cache, sms,
+    const int r = ffa_k_cache_init(dtype, batch * heads, rows, src_max_len, dst_max_len, head_dim, k_src, v_src, k_dst, v_dst, sms,
                                    static_cast<cudaStream_t>(stream));
-    if (r != 0) return cuda_fail(r, "cache init launch");
+    if (r != 0) return cuda_fail(r, "cache copy launch");
     g_launches.fetch_add(1);
     return FFA_OK;
+}
+
+int ffa_cache_init(int dtype, int batch, int heads, int prompt_len, int max_len, int head_dim, const void* k_src,
+                   const void* v_src, void* k_cache, void* v_cache, void* stream)
+{
+    if (prompt_len > max_len) return fail(FFA_ERR_RANGE, "need 0 <= prompt_len (%d) <= max_len (%d)", prompt_len, max_len);
+    return ffa_cache_copy(dtype, batch, heads, prompt_len, prompt_len, max_len, head_dim, k_src, v_src, k_cache, v_cache, stream);
 }
 
 int ffa_plan_create(int dtype, int batch, int heads, int head_dim, int max_len, int use_default_launch, int device,

@@ -1220,18 +1220,20 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
 }
 
 // ------------------------------------------------------------------------------------------
-// Cache build: prompt [BH, Lp, Dh] -> rows [0, Lp) of [BH, Lmax, Dh], K and V in one launch
+// Cache build: rows [0, Lp) of [BH, Lsrc, Dh] -> rows [0, Lp) of [BH, Lmax, Dh], K and V in one launch
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) ffa_cache_init_kernel(const uint4* __restrict__ k_src, const uint4* __restrict__ v_src,
                                                               uint4* __restrict__ k_dst, uint4* __restrict__ v_dst,
-                                                              long long src_vecs_per_bh, long long dst_vecs_per_bh,
-                                                              long long total_vecs)
+                                                              long long copy_vecs_per_bh, long long src_vecs_per_bh,
+                                                              long long dst_vecs_per_bh, long long total_vecs)
 {
+    // copies the first copy_vecs_per_bh vectors of every (batch, head) from a source whose pairs
+    // are src_vecs_per_bh apart to a destination whose pairs are dst_vecs_per_bh apart
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs; i += stride) {
-        const long long bh = i / src_vecs_per_bh, r = i - bh * src_vecs_per_bh;
-        const long long o = bh * dst_vecs_per_bh + r;
-        const uint4 kk = __ldcs(k_src + i), vv = __ldcs(v_src + i);
+        const long long bh = i / copy_vecs_per_bh, r = i - bh * copy_vecs_per_bh;
+        const long long o = bh * dst_vecs_per_bh + r, si = bh * src_vecs_per_bh + r;
+        const uint4 kk = __ldcs(k_src + si), vv = __ldcs(v_src + si);
         k_dst[o] = kk;
         v_dst[o] = vv;
     }
@@ -1342,18 +1344,18 @@ int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes)
     });
 }
 
-int ffa_k_cache_init(int dtype, int BH, int prompt_len, int max_len, int head_dim, const void* k_src, const void* v_src,
-                     void* k_cache, void* v_cache, int sms, cudaStream_t stream)
+int ffa_k_cache_init(int dtype, int BH, int prompt_len, int src_len, int max_len, int head_dim, const void* k_src,
+                     const void* v_src, void* k_cache, void* v_cache, int sms, cudaStream_t stream)
 {
     const long long rowv = (long long)head_dim * elem_size(dtype) / 16;
-    const long long src_per = rowv * prompt_len, dst_per = rowv * max_len, total = src_per * BH;
+    const long long copy_per = rowv * prompt_len, src_per = rowv * src_len, dst_per = rowv * max_len, total = copy_per * BH;
     if (total == 0) return 0;
     long long blocks = (total + 255) / 256;
     const long long cap = (long long)sms * 16;
     if (blocks > cap) blocks = cap;
     ffa_cache_init_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(k_src), static_cast<const uint4*>(v_src),
                                                                 static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
-                                                                src_per, dst_per, total);
+                                                                copy_per, src_per, dst_per, total);
     return (int)cudaGetLastError();
 }
 

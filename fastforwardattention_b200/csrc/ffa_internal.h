@@ -35,8 +35,8 @@ struct FfaStepParams {
 
 // dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.
 int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes);
-int ffa_k_cache_init(int dtype, int BH, int prompt_len, int max_len, int head_dim, const void* k_src, const void* v_src,
-                     void* k_cache, void* v_cache, int sms, cudaStream_t stream);
+int ffa_k_cache_init(int dtype, int BH, int prompt_len, int src_len, int max_len, int head_dim, const void* k_src,
+                     const void* v_src, void* k_cache, void* v_cache, int sms, cudaStream_t stream);
 // p == 0, exact mode: one launch.
 int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int threads, int smem, cudaStream_t stream);
 // p > 0 or round-like-torch: score pass then value pass, two launches.

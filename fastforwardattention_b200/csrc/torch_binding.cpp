@@ -15,6 +15,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <memory>
 #include <utility>
 
 #include "ffa_c_api.h"
@@ -48,6 +49,7 @@ struct FastForwardAttn {
         dtype = dtype_code(K);
         c10::cuda::CUDAGuard guard(K.device());
         device = K.device();
+        use_default = use_default_kernel_launch;
         check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)Lmax, use_default_kernel_launch, K.device().index(), &plan),
               "plan");
         k_cache = torch::empty({B, H, Lmax, Dh}, K.options());
@@ -61,6 +63,52 @@ struct FastForwardAttn {
         // returns, so the first step may run on any stream
         stream.synchronize();
     }
+    // Adopts caches the caller already filled (a prefill that writes K and V straight into
+    // [batch, heads, max_len, head_dim] slabs needs no copy at all): rows [0, t) are whatever the
+    // caller put there.  Replaces the copy in init_attention_cache (torch_ffa_api.cpp:68-77, 88-97).
+    struct AdoptTag {};
+    FastForwardAttn(AdoptTag, torch::Tensor kc, torch::Tensor vc, bool use_default_kernel_launch)
+    {
+        TORCH_CHECK(kc.is_cuda() && vc.is_cuda() && kc.dim() == 4 && vc.sizes() == kc.sizes() && kc.scalar_type() == vc.scalar_type() &&
+                        kc.device() == vc.device() && kc.is_contiguous() && vc.is_contiguous(),
+                    "FastForwardAttn.adopt: caches must be two contiguous CUDA tensors [batch, heads, max_len, head_dim] of one dtype");
+        B = kc.size(0), H = kc.size(1), Lmax = kc.size(2), Dh = kc.size(3);
+        TORCH_CHECK(Lmax > 0 && Lmax < (int64_t(1) << 31) && B * H < (int64_t(1) << 31), "FastForwardAttn.adopt: sizes out of range");
+        dtype = dtype_code(kc);
+        c10::cuda::CUDAGuard guard(kc.device());
+        device = kc.device();
+        use_default = use_default_kernel_launch;
+        check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)Lmax, use_default, device.index(), &plan), "plan");
+        k_cache = kc, v_cache = vc;
+        bind_workspace(false);
+        at::cuda::getCurrentCUDAStream().synchronize();
+    }
+
+    // Grows both caches to new_max_len rows (contents kept), re-plans and re-binds the workspace.
+    // Tensors handed out by get_cache() before the call keep pointing at the old slabs.
+    void grow(int64_t new_max_len)
+    {
+        TORCH_CHECK(new_max_len > Lmax && new_max_len < (int64_t(1) << 31), "FastForwardAttn.grow: new length ", new_max_len,
+                    " must exceed the current ", Lmax);
+        c10::cuda::CUDAGuard guard(device);
+        auto stream = at::cuda::getCurrentCUDAStream();
+        torch::Tensor nk = torch::empty({B, H, new_max_len, Dh}, k_cache.options());
+        torch::Tensor nv = torch::empty({B, H, new_max_len, Dh}, k_cache.options());
+        check(ffa_cache_copy(dtype, (int)B, (int)H, (int)Lmax, (int)Lmax, (int)new_max_len, (int)Dh, k_cache.data_ptr(),
+                             v_cache.data_ptr(), nk.data_ptr(), nv.data_ptr(), stream.stream()),
+              "cache copy");
+        ffa_plan_t* np = nullptr;
+        check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)new_max_len, use_default, device.index(), &np), "plan");
+        check(ffa_plan_set_mode(np, mode), "mode");
+        stream.synchronize();   // the old slabs may be freed once the copy is done
+        ffa_plan_destroy(plan);
+        plan = np, k_cache = nk, v_cache = nv, Lmax = new_max_len;
+        kept_mask = torch::Tensor();
+        bind_workspace(false);
+        stream.synchronize();
+    }
+    int64_t max_len() const { return Lmax; }
+
     ~FastForwardAttn() { ffa_plan_destroy(plan); }
     FastForwardAttn(const FastForwardAttn&) = delete;
     FastForwardAttn& operator=(const FastForwardAttn&) = delete;
@@ -199,7 +247,7 @@ struct FastForwardAttn {
     c10::Device device{c10::kCUDA, 0};
     int64_t B = 0, H = 0, Dh = 0, Lmax = 0;
     int dtype = 0, mode = FFA_MODE_EXACT;
-    bool has_scores = false, want_mask = false;
+    bool has_scores = false, want_mask = false, use_default = false;
 };
 
 }  // namespace
@@ -211,6 +259,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     py::class_<FastForwardAttn>(m, "FastForwardAttn")
         .def(py::init<torch::Tensor, torch::Tensor, int64_t, bool>(), py::arg("K"), py::arg("V"), py::arg("max_timesteps"),
              py::arg("use_default_kernel_launch") = false)
+        .def_static("adopt", [](torch::Tensor kc, torch::Tensor vc, bool use_default_kernel_launch) {
+                        return std::make_unique<FastForwardAttn>(FastForwardAttn::AdoptTag{}, kc, vc, use_default_kernel_launch);
+                    }, py::arg("k_cache"), py::arg("v_cache"), py::arg("use_default_kernel_launch") = false,
+                    "engine over caches [batch, heads, max_len, head_dim] the caller has already filled (no copy)")
+        .def("grow", &FastForwardAttn::grow, py::arg("new_max_len"), "reallocate both caches to a longer max_len, contents kept")
+        .def_property_readonly("max_len", &FastForwardAttn::max_len)
         .def("get_cache", &FastForwardAttn::get_cache, "the live (k_cache, v_cache) tensors, [batch, heads, max_len, head_dim]")
         .def("attention", &FastForwardAttn::attention, "decode step on the engine's own caches", py::arg("q"), py::arg("k"),
              py::arg("v"), py::arg("softmax_scale"), py::arg("curr_timestep"), py::arg("prob_thresh") = 0.0,

@@ -77,6 +77,13 @@ int ffa_cache_bytes(int dtype, int batch, int heads, int max_len, int head_dim, 
 int ffa_cache_init(int dtype, int batch, int heads, int prompt_len, int max_len, int head_dim,
                    const void* k_src, const void* v_src, void* k_cache, void* v_cache, void* stream);
 
+/* Copies rows [0, rows) of every (batch, head) between two cache slabs of different lengths
+ * ([batch, heads, src_max_len, head_dim] -> [batch, heads, dst_max_len, head_dim]): how a cache
+ * grows.  No counterpart in the reference, whose cache length is fixed at construction
+ * (torch_ffa_api.cpp:65-66). */
+int ffa_cache_copy(int dtype, int batch, int heads, int rows, int src_max_len, int dst_max_len, int head_dim,
+                   const void* k_src, const void* v_src, void* k_dst, void* v_dst, void* stream);
+
 /* Creates the per-engine plan: validates the shape, queries the device once, prepares the
  * kernels.  use_default_launch != 0 selects the fixed analytic launch rule, 0 the table
  * measured on B200.  Host memory only; no device allocation.

@@ -178,3 +178,42 @@ def test_graphed_step_helper():
     with pytest.raises(RuntimeError, match="full"):
         step(q.cuda(), k.cuda(), v.cuda())
     assert ffa.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.float32])
+def test_adopt_prefilled_caches_and_grow(dt):
+    """Prefill writes K and V straight into the cache slabs (no copy at construction); the cache
+    then grows past its first length while decoding."""
+    from fastforwardattention_b200 import FastForwardAttn
+
+    g = torch.Generator().manual_seed(21)
+    B, H, Dh, Lp, L0 = 2, 3, 64, 50, 53
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    kc = torch.full((B, H, L0, Dh), 7.0, dtype=dt, device="cuda")
+    vc = torch.full((B, H, L0, Dh), 7.0, dtype=dt, device="cuda")
+    kc[:, :, :Lp] = K.cuda()          # "prefill" writing in place
+    vc[:, :, :Lp] = V.cuda()
+    ffa = FastForwardAttn.adopt(kc, vc, False)
+    a, b = ffa.get_cache()
+    assert a.data_ptr() == kc.data_ptr() and b.data_ptr() == vc.data_ptr() and ffa.max_len == L0
+    n = 9
+    orc = O.DecodeOracle(K, V, Lp + n, compute_dtype=torch.float64)
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3}[dt]
+    for i in range(n):
+        t = Lp + i
+        if t >= ffa.max_len:
+            with pytest.raises(RuntimeError, match="curr_timestep"):
+                ffa.attention(torch.zeros(B, H, 1, Dh, dtype=dt, device="cuda"), kc[:, :, :1], kc[:, :, :1], 0.125, t, 0)
+            ffa.grow(2 * ffa.max_len)
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        out = ffa.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, t, 0)
+        ref = orc.step(q, k, v, 0.125, t)
+        assert (out.cpu().double() - ref).abs().max().item() <= tol, i
+    assert ffa.max_len == 2 * L0
+    nk, nv = ffa.get_cache()
+    assert nk.shape == (B, H, 2 * L0, Dh)
+    assert torch.equal(nk[:, :, : Lp + n].cpu().double(), orc.K.view(B, H, -1, Dh)[:, :, : Lp + n].to(dt).double())
+    with pytest.raises(RuntimeError, match="must exceed"):
+        ffa.grow(10)
+    assert ffa.device_status() == 0
