@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import importlib
 
-__all__ = ["FastForwardAttn", "ShardedFastForwardAttn", "GraphedStep", "launch_count"]
+__all__ = ["FastForwardAttn", "ShardedFastForwardAttn", "GraphedStep", "PagePool", "PagedFastForwardAttn", "launch_count"]
 
 
 def _extension():
@@ -29,6 +29,10 @@ def __getattr__(name):
         return _extension().FastForwardAttn
     if name == "launch_count":
         return _extension().launch_count
+    if name in ("PagePool", "PagedFastForwardAttn"):
+        from . import paged
+
+        return getattr(paged, name)
     if name == "GraphedStep":
         from .graphed import GraphedStep
 

@@ -16,7 +16,7 @@ MODE_EXACT, MODE_ROUND_LIKE_TORCH = 0, 1
 SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_destroy", "ffa_plan_get_launch",
            "ffa_plan_set_launch", "ffa_plan_set_mode", "ffa_workspace_bytes", "ffa_workspace_bind", "ffa_attention",
            "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
-           "ffa_plan_get_prune_launch", "ffa_cache_copy"]
+           "ffa_plan_get_prune_launch", "ffa_cache_copy", "ffa_attention_paged"]
 
 
 class Launch(C.Structure):
@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
         L.ffa_workspace_bytes.restype = sz
         L.ffa_workspace_bind.argtypes = [vp, vp, sz, vp]
         L.ffa_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, f, i, vp, i, f, vp, vp]
+        L.ffa_attention_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, vp, f, i, vp, i, vp]
         L.ffa_device_status.argtypes = [vp, vp, C.POINTER(i)]
         L.ffa_attention_static_scratch.argtypes = [i, i, i, i, i, vp, vp, vp, vp, vp, vp, f, i, vp, vp, C.c_char_p, sz]
         L.ffa_selftest_wait_timeout.argtypes = [vp, C.c_uint, vp]

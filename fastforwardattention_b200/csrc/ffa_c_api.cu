@@ -149,7 +149,7 @@ Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int
     return s;
 }
 
-int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
+int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, bool pow2_tiles = false)
 {
     const int rowb = p->Dh * elem_size(p->dtype);
     const long long BH = (long long)p->B * p->H;
@@ -185,6 +185,11 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out)
             // small problems: shrink tiles until every CTA slot has a few units to stream
             while (s.tile_rows > 8 && BH * (cap_rows / s.tile_rows + 1) < 4 * slots0) s.tile_rows = (s.tile_rows / 2 + 7) / 8 * 8;
         }
+    }
+    if (pow2_tiles) {   // paged caches: tiles must divide the page
+        int t2 = 8;
+        while (t2 * 2 <= s.tile_rows) t2 *= 2;
+        s.tile_rows = t2;
     }
     // shared-memory budget: per CTA and per SM
     for (;;) {
@@ -529,6 +534,47 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     r = ffa_k_decode_twopass(plan->dtype, plan->Dh, P, V, threads, L.smem_bytes, smem_v, st);
     if (r != 0) return cuda_fail(r, "two-pass attention launch");
     g_launches.fetch_add(2);
+    return FFA_OK;
+}
+
+int ffa_attention_paged(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_pool, void* v_pool,
+                        const int* page_table, int max_pages, int page_rows, void* out, float softmax_scale, int t,
+                        const int* seq_lengths, int right_or_no_padding, void* stream)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (plan->offline) return fail(FFA_ERR_ARG, "this plan was created offline (planning only) and cannot launch");
+    if (!q || !k || !v || !k_pool || !v_pool || !out || !page_table) return fail(FFA_ERR_ARG, "null pointer");
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out))
+        return fail(FFA_ERR_ARG, "tensor pointers must be 16-byte aligned");
+    if (page_rows <= 0 || page_rows % 128 != 0) return fail(FFA_ERR_RANGE, "page_rows (%d) must be a positive multiple of 128", page_rows);
+    if (max_pages <= 0 || (long long)max_pages * page_rows != plan->Lmax)
+        return fail(FFA_ERR_RANGE, "max_pages * page_rows (%d * %d) must equal the plan's max_len (%d)", max_pages, page_rows, plan->Lmax);
+    if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
+    if (seq_lengths == nullptr && !right_or_no_padding)
+        return fail(FFA_ERR_ARG, "left padding (right_or_no_padding = 0) needs seq_lengths");
+    if (plan->mode != FFA_MODE_EXACT) return fail(FFA_ERR_ARG, "paged caches support the exact mode only");
+    if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
+    const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
+    const long long BH = (long long)plan->B * plan->H;
+    FfaStepParams P;
+    std::memset(&P, 0, sizeof(P));
+    P.q = q, P.k = k, P.v = v, P.k_cache = k_pool, P.v_cache = v_pool, P.out = out;
+    P.seq_lengths = seq_lengths, P.right_or_no_padding = right_or_no_padding != 0;
+    P.B = plan->B, P.H = plan->H, P.Lmax = plan->Lmax, P.t = t;
+    P.scale = softmax_scale, P.p = 0.f;
+    P.partials = plan->partials, P.tickets = plan->tickets, P.status = plan->status;
+    P.page_table = page_table, P.max_pages = max_pages, P.page_rows = page_rows;
+    ffa_launch_t L;
+    int r = fit_launch(plan, cap, 2, &L, /*pow2_tiles=*/true);
+    if (r != FFA_OK) return r;
+    if (page_rows % L.tile_rows != 0) return fail(FFA_ERR_ARG, "tile of %d rows does not divide the page", L.tile_rows);
+    P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
+    P.units_per_bh = cap / L.tile_rows + 1;
+    P.parts_per_bh = L.parts_per_bh;
+    P.total_units = BH * P.units_per_bh;
+    r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, 32 * (L.consumer_warps + 1), L.smem_bytes, static_cast<cudaStream_t>(stream));
+    if (r != 0) return cuda_fail(r, "paged attention launch");
+    g_launches.fetch_add(1);
     return FFA_OK;
 }
 

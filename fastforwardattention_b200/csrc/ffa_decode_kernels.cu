@@ -239,6 +239,18 @@ __device__ __forceinline__ SampleRange sample_range(const FfaStepParams& P, int 
     return r;
 }
 
+// Byte offset of cache row `row` of pair bh from the start of the cache (or page pool).
+// Contiguous slabs: [B*H, Lmax, Dh].  Paged: the pool is [pages, H, page_rows, Dh] and
+// page_table[b][row / page_rows] names the page; rows of one (pair, page) are contiguous, and
+// tiles never straddle pages because tile_rows divides page_rows.
+__device__ __forceinline__ size_t cache_row_offset(const FfaStepParams& P, int bh, int row, int rowb)
+{
+    if (P.page_table == nullptr) return ((size_t)bh * P.Lmax + row) * rowb;
+    const int b = bh / P.H, h = bh - b * P.H;
+    const int page = P.page_table[(size_t)b * P.max_pages + row / P.page_rows];
+    return (((size_t)page * P.H + h) * P.page_rows + row % P.page_rows) * rowb;
+}
+
 // Work decomposition.  Every (batch, head) is cut into `parts_per_bh` parts of whole tiles
 // (part p of a pair covers its units [p*upb/C, (p+1)*upb/C)); the flat list of B*H*C parts is
 // cut into `grid` equal contiguous runs, one per CTA.  With C = units per pair this is a plain
@@ -360,7 +372,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 if (hi <= lo) continue;
                 if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
                 const uint32_t bytes = (uint32_t)(hi - lo) * ROWB;
-                const size_t off = ((size_t)bh * P.Lmax + lo) * ROWB;
+                const size_t off = cache_row_offset(P, bh, lo, ROWB);
                 mbar_expect_tx(bar_full + 8 * stage, bytes * TENSORS);
                 bulk_copy_g2s(ring + stage * stage_bytes, kc + off, bytes, bar_full + 8 * stage);
                 if (TENSORS == 2) bulk_copy_g2s(ring + stage * stage_bytes + tile_bytes, vc + off, bytes, bar_full + 8 * stage);
@@ -568,7 +580,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                     const float corr = expo(m - m_new), pr = expo(st - m_new);
                     m = m_new;
                     l = l * corr + pr;
-                    const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+                    const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
                         const int vec = li + x * LPR;

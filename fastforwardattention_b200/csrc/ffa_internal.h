@@ -31,6 +31,10 @@ struct FfaStepParams {
     int mask_words;
     // fused pruning kernel: CTAs per (batch, head) cluster, cache rows per CTA (multiple of 32)
     int cluster, chunk_rows;
+    // paged caches (exact path only): k_cache / v_cache are page pools [pages, H, page_rows, Dh] and
+    // page_table [B, max_pages] names the page of every page_rows rows of a sequence; null = contiguous
+    const int* page_table;
+    int max_pages, page_rows;
 };
 
 // dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.

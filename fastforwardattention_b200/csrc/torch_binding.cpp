@@ -250,6 +250,92 @@ struct FastForwardAttn {
     bool has_scores = false, want_mask = false, use_default = false;
 };
 
+// Decode steps over PAGED caches (exact attention): the K and V pools are
+// [pages, heads, page_rows, head_dim]; a page table [batch, max_pages] maps every page_rows rows of a
+// sequence to a pool page.  The pools and the table belong to the caller (see paged.py for an
+// allocator); this class holds the plan and the workspace.  The reference has nothing like it:
+// its caches are max_len rows per sequence, allocated up front (torch_ffa_api.cpp:65-66).
+struct PagedEngine {
+    PagedEngine(torch::Tensor k_pool, torch::Tensor v_pool, int64_t batch, int64_t max_pages, bool use_default_kernel_launch)
+    {
+        TORCH_CHECK(k_pool.is_cuda() && v_pool.is_cuda() && k_pool.dim() == 4 && v_pool.sizes() == k_pool.sizes() &&
+                        k_pool.scalar_type() == v_pool.scalar_type() && k_pool.device() == v_pool.device() &&
+                        k_pool.is_contiguous() && v_pool.is_contiguous(),
+                    "PagedEngine: pools must be two contiguous CUDA tensors [pages, heads, page_rows, head_dim] of one dtype");
+        kp = k_pool, vp = v_pool;
+        B = batch, H = k_pool.size(1), page_rows = k_pool.size(2), Dh = k_pool.size(3), this->max_pages = max_pages;
+        TORCH_CHECK(B > 0 && max_pages > 0 && max_pages * page_rows < (int64_t(1) << 31), "PagedEngine: sizes out of range");
+        dtype = dtype_code(k_pool);
+        device = k_pool.device();
+        c10::cuda::CUDAGuard guard(device);
+        check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)(max_pages * page_rows), use_default_kernel_launch, device.index(), &plan),
+              "plan");
+        const size_t n = ffa_workspace_bytes(plan, 0);
+        workspace = torch::empty({(int64_t)n}, torch::TensorOptions().dtype(torch::kUInt8).device(device));
+        auto stream = at::cuda::getCurrentCUDAStream();
+        check(ffa_workspace_bind(plan, workspace.data_ptr(), n, stream.stream()), "workspace");
+        stream.synchronize();
+    }
+    ~PagedEngine() { ffa_plan_destroy(plan); }
+    PagedEngine(const PagedEngine&) = delete;
+    PagedEngine& operator=(const PagedEngine&) = delete;
+
+    torch::Tensor run(const torch::Tensor& q_, const torch::Tensor& k_, const torch::Tensor& v_, const torch::Tensor& table,
+                      double softmax_scale, int64_t t, const torch::Tensor* rows, c10::optional<torch::Tensor> out_opt)
+    {
+        const int64_t n = B * H * Dh;
+        auto prep = [&](const torch::Tensor& x, const char* name) {
+            TORCH_CHECK(x.is_cuda() && x.device() == device && dtype_code(x) == dtype && x.numel() == n, "PagedEngine: ", name,
+                        " must hold batch*heads*head_dim = ", n, " elements of the pool's dtype on the pool's device");
+            return x.contiguous();
+        };
+        torch::Tensor q = prep(q_, "q"), k = prep(k_, "k"), v = prep(v_, "v");
+        TORCH_CHECK(table.is_cuda() && table.device() == device && table.scalar_type() == torch::kInt && table.is_contiguous() &&
+                        table.dim() == 2 && table.size(0) == B && table.size(1) == max_pages,
+                    "PagedEngine: page_table must be a contiguous int32 CUDA tensor [batch, max_pages]");
+        torch::Tensor sl;
+        if (rows != nullptr) {
+            TORCH_CHECK(rows->is_cuda() && rows->device() == device && rows->scalar_type() == torch::kInt && rows->numel() == B,
+                        "PagedEngine: rows must be an int32 CUDA tensor with one entry per sequence");
+            sl = rows->contiguous();
+        }
+        TORCH_CHECK(t >= 0 && t < max_pages * page_rows, "PagedEngine: curr_timestep ", t, " outside [0, ", max_pages * page_rows, ")");
+        c10::cuda::CUDAGuard guard(device);
+        torch::Tensor out = out_opt.has_value() ? *out_opt : torch::empty({B, H, Dh}, q.options());
+        TORCH_CHECK(out.is_cuda() && out.device() == device && dtype_code(out) == dtype && out.is_contiguous() && out.numel() == n,
+                    "PagedEngine: out must be a contiguous tensor of batch*heads*head_dim elements on the pool's device");
+        check(ffa_attention_paged(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr<int>(),
+                                  (int)max_pages, (int)page_rows, out.data_ptr(), (float)softmax_scale, (int)t,
+                                  rows ? sl.data_ptr<int>() : nullptr, 1, at::cuda::getCurrentCUDAStream().stream()),
+              "paged attention");
+        return out;
+    }
+    torch::Tensor attention(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor table, double scale, int64_t t,
+                            c10::optional<torch::Tensor> out)
+    {
+        return run(q, k, v, table, scale, t, nullptr, out);
+    }
+    torch::Tensor attention_per_sample(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor table, double scale,
+                                       torch::Tensor rows, c10::optional<torch::Tensor> out)
+    {
+        return run(q, k, v, table, scale, 0, &rows, out);
+    }
+    int device_status()
+    {
+        c10::cuda::CUDAGuard guard(device);
+        int st = 0;
+        const int rc = ffa_device_status(plan, at::cuda::getCurrentCUDAStream().stream(), &st);
+        TORCH_CHECK(rc == FFA_OK || rc == FFA_ERR_DEVICE, "PagedEngine: status: ", ffa_last_error());
+        return st;
+    }
+
+    ffa_plan_t* plan = nullptr;
+    torch::Tensor kp, vp, workspace;
+    c10::Device device{c10::kCUDA, 0};
+    int64_t B = 0, H = 0, Dh = 0, page_rows = 0, max_pages = 0;
+    int dtype = 0;
+};
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
@@ -287,4 +373,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("record_kept_mask", &FastForwardAttn::record_kept_mask)
         .def("get_kept_mask", &FastForwardAttn::get_kept_mask)
         .def("device_status", &FastForwardAttn::device_status, "synchronises; 0 when the kernels recorded no error");
+    py::class_<PagedEngine>(m, "PagedEngine")
+        .def(py::init<torch::Tensor, torch::Tensor, int64_t, int64_t, bool>(), py::arg("k_pool"), py::arg("v_pool"), py::arg("batch"),
+             py::arg("max_pages"), py::arg("use_default_kernel_launch") = false)
+        .def("attention", &PagedEngine::attention, "exact decode step, every sequence at row curr_timestep", py::arg("q"), py::arg("k"),
+             py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("curr_timestep"), py::arg("out") = py::none())
+        .def("attention_per_sample", &PagedEngine::attention_per_sample, "exact decode step, sequence b at row rows[b]", py::arg("q"),
+             py::arg("k"), py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("rows"), py::arg("out") = py::none())
+        .def("device_status", &PagedEngine::device_status);
 }
