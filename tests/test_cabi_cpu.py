@@ -66,3 +66,19 @@ def test_extension_class_surface():
 
     with pytest.raises(RuntimeError, match="CUDA tensors"):
         FastForwardAttn(torch.zeros(1, 1, 4, 64), torch.zeros(1, 1, 4, 64), 8, False)
+
+
+def test_header_is_plain_c_and_links(tmp_path):
+    """include/ffa_c_api.h must be usable from C (no C++, no CUDA headers): compile a C99
+    translation unit against it, link the shared library, call one entry point."""
+    import subprocess
+
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "ffa_c_api.h"\n'
+                   "int main(void) { size_t a, b; if (ffa_cache_bytes(FFA_DTYPE_F16, 2, 3, 8, 64, &a, &b) != FFA_OK) return 1;\n"
+                   "  return (a == 2u * 3u * 8u * 64u * 2u && a == b && ffa_last_error() != 0) ? 0 : 2; }\n")
+    exe = tmp_path / "use_header"
+    libdir = os.path.dirname(capi.LIB_PATH)
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"), str(src),
+                    "-L", libdir, "-lffa_b200", f"-Wl,-rpath,{libdir}", "-o", str(exe)], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
