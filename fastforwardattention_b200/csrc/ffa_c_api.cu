@@ -510,7 +510,6 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
     P.units_per_bh = cap / L.tile_rows + 1;
     P.parts_per_bh = L.parts_per_bh;
-    P.total_units = BH * P.units_per_bh;
     const int threads = 32 * (L.consumer_warps + 1);
     if (!twopass) {
         r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, threads, L.smem_bytes, st);
@@ -524,9 +523,9 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     V.stages = 0;
     V.units_per_bh = cap / V.tile_rows + 1;
     V.parts_per_bh = V.units_per_bh;
-    V.total_units = BH * V.units_per_bh;
+    const long long v_units = BH * V.units_per_bh;
     long long vgrid = (long long)plan->sms * 4;
-    if (vgrid > V.total_units) vgrid = V.total_units;
+    if (vgrid > v_units) vgrid = v_units;
     if (vgrid > plan->max_grid) vgrid = plan->max_grid;
     V.grid = (int)vgrid;
     V.tickets = plan->tickets + BH;
@@ -555,7 +554,6 @@ int ffa_attention_paged(ffa_plan_t* plan, const void* q, const void* k, const vo
     if (plan->mode != FFA_MODE_EXACT) return fail(FFA_ERR_ARG, "paged caches support the exact mode only");
     if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
     const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
-    const long long BH = (long long)plan->B * plan->H;
     FfaStepParams P;
     std::memset(&P, 0, sizeof(P));
     P.q = q, P.k = k, P.v = v, P.k_cache = k_pool, P.v_cache = v_pool, P.out = out;
@@ -571,7 +569,6 @@ int ffa_attention_paged(ffa_plan_t* plan, const void* q, const void* k, const vo
     P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
     P.units_per_bh = cap / L.tile_rows + 1;
     P.parts_per_bh = L.parts_per_bh;
-    P.total_units = BH * P.units_per_bh;
     r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, 32 * (L.consumer_warps + 1), L.smem_bytes, static_cast<cudaStream_t>(stream));
     if (r != 0) return cuda_fail(r, "paged attention launch");
     g_launches.fetch_add(1);

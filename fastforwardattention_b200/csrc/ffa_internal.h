@@ -17,7 +17,6 @@ struct FfaStepParams {
     // work decomposition: every (batch, head) owns units_per_bh tiles of tile_rows cache rows, grouped
     // into parts_per_bh parts; the flat list of B*H*parts_per_bh parts is cut into `grid` equal runs
     int tile_rows, stages, units_per_bh, parts_per_bh, grid;
-    long long total_units;
     float scale;
     float p;
     int round_like_torch;

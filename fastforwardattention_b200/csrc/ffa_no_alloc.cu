@@ -147,7 +147,6 @@ extern "C" int ffa_attention_static_scratch(int dtype, int batch, int heads, int
     P.seq_lengths = nullptr, P.right_or_no_padding = 1;
     P.B = batch, P.H = heads, P.Lmax = max_len, P.t = t;
     P.tile_rows = tile_rows, P.stages = stages, P.units_per_bh = upb, P.parts_per_bh = upb, P.grid = (int)grid;
-    P.total_units = BH * upb;
     P.scale = softmax_scale, P.p = 0.f;
     P.status = device_status != nullptr ? device_status : reinterpret_cast<int*>(st.scratch);
     P.tickets = reinterpret_cast<int*>(st.scratch + tickets_off);
