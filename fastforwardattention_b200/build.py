@@ -24,7 +24,8 @@ LIB = os.path.join(PKG, "libffa_b200.so")
 EXT = os.path.join(PKG, "ff_attention" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 CUDA_SOURCES = ["ffa_decode_kernels.cu", "ffa_c_api.cu", "ffa_no_alloc.cu"]
-CUDA_DEPS = CUDA_SOURCES + ["ffa_internal.h", os.path.join(ROOT, "include", "ffa_c_api.h")]
+KERNEL_HEADERS = ["ffa_internal.h", "ffa_device_common.cuh", "ffa_stream_kernel.cuh", "ffa_prune_kernels.cuh"]
+CUDA_DEPS = CUDA_SOURCES + KERNEL_HEADERS + [os.path.join(ROOT, "include", "ffa_c_api.h")]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
@@ -48,7 +49,7 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
             obj = os.path.join(PKG, "build", src.replace(".cu", ".o"))
             os.makedirs(os.path.dirname(obj), exist_ok=True)
             if force or _stale(obj, CUDA_DEPS if src != "ffa_decode_kernels.cu" else
-                               ["ffa_decode_kernels.cu", "ffa_internal.h"]):
+                               ["ffa_decode_kernels.cu"] + KERNEL_HEADERS):
                 _run([NVCC, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose_ptxas else []), "-c",
                       os.path.join(CSRC, src), "-o", obj])
             objs.append(obj)

@@ -1,0 +1,289 @@
+// Device-side building blocks shared by the decode kernels: mbarrier / bulk-copy PTX wrappers
+// with time-bounded waits, element traits (16-byte vectors <-> fp32), the lane-group geometry of
+// a cache row, per-sample ranges, cache addressing (contiguous or paged) and the work partition.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include <cstring>
+#include <type_traits>
+
+#include "ffa_internal.h"
+
+namespace ffa_dev {
+
+
+constexpr int kPassOne = 0;
+constexpr int kPassScore = 1;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bounded barrier wait: 2 s, then give up
+constexpr uint32_t kDrainPolls = 1u << 20;
+constexpr int kStatusWaitTimeout = 1;
+constexpr int kStatusBadLength = 2;
+constexpr int kGatherThreads = 256;
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers: mbarrier + 1-D bulk copy global -> this CTA's shared memory
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// same, but the hardware may park the thread for up to `hint_ns` before answering
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the phase with the given parity.  Never spins for ever: after kWaitLimitNs of wall
+// time (or as soon as another thread of the CTA gave up) it raises the CTA's `dead` flag and
+// returns false; callers then skip the data but keep walking the same control flow so every
+// CTA-level barrier is still reached by everyone.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* dead,
+                                                  unsigned long long limit_ns = kWaitLimitNs)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
+        if (*dead) return false;
+        if (global_timer_ns() - t0 > limit_ns) break;
+    }
+    *dead = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ------------------------------------------------------------------------------------------
+// Element traits: a 16-byte vector holds EPV elements; unpack to fp32, round from fp32
+// ------------------------------------------------------------------------------------------
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+    static constexpr int EPV = 4;
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f)
+    {
+        f[0] = __uint_as_float(r.x), f[1] = __uint_as_float(r.y), f[2] = __uint_as_float(r.z),
+        f[3] = __uint_as_float(r.w);
+    }
+    static __device__ __forceinline__ void unpack2(const uint4& r, float2* f)
+    {
+        f[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+        f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+    }
+    static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ void store(float* p, float x) { *p = x; }
+    // attention.cu:461-464
+    static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
+};
+template <>
+struct Elem<__half> {
+    static constexpr int EPV = 8;
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = t.x, f[2 * i + 1] = t.y;
+        }
+    }
+    static __device__ __forceinline__ void unpack2(const uint4& r, float2* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    }
+    static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ void store(__half* p, float x) { *p = __float2half_rn(x); }
+    // attention.cu:466-469 hands two raw bit patterns to __hle; the unsigned short -> __half
+    // conversion there is the NUMERIC one, so the patterns themselves are rounded to 11
+    // significant bits and compared.  Reproduced literally.
+    static __device__ __forceinline__ bool leq(float a, float b)
+    {
+        const unsigned short ba = __half_as_ushort(__float2half_rn(a));
+        const unsigned short bb = __half_as_ushort(__float2half_rn(b));
+        return __hle(__ushort2half_rn(ba), __ushort2half_rn(bb));
+    }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+    static constexpr int EPV = 8;
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void unpack2(const uint4& r, float2* f)
+    {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    }
+    static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+    // the reference has no bf16; plain value comparison
+    static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
+};
+
+// Geometry of one cache row of DH elements of T, and of the lane group that owns a row.
+template <typename T, int DH>
+struct RowGeom {
+    static constexpr int EPV = Elem<T>::EPV;
+    static constexpr int ROWB = DH * (int)sizeof(T);   // bytes per row, multiple of 16
+    static constexpr int VPR = ROWB / 16;               // 16-byte vectors per row
+    // Lanes per row group and vectors per lane.  Power-of-two rows: one vector per lane up to a
+    // full warp, two per lane for 1024-byte rows.  head_dim 80 (10 or 20 vectors): five vectors
+    // per lane and 2 or 4 lanes per row, so that no lane idles.
+    static constexpr bool kFiveWide = (VPR % 5) == 0;
+    static constexpr int LPR = kFiveWide ? VPR / 5 : (VPR >= 32 ? 32 : VPR);
+    static constexpr int VPL = kFiveWide ? 5 : (VPR + 31) / 32;
+    static constexpr int RB = VPL >= 4 ? 2 : 4;          // rows per lane group and batch (register budget)
+    static_assert(LPR * VPL == VPR && (LPR & (LPR - 1)) == 0, "every lane of a power-of-two group owns VPL vectors");
+    static_assert(ROWB % 16 == 0, "rows must be 16-byte multiples");
+};
+
+// Per-sample view of the cache for this step (attention.cu:805-817).  `row` is where the new
+// token goes and the number of cached rows attended; keys below `first` are masked.
+struct SampleRange {
+    int first, row;
+    bool ok;
+};
+__device__ __forceinline__ SampleRange sample_range(const FfaStepParams& P, int b)
+{
+    SampleRange r;
+    r.first = 0, r.row = P.t;
+    if (P.seq_lengths != nullptr) {
+        const int s = P.seq_lengths[b];
+        if (P.right_or_no_padding) r.row = s;
+        else r.first = s;
+    }
+    r.ok = r.row >= 0 && r.row < P.Lmax;
+    if (!r.ok) r.row = 0;
+    r.first = min(max(r.first, 0), r.row);
+    return r;
+}
+
+// Byte offset of cache row `row` of pair bh from the start of the cache (or page pool).
+// Contiguous slabs: [B*H, Lmax, Dh].  Paged: the pool is [pages, H, page_rows, Dh] and
+// page_table[b][row / page_rows] names the page; rows of one (pair, page) are contiguous, and
+// tiles never straddle pages because tile_rows divides page_rows.
+__device__ __forceinline__ size_t cache_row_offset(const FfaStepParams& P, int bh, int row, int rowb)
+{
+    if (P.page_table == nullptr) return ((size_t)bh * P.Lmax + row) * rowb;
+    const int b = bh / P.H, h = bh - b * P.H;
+    const int page = P.page_table[(size_t)b * P.max_pages + row / P.page_rows];
+    return (((size_t)page * P.H + h) * P.page_rows + row % P.page_rows) * rowb;
+}
+
+// Work decomposition.  Every (batch, head) is cut into `parts_per_bh` parts of whole tiles
+// (part p of a pair covers its units [p*upb/C, (p+1)*upb/C)); the flat list of B*H*C parts is
+// cut into `grid` equal contiguous runs, one per CTA.  With C = units per pair this is a plain
+// even cut of the unit list (large problems: perfect balance); with a small C and grid = B*H*C
+// or B*H/k every CTA boundary falls on a part boundary, so a CTA owns exactly one segment and
+// a pair is merged from exactly C partials (small problems: the serial per-segment latency
+// and the merge traffic are what cost).  Requires C <= upb and grid <= B*H*C.
+struct Partition {
+    long long parts_total;
+    int upb, C, G;
+    __device__ __forceinline__ long long unit_of_part(long long p) const
+    {
+        const long long bh = p / C;
+        return bh * upb + ((p - bh * C) * upb) / C;
+    }
+    __device__ __forceinline__ long long first_unit(long long cta) const { return unit_of_part(cta * parts_total / G); }
+    // the CTA that owns part p
+    __device__ __forceinline__ int cta_of_part(long long p) const { return (int)(((p + 1) * G + parts_total - 1) / parts_total - 1); }
+    __device__ __forceinline__ int first_cta_of(int bh) const { return cta_of_part((long long)bh * C); }
+    __device__ __forceinline__ int last_cta_of(int bh) const { return cta_of_part((long long)(bh + 1) * C - 1); }
+};
+__device__ __forceinline__ Partition make_partition(const FfaStepParams& P)
+{
+    Partition q;
+    q.upb = P.units_per_bh, q.C = P.parts_per_bh, q.G = P.grid;
+    q.parts_total = (long long)P.B * P.H * P.parts_per_bh;
+    return q;
+}
+
+template <typename T, int DH>
+__device__ __forceinline__ void load_row_f32(const unsigned char* row, int li, float (&f)[RowGeom<T, DH>::VPL][RowGeom<T, DH>::EPV])
+{
+    using G = RowGeom<T, DH>;
+#pragma unroll
+    for (int x = 0; x < G::VPL; ++x) {
+        const int vec = li + x * G::LPR;
+        if (vec < G::VPR) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + vec * 16);
+            Elem<T>::unpack(raw, f[x]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < G::EPV; ++e) f[x][e] = 0.f;
+        }
+    }
+}
+
+template <int LPR>
+__device__ __forceinline__ float group_sum(float x)
+{
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+    return x;
+}
+
+}  // namespace ffa_dev

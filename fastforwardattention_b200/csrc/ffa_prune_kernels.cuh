@@ -1,0 +1,557 @@
+// Pruning (and torch-rounding) kernels: the value pass of the two-launch path and the fused cluster kernel.
+#pragma once
+#include "ffa_device_common.cuh"
+
+namespace ffa_dev {
+
+// ------------------------------------------------------------------------------------------
+// Value pass of the two-pass modes: prune test on every cached row, gather the survivors
+// ------------------------------------------------------------------------------------------
+// Shared memory: kept-row list (index + probability) for one unit of tile_rows rows, then the
+// group reduction area [NG][DH].  All 8 warps compute; rows that survive are fetched with
+// 16-byte global loads, four rows in flight per lane group.
+template <typename T, int DH>
+__global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const FfaStepParams P)
+{
+    using G = RowGeom<T, DH>;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
+    constexpr int NT = kGatherThreads, NG = NT / LPR;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int R = P.tile_rows;  // multiple of 32
+    int* list_idx = reinterpret_cast<int*>(smem);
+    float* list_p = reinterpret_cast<float*>(list_idx + R);
+    float* red = list_p + R;  // [NG][DH]
+    __shared__ int s_n, s_last;
+    __shared__ unsigned s_words[16];   // one ballot per 32 rows of a 512-row unit
+
+    const int upb = P.units_per_bh;
+    const Partition cut = make_partition(P);
+    const long long u0 = cut.first_unit(blockIdx.x), u1 = cut.first_unit(blockIdx.x + 1);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = tid / LPR, li = tid % LPR;
+    const bool prune = P.p > 0.f;
+    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
+
+    long long u = u0;
+    while (u < u1) {
+        const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
+        const int j1 = (int)min((long long)upb, j0 + (u1 - u));
+        const SampleRange sr = sample_range(P, bh / P.H);
+        const int jt = sr.row / R;
+        const float M = P.stats[2 * bh], Lsum = P.stats[2 * bh + 1];
+        // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125,
+        // 1185); the torch-rounding mode divides exactly like torch's softmax does
+        const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
+        const float theta = Elem<T>::round(P.p * inv);
+        const float* sc = P.scores + (size_t)bh * P.Lmax;
+        auto prob_of = [&](float s) -> float {
+            if (prune) return Elem<T>::round(__expf(s - M) * inv);
+            return Elem<T>::round(expf(s - M) / Lsum);
+        };
+
+        float acc[VPL][EPV];
+#pragma unroll
+        for (int x = 0; x < VPL; ++x)
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) acc[x][e] = 0.f;
+
+        for (int j = j0; j < j1 && sr.ok; ++j) {
+            const int lo = j * R, hi = min((j + 1) * R, sr.row + 1);  // includes the new token's bit
+            if (hi <= lo) break;
+            // survivors are listed in row order: ballots first, then a prefix over the words
+            __syncthreads();
+            float my_p[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int base = lo + (warp + 8 * k) * 32;
+                my_p[k] = -1.f;
+                if (base >= hi) continue;   // warp-uniform
+                const int i = base + lane;
+                const bool cached = i < sr.row && i >= sr.first;
+                float pr = 0.f;
+                bool keep = false;
+                if (cached) {
+                    pr = prob_of(sc[i]);
+                    keep = prune ? !Elem<T>::leq(pr, theta) : true;
+                }
+                const unsigned bal = __ballot_sync(0xffffffffu, keep);
+                if (P.kept_mask != nullptr && lane == 0)
+                    P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
+                        bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+                if (lane == 0) s_words[warp + 8 * k] = bal;
+                if (keep) my_p[k] = pr;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                if (my_p[k] >= 0.f) {
+                    const int w = warp + 8 * k;
+                    int pos = __popc(s_words[w] & ((1u << lane) - 1u));
+                    for (int ww = 0; ww < w; ++ww) pos += __popc(s_words[ww]);
+                    list_idx[pos] = lo + w * 32 + lane, list_p[pos] = my_p[k];
+                }
+            }
+            if (tid == 0) {
+                int tot = 0;
+                for (int w = 0; w < ((hi - lo + 31) >> 5); ++w) tot += __popc(s_words[w]);
+                s_n = tot;
+            }
+            __syncthreads();
+            const int n = s_n;
+            for (int base = 0; base < n; base += RB * NG) {
+                uint4 raw[RB][VPL];
+                float pr[RB];
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) {
+                    const int idx = base + uu * NG + g;
+                    const bool okr = idx < n;
+                    pr[uu] = okr ? list_p[idx] : 0.f;
+                    const int row = okr ? list_idx[idx] : 0;
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        const int vec = li + x * LPR;
+                        raw[uu][x] = make_uint4(0, 0, 0, 0);
+                        if (okr && vec < VPR)
+                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + ((size_t)bh * P.Lmax + row) * ROWB + vec * 16));
+                    }
+                }
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu)
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        float vf[EPV];
+                        Elem<T>::unpack(raw[uu][x], vf);
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr[uu], vf[e], acc[x][e]);
+                    }
+            }
+        }
+
+        // the new token is never pruned (attention.cu:1227-1256): append v, add P_t * v
+        if (sr.ok && j0 <= jt && jt < j1 && g == 0) {
+            const float pt = prob_of(sc[sr.row]);
+            const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                const int vec = li + x * LPR;
+                if (vec < VPR) {
+                    const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + (size_t)bh * ROWB + vec * 16);
+                    *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
+                    float vf[EPV];
+                    Elem<T>::unpack(vraw, vf);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pt, vf[e], acc[x][e]);
+                }
+            }
+        }
+
+        // ---- sum the groups, then the CTAs ----
+        __syncthreads();
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) {
+            const int vec = li + x * LPR;
+            if (vec < VPR) {
+#pragma unroll
+                for (int e = 0; e < EPV; e += 4)
+                    *reinterpret_cast<float4*>(red + g * DH + vec * EPV + e) =
+                        make_float4(acc[x][e], acc[x][e + 1], acc[x][e + 2], acc[x][e + 3]);
+            }
+        }
+        __syncthreads();
+        const bool whole = (j0 == 0 && j1 == upb);
+        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+        float* part = P.partials + (size_t)(blockIdx.x + bh) * (DH + 2);
+        for (int d = tid; d < DH; d += NT) {
+            float A = 0.f;
+            for (int gg = 0; gg < NG; ++gg) A += red[gg * DH + d];
+            if (whole) Elem<T>::store(outp + d, A);
+            else part[d] = A;
+        }
+        if (!whole) {
+            __threadfence();
+            __syncthreads();
+            const int c_first = cut.first_cta_of(bh), c_last = cut.last_cta_of(bh);
+            const int count = c_last - c_first + 1;
+            if (tid == 0) s_last = (atomicAdd(P.tickets + bh, 1) == count - 1);
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const float* pbase = P.partials + (size_t)(c_first + bh) * (DH + 2);
+                for (int d = tid; d < DH; d += NT) {
+                    float A = 0.f;
+                    for (int k = 0; k < count; ++k) A += __ldcg(pbase + (size_t)k * (DH + 2) + d);
+                    Elem<T>::store(outp + d, A);
+                }
+                if (tid == 0) P.tickets[bh] = 0;
+            }
+        }
+        if (!sr.ok && tid == 0) atomicOr(P.status, kStatusBadLength);
+        u += j1 - j0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Fused pruning step: one thread-block cluster per (batch, head), scores never leave the SMs
+// ------------------------------------------------------------------------------------------
+// The pruning rule needs the global max and sum of a (batch, head) before any V row may be
+// touched (attention.cu:1184-1191), so the score pass and the value pass cannot be one
+// streaming sweep.  Here both live in one kernel: a cluster of C CTAs owns a (batch, head);
+// CTA r scores its slice of rows from a K-only bulk-copy ring into its OWN shared memory,
+// the C pairs (max, sum) are exchanged through distributed shared memory behind a cluster
+// barrier, every CTA prunes and gathers the V rows of its slice, and CTA 0 adds the C partial
+// outputs (again through distributed shared memory).  No score scratch in HBM, no second
+// launch, no arrival counters.  Used when a slice's scores fit in shared memory; the two
+// kernels above remain for everything else.
+//
+// Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (index, probability)
+// | ballot words | group reduction area [NG][DH + 4] | partial output [DH] | (max, sum) | barriers | flags.
+constexpr int kFusedThreads = 160;   // 1 copy warp + 4 compute warps
+constexpr int kFusedListCap = 512;   // rows pruned and gathered per round (multiple of 32)
+
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_smem_f32(const void* own_smem_ptr, uint32_t peer_rank)
+{
+    uint32_t peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_smem_ptr)), "r"(peer_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const FfaStepParams P)
+{
+    using G = RowGeom<T, DH>;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
+    constexpr int NCW = 4, NCT = NCW * 32, NG = NCT / LPR, RS = DH + 4, E2 = EPV / 2;
+    constexpr bool kAllLanes = (VPR == LPR * VPL);
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int R = P.tile_rows, S = P.stages, C = P.cluster, chunk = P.chunk_rows;
+    const uint32_t tile_bytes = (uint32_t)R * ROWB;
+    float* sc = reinterpret_cast<float*>(smem + (size_t)S * tile_bytes);
+    int* list_idx = reinterpret_cast<int*>(sc + chunk);
+    float* list_p = reinterpret_cast<float*>(list_idx + kFusedListCap);
+    unsigned* words = reinterpret_cast<unsigned*>(list_p + kFusedListCap);   // one ballot per 32 rows of a round
+    float* red = reinterpret_cast<float*>(words + kFusedListCap / 32);
+    float* accs = red + NG * RS;
+    float* stat = accs + DH;                       // [0] max, [1] sum of this CTA's slice
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4);
+    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead, [1] list length
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S), ring = smem_u32(smem);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t rank = cluster_rank();
+    const int bh = blockIdx.x / C;
+    const SampleRange sr = sample_range(P, bh / P.H);
+    const int c0 = (int)rank * chunk;                                   // first absolute row of this slice
+    const int lo = sr.ok ? max(c0, sr.first) : 0;
+    const int hi = sr.ok ? min(c0 + chunk, sr.row) : 0;                 // cached rows [lo, hi)
+    const bool owns_new = sr.ok && sr.row >= c0 && sr.row < c0 + chunk; // the new token's row is in this slice
+    const int nrows = max(hi - lo, 0), ntiles = (nrows + R - 1) / R;
+    const bool prune = P.p > 0.f;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, NCW);
+        }
+        flags[0] = 0, flags[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int ctid = tid - 32, g = ctid / LPR, li = ctid % LPR;   // meaningful for compute warps only
+    float2 q2[VPL][E2];
+    float qf[VPL][EPV];
+    float m = -CUDART_INF_F, l = 0.f;
+
+    auto score_of = [&](float dot) -> float {
+        if (P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
+        return dot * P.scale;
+    };
+
+    // ---------------- phase 1: scores of this slice into shared memory ----------------
+    if (warp == 0) {
+        if (tid == 0) {
+            const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache) + ((size_t)bh * P.Lmax + lo) * ROWB;
+            uint32_t stage = 0, use = 0;
+            for (int j = 0; j < ntiles; ++j) {
+                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
+                const uint32_t bytes = (uint32_t)min(R, nrows - j * R) * ROWB;
+                mbar_expect_tx(bar_full + 8 * stage, bytes);
+                bulk_copy_g2s(ring + stage * tile_bytes, kc + (size_t)j * tile_bytes, bytes, bar_full + 8 * stage);
+                if (++stage == (uint32_t)S) stage = 0, ++use;
+            }
+        }
+    } else {
+        load_row_f32<T, DH>(static_cast<const unsigned char*>(P.q) + (size_t)bh * ROWB, li, qf);
+#pragma unroll
+        for (int x = 0; x < VPL; ++x)
+#pragma unroll
+            for (int e = 1; e < EPV; e += 2) q2[x][e >> 1] = make_float2(qf[x][e - 1], qf[x][e]);
+
+        uint32_t stage = 0, phase = 0;
+        for (int j = 0; j < ntiles; ++j) {
+            const int n = min(R, nrows - j * R);
+            const bool ready = mbar_wait_bounded(bar_full + 8 * stage, phase, flags);
+            const unsigned char* ks = smem + (size_t)stage * tile_bytes;
+            float* sc_tile = sc + (lo - c0) + j * R;
+            if (ready) {
+                // RB rows per lane group at a time, loads first; FULL: every row of the batch exists
+                auto batch = [&](auto full_tag, int base) {
+                    constexpr bool FULL = decltype(full_tag)::value;
+                    uint4 kraw[RB][VPL];
+#pragma unroll
+                    for (int uu = 0; uu < RB; ++uu) {
+                        const int r = base + uu * NG + g;
+                        const int rc = FULL ? r : min(r, n - 1);
+#pragma unroll
+                        for (int x = 0; x < VPL; ++x)
+                            kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc * ROWB + (li + x * LPR) * 16);
+                    }
+                    float s4[RB];
+#pragma unroll
+                    for (int uu = 0; uu < RB; ++uu) {
+                        float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int x = 0; x < VPL; ++x) {
+                            float2 k2[E2];
+                            Elem<T>::unpack2(kraw[uu][x], k2);
+#pragma unroll
+                            for (int e = 0; e < E2; ++e) a = __ffma2_rn(q2[x][e], k2[e], a);
+                        }
+                        s4[uu] = a.x + a.y;
+                    }
+#pragma unroll
+                    for (int off = LPR / 2; off >= 1; off >>= 1)
+#pragma unroll
+                        for (int uu = 0; uu < RB; ++uu) s4[uu] += __shfl_xor_sync(0xffffffffu, s4[uu], off);
+                    float m_new = m;
+#pragma unroll
+                    for (int uu = 0; uu < RB; ++uu) {
+                        const int r = base + uu * NG + g;
+                        const bool okr = FULL || r < n;
+                        s4[uu] = okr ? score_of(s4[uu]) : -CUDART_INF_F;
+                        if (okr && li == 0) sc_tile[r] = s4[uu];
+                        m_new = fmaxf(m_new, s4[uu]);
+                    }
+                    if (FULL || m_new != -CUDART_INF_F) {
+                        float psum = 0.f;
+#pragma unroll
+                        for (int uu = 0; uu < RB; ++uu) psum += __expf(s4[uu] - m_new);   // as attention.cu:1113
+                        l = l * __expf(m - m_new) + psum;
+                        m = m_new;
+                    }
+                };
+                int base = 0;
+                for (; base + RB * NG <= n; base += RB * NG) batch(std::true_type{}, base);
+                if (base < n) batch(std::false_type{}, base);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+            if (++stage == (uint32_t)S) stage = 0, phase ^= 1;
+        }
+        // the new token: score against k, append k at row sr.row (attention.cu:900-958)
+        if (owns_new) {
+            float kf[VPL][EPV];
+            load_row_f32<T, DH>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB, li, kf);
+            float dot = 0.f;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[x][e], dot);
+            dot = group_sum<LPR>(dot);
+            if (g == 0) {
+                const float st = score_of(dot);
+                const float m_new = fmaxf(m, st);
+                l = l * __expf(m - m_new) + __expf(st - m_new);
+                m = m_new;
+                if (li == 0) sc[sr.row - c0] = st;
+                const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+                for (int x = 0; x < VPL; ++x) {
+                    const int vec = li + x * LPR;
+                    if (vec < VPR)
+                        *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + vec * 16) =
+                            *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB + vec * 16);
+                }
+            }
+        }
+        if (li == 0) red[g * RS] = m, red[g * RS + 1] = l;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float Mc = -CUDART_INF_F, Lc = 0.f;
+        for (int gg = 0; gg < NG; ++gg) Mc = fmaxf(Mc, red[gg * RS]);
+        for (int gg = 0; gg < NG; ++gg)
+            if (red[gg * RS] != -CUDART_INF_F) Lc += red[gg * RS + 1] * __expf(red[gg * RS] - Mc);
+        stat[0] = Mc, stat[1] = Lc;
+    }
+    cluster_sync_all();   // every slice's (max, sum) is visible cluster-wide; also a CTA barrier
+
+    // ---------------- global statistics of the (batch, head) ----------------
+    float M = -CUDART_INF_F, Lsum = 0.f;
+    for (int c = 0; c < C; ++c) M = fmaxf(M, ld_peer_smem_f32(stat, c));
+    for (int c = 0; c < C; ++c) {
+        const float mc = ld_peer_smem_f32(stat, c);
+        if (mc != -CUDART_INF_F) Lsum += ld_peer_smem_f32(stat + 1, c) * __expf(mc - M);
+    }
+    // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
+    // the torch-rounding mode divides exactly like torch's softmax does
+    const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
+    const float theta = Elem<T>::round(P.p * inv);
+    auto prob_of = [&](float s) -> float {
+        if (prune) return Elem<T>::round(__expf(s - M) * inv);
+        return Elem<T>::round(expf(s - M) / Lsum);
+    };
+
+    // ---------------- phase 2: prune, gather the surviving V rows ----------------
+    float2 acc2[VPL][E2];
+#pragma unroll
+    for (int x = 0; x < VPL; ++x)
+#pragma unroll
+        for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
+    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache) + (size_t)bh * P.Lmax * ROWB;
+    const int hi_mask = sr.ok ? min(c0 + chunk, sr.row + 1) : c0;   // rows whose mask bit this slice writes
+    for (int sub = c0; sub < hi_mask; sub += kFusedListCap) {
+        // Survivors are listed in row order (ballots first, then a prefix over the 32-row
+        // words), so the order of the floating-point sums below never depends on timing.
+        __syncthreads();
+        const int sub_hi = min(sub + kFusedListCap, hi_mask);
+        constexpr int kMine = (kFusedListCap / 32 + 4) / 5;   // 32-row words per warp and round
+        float my_p[kMine];
+#pragma unroll
+        for (int k = 0; k < kMine; ++k) {
+            const int base = sub + (warp + 5 * k) * 32;
+            my_p[k] = -1.f;
+            if (base >= sub_hi) continue;   // warp-uniform
+            const int i = base + lane;
+            const bool cached = i >= lo && i < hi;
+            float pr = 0.f;
+            bool keep = false;
+            if (cached) {
+                pr = prob_of(sc[i - c0]);
+                keep = prune ? !Elem<T>::leq(pr, theta) : true;
+            }
+            const unsigned bal = __ballot_sync(0xffffffffu, keep);
+            if (P.kept_mask != nullptr && lane == 0)
+                P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
+                    bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+            if (lane == 0) words[warp + 5 * k] = bal;
+            if (keep) my_p[k] = pr;
+        }
+        __syncthreads();
+        const int nwords = (sub_hi - sub + 31) >> 5;
+#pragma unroll
+        for (int k = 0; k < kMine; ++k) {
+            if (my_p[k] >= 0.f) {
+                const int w = warp + 5 * k;
+                int pos = __popc(words[w] & ((1u << lane) - 1u));
+                for (int ww = 0; ww < w; ++ww) pos += __popc(words[ww]);
+                list_idx[pos] = sub + w * 32 + lane, list_p[pos] = my_p[k];
+            }
+        }
+        if (tid == 0) {
+            int tot = 0;
+            for (int w = 0; w < nwords; ++w) tot += __popc(words[w]);
+            flags[1] = tot;
+        }
+        __syncthreads();
+        const int n = flags[1];
+        if (warp > 0) {
+            for (int base = 0; base < n; base += RB * NG) {
+                uint4 raw[RB][VPL];
+                float pr[RB];
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) {
+                    const int idx = base + uu * NG + g;
+                    const bool okr = idx < n;
+                    pr[uu] = okr ? list_p[idx] : 0.f;
+                    const int row = okr ? list_idx[idx] : lo;
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        raw[uu][x] = make_uint4(0, 0, 0, 0);
+                        if (okr && (kAllLanes || li + x * LPR < VPR))
+                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + (size_t)row * ROWB + (li + x * LPR) * 16));
+                    }
+                }
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) {
+                    const float2 p2 = make_float2(pr[uu], pr[uu]);
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x) {
+                        float2 v2[E2];
+                        Elem<T>::unpack2(raw[uu][x], v2);
+#pragma unroll
+                        for (int e = 0; e < E2; ++e) acc2[x][e] = __ffma2_rn(p2, v2[e], acc2[x][e]);
+                    }
+                }
+            }
+        }
+    }
+    // the new token is never pruned (attention.cu:1227-1256): append v, add P_t * v
+    if (warp > 0) {
+        if (owns_new && g == 0) {
+            const float pt = prob_of(sc[sr.row - c0]);
+            const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                const int vec = li + x * LPR;
+                if (vec < VPR) {
+                    const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + (size_t)bh * ROWB + vec * 16);
+                    *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
+                    float2 v2[E2];
+                    Elem<T>::unpack2(vraw, v2);
+#pragma unroll
+                    for (int e = 0; e < E2; ++e) {
+                        acc2[x][e].x = fmaf(pt, v2[e].x, acc2[x][e].x);
+                        acc2[x][e].y = fmaf(pt, v2[e].y, acc2[x][e].y);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) {
+            const int vec = li + x * LPR;
+            if (vec < VPR) {
+#pragma unroll
+                for (int e = 0; e < E2; e += 2)
+                    *reinterpret_cast<float4*>(red + g * RS + vec * EPV + 2 * e) =
+                        make_float4(acc2[x][e].x, acc2[x][e].y, acc2[x][e + 1].x, acc2[x][e + 1].y);
+            }
+        }
+    }
+    __syncthreads();
+    for (int d = tid; d < DH; d += kFusedThreads) {
+        float A = 0.f;
+        for (int gg = 0; gg < NG; ++gg) A += red[gg * RS + d];
+        accs[d] = A;
+    }
+    cluster_sync_all();   // every slice's partial output is visible cluster-wide
+    if (rank == 0) {
+        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+        for (int d = tid; d < DH; d += kFusedThreads) {
+            float A = 0.f;
+            for (int c = 0; c < C; ++c) A += ld_peer_smem_f32(accs + d, c);   // slice order: deterministic
+            Elem<T>::store(outp + d, sr.ok ? A : 0.f);
+        }
+    }
+    cluster_sync_all();   // peers keep their shared memory alive until CTA 0 has read it
+    if (tid == 0) {
+        if (flags[0]) atomicOr(P.status, kStatusWaitTimeout);
+        if (!sr.ok && rank == 0) atomicOr(P.status, kStatusBadLength);
+    }
+}
+
+}  // namespace ffa_dev
