@@ -1,11 +1,12 @@
-// Decode masked multi-head attention for sm_100a: streaming split-KV kernels.
+// Decode masked multi-head attention for sm_100a: launch glue for the kernels in
+// ffa_stream_kernel.cuh and ffa_prune_kernels.cuh, the cache-build kernel and a diagnostic.
 //
 // Replaces mmha::masked_multihead_attention_kernel_optimized (attention.cu:698-1295) and the
 // two cache-init kernels (attention.cu:1556-1609) of the reference.  The reference runs one
 // CTA per (batch, head) that walks the whole sequence serially and stages every score in
-// shared memory; here the flat list of (batch*head, row-tile) units is cut into equal
-// contiguous runs, one per CTA of a persistent grid, so all SMs stream from HBM whatever the
-// batch*head count and the sequence length is bounded by memory only.
+// shared memory; here the flat list of (batch*head, row-tile) units is cut into contiguous
+// runs, one per CTA of a persistent grid, so all SMs stream from HBM whatever the batch*head
+// count and the sequence length is bounded by memory only.
 //
 //   ffa_stream_kernel<T, DH, PASS_ONE>    p == 0: K and V tiles through a bulk-copy ring,
 //                                         online softmax, cross-CTA merge by the CTA that
