@@ -56,7 +56,7 @@ def lib() -> C.CDLL:
         L.ffa_workspace_bytes.restype = sz
         L.ffa_workspace_bind.argtypes = [vp, vp, sz, vp]
         L.ffa_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, f, i, vp, i, f, vp, vp]
-        L.ffa_attention_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, vp, f, i, vp, i, vp]
+        L.ffa_attention_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, vp, f, i, vp, i, f, vp, vp]
         L.ffa_device_status.argtypes = [vp, vp, C.POINTER(i)]
         L.ffa_attention_static_scratch.argtypes = [i, i, i, i, i, vp, vp, vp, vp, vp, vp, f, i, vp, vp, C.c_char_p, sz]
         L.ffa_selftest_wait_timeout.argtypes = [vp, C.c_uint, vp]

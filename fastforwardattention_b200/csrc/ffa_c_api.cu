@@ -461,9 +461,17 @@ int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* st
     return FFA_OK;
 }
 
-int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_cache, void* v_cache, void* out,
-                  float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding, float p,
-                  uint32_t* kept_mask, void* stream)
+namespace {
+
+struct PageArgs {
+    const int* table = nullptr;
+    int max_pages = 0, page_rows = 0;
+};
+
+// One decode step on contiguous caches (pages.table == nullptr) or page pools.
+int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_cache, void* v_cache, void* out,
+             float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding, float p, uint32_t* kept_mask,
+             const PageArgs& pages, void* stream)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
     if (plan->offline) return fail(FFA_ERR_ARG, "this plan was created offline (planning only) and cannot launch");
@@ -475,6 +483,7 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     if (seq_lengths == nullptr && !right_or_no_padding)
         return fail(FFA_ERR_ARG, "left padding (right_or_no_padding = 0) needs seq_lengths");
     if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
+    const bool paged = pages.table != nullptr;
     const bool twopass = p > 0.f || plan->mode == FFA_MODE_ROUND_LIKE_TORCH;
     const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
     const long long BH = (long long)plan->B * plan->H;
@@ -488,6 +497,7 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     P.partials = plan->partials, P.tickets = plan->tickets, P.status = plan->status;
     P.stats = plan->stats, P.scores = plan->scores;
     P.kept_mask = kept_mask, P.mask_words = (plan->Lmax + 31) / 32;
+    P.page_table = pages.table, P.max_pages = pages.max_pages, P.page_rows = pages.page_rows;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     if (twopass && plan->prune_path != 2) {
@@ -505,8 +515,10 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
         return fail(FFA_ERR_WORKSPACE, "this shape needs the two-kernel pruning path: bind a workspace sized with with_scores = 1");
 
     ffa_launch_t L;
-    int r = fit_launch(plan, cap, twopass ? 1 : 2, &L);
+    // the streaming kernel never lets a tile straddle a page: tiles are powers of two that divide it
+    int r = fit_launch(plan, cap, twopass ? 1 : 2, &L, /*pow2_tiles=*/paged);
     if (r != FFA_OK) return r;
+    if (paged && pages.page_rows % L.tile_rows != 0) return fail(FFA_ERR_ARG, "tile of %d rows does not divide the page", L.tile_rows);
     P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
     P.units_per_bh = cap / L.tile_rows + 1;
     P.parts_per_bh = L.parts_per_bh;
@@ -536,43 +548,29 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
     return FFA_OK;
 }
 
+}  // namespace
+
+int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_cache, void* v_cache, void* out,
+                  float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding, float p,
+                  uint32_t* kept_mask, void* stream)
+{
+    return run_step(plan, q, k, v, k_cache, v_cache, out, softmax_scale, t, seq_lengths, right_or_no_padding, p, kept_mask,
+                    PageArgs{}, stream);
+}
+
 int ffa_attention_paged(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_pool, void* v_pool,
                         const int* page_table, int max_pages, int page_rows, void* out, float softmax_scale, int t,
-                        const int* seq_lengths, int right_or_no_padding, void* stream)
+                        const int* seq_lengths, int right_or_no_padding, float p, uint32_t* kept_mask, void* stream)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
-    if (plan->offline) return fail(FFA_ERR_ARG, "this plan was created offline (planning only) and cannot launch");
-    if (!q || !k || !v || !k_pool || !v_pool || !out || !page_table) return fail(FFA_ERR_ARG, "null pointer");
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out))
-        return fail(FFA_ERR_ARG, "tensor pointers must be 16-byte aligned");
+    if (page_table == nullptr) return fail(FFA_ERR_ARG, "null page table");
     if (page_rows <= 0 || page_rows % 128 != 0) return fail(FFA_ERR_RANGE, "page_rows (%d) must be a positive multiple of 128", page_rows);
     if (max_pages <= 0 || (long long)max_pages * page_rows != plan->Lmax)
         return fail(FFA_ERR_RANGE, "max_pages * page_rows (%d * %d) must equal the plan's max_len (%d)", max_pages, page_rows, plan->Lmax);
-    if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
-    if (seq_lengths == nullptr && !right_or_no_padding)
-        return fail(FFA_ERR_ARG, "left padding (right_or_no_padding = 0) needs seq_lengths");
-    if (plan->mode != FFA_MODE_EXACT) return fail(FFA_ERR_ARG, "paged caches support the exact mode only");
-    if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
-    const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
-    FfaStepParams P;
-    std::memset(&P, 0, sizeof(P));
-    P.q = q, P.k = k, P.v = v, P.k_cache = k_pool, P.v_cache = v_pool, P.out = out;
-    P.seq_lengths = seq_lengths, P.right_or_no_padding = right_or_no_padding != 0;
-    P.B = plan->B, P.H = plan->H, P.Lmax = plan->Lmax, P.t = t;
-    P.scale = softmax_scale, P.p = 0.f;
-    P.partials = plan->partials, P.tickets = plan->tickets, P.status = plan->status;
-    P.page_table = page_table, P.max_pages = max_pages, P.page_rows = page_rows;
-    ffa_launch_t L;
-    int r = fit_launch(plan, cap, 2, &L, /*pow2_tiles=*/true);
-    if (r != FFA_OK) return r;
-    if (page_rows % L.tile_rows != 0) return fail(FFA_ERR_ARG, "tile of %d rows does not divide the page", L.tile_rows);
-    P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
-    P.units_per_bh = cap / L.tile_rows + 1;
-    P.parts_per_bh = L.parts_per_bh;
-    r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, 32 * (L.consumer_warps + 1), L.smem_bytes, static_cast<cudaStream_t>(stream));
-    if (r != 0) return cuda_fail(r, "paged attention launch");
-    g_launches.fetch_add(1);
-    return FFA_OK;
+    PageArgs pages;
+    pages.table = page_table, pages.max_pages = max_pages, pages.page_rows = page_rows;
+    return run_step(plan, q, k, v, k_pool, v_pool, out, softmax_scale, t, seq_lengths, right_or_no_padding, p, kept_mask, pages,
+                    stream);
 }
 
 int ffa_selftest_wait_timeout(ffa_plan_t* plan, unsigned int limit_ms, void* stream)

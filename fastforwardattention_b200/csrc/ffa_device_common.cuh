@@ -223,7 +223,8 @@ __device__ __forceinline__ SampleRange sample_range(const FfaStepParams& P, int 
 // Byte offset of cache row `row` of pair bh from the start of the cache (or page pool).
 // Contiguous slabs: [B*H, Lmax, Dh].  Paged: the pool is [pages, H, page_rows, Dh] and
 // page_table[b][row / page_rows] names the page; rows of one (pair, page) are contiguous, and
-// tiles never straddle pages because tile_rows divides page_rows.
+// the streaming kernel's tiles never straddle pages because tile_rows divides page_rows (the
+// fused pruning kernel splits a tile's copy at page boundaries instead).
 __device__ __forceinline__ size_t cache_row_offset(const FfaStepParams& P, int bh, int row, int rowb)
 {
     if (P.page_table == nullptr) return ((size_t)bh * P.Lmax + row) * rowb;

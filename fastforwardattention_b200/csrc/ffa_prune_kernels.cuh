@@ -107,13 +107,13 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
                     const int idx = base + uu * NG + g;
                     const bool okr = idx < n;
                     pr[uu] = okr ? list_p[idx] : 0.f;
-                    const int row = okr ? list_idx[idx] : 0;
+                    const size_t roff = okr ? cache_row_offset(P, bh, list_idx[idx], ROWB) : 0;
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
                         const int vec = li + x * LPR;
                         raw[uu][x] = make_uint4(0, 0, 0, 0);
                         if (okr && vec < VPR)
-                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + ((size_t)bh * P.Lmax + row) * ROWB + vec * 16));
+                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + roff + vec * 16));
                     }
                 }
 #pragma unroll
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
         // the new token is never pruned (attention.cu:1227-1256): append v, add P_t * v
         if (sr.ok && j0 <= jt && jt < j1 && g == 0) {
             const float pt = prob_of(sc[sr.row]);
-            const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+            const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
 #pragma unroll
             for (int x = 0; x < VPL; ++x) {
                 const int vec = li + x * LPR;
@@ -284,13 +284,22 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     // ---------------- phase 1: scores of this slice into shared memory ----------------
     if (warp == 0) {
         if (tid == 0) {
-            const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache) + ((size_t)bh * P.Lmax + lo) * ROWB;
+            const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache);
+            // rows of one page are contiguous; a tile that crosses a page boundary arrives as
+            // one copy per page, all counted on the same barrier (contiguous caches: one copy)
+            const int run_rows = P.page_table != nullptr ? P.page_rows : P.Lmax;
             uint32_t stage = 0, use = 0;
             for (int j = 0; j < ntiles; ++j) {
                 if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
-                const uint32_t bytes = (uint32_t)min(R, nrows - j * R) * ROWB;
-                mbar_expect_tx(bar_full + 8 * stage, bytes);
-                bulk_copy_g2s(ring + stage * tile_bytes, kc + (size_t)j * tile_bytes, bytes, bar_full + 8 * stage);
+                const int n = min(R, nrows - j * R);
+                mbar_expect_tx(bar_full + 8 * stage, (uint32_t)n * ROWB);
+                for (int done = 0; done < n;) {
+                    const int row = lo + j * R + done;
+                    const int seg = min(n - done, run_rows - row % run_rows);
+                    bulk_copy_g2s(ring + stage * tile_bytes + (uint32_t)done * ROWB, kc + cache_row_offset(P, bh, row, ROWB),
+                                  (uint32_t)seg * ROWB, bar_full + 8 * stage);
+                    done += seg;
+                }
                 if (++stage == (uint32_t)S) stage = 0, ++use;
             }
         }
@@ -378,7 +387,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
                 l = l * __expf(m - m_new) + __expf(st - m_new);
                 m = m_new;
                 if (li == 0) sc[sr.row - c0] = st;
-                const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+                const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
 #pragma unroll
                 for (int x = 0; x < VPL; ++x) {
                     const int vec = li + x * LPR;
@@ -422,7 +431,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     for (int x = 0; x < VPL; ++x)
 #pragma unroll
         for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
-    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache) + (size_t)bh * P.Lmax * ROWB;
+    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
     const int hi_mask = sr.ok ? min(c0 + chunk, sr.row + 1) : c0;   // rows whose mask bit this slice writes
     for (int sub = c0; sub < hi_mask; sub += kFusedListCap) {
         // Survivors are listed in row order (ballots first, then a prefix over the 32-row
@@ -478,12 +487,12 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
                     const int idx = base + uu * NG + g;
                     const bool okr = idx < n;
                     pr[uu] = okr ? list_p[idx] : 0.f;
-                    const int row = okr ? list_idx[idx] : lo;
+                    const size_t roff = okr ? cache_row_offset(P, bh, list_idx[idx], ROWB) : 0;
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
                         raw[uu][x] = make_uint4(0, 0, 0, 0);
                         if (okr && (kAllLanes || li + x * LPR < VPR))
-                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + (size_t)row * ROWB + (li + x * LPR) * 16));
+                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + roff + (li + x * LPR) * 16));
                     }
                 }
 #pragma unroll
@@ -504,7 +513,7 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     if (warp > 0) {
         if (owns_new && g == 0) {
             const float pt = prob_of(sc[sr.row - c0]);
-            const size_t row_off = ((size_t)bh * P.Lmax + sr.row) * ROWB;
+            const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
 #pragma unroll
             for (int x = 0; x < VPL; ++x) {
                 const int vec = li + x * LPR;

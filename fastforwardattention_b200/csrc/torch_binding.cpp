@@ -270,20 +270,25 @@ struct PagedEngine {
         c10::cuda::CUDAGuard guard(device);
         check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)(max_pages * page_rows), use_default_kernel_launch, device.index(), &plan),
               "plan");
-        const size_t n = ffa_workspace_bytes(plan, 0);
-        workspace = torch::empty({(int64_t)n}, torch::TensorOptions().dtype(torch::kUInt8).device(device));
-        auto stream = at::cuda::getCurrentCUDAStream();
-        check(ffa_workspace_bind(plan, workspace.data_ptr(), n, stream.stream()), "workspace");
-        stream.synchronize();
+        bind_workspace(false);
+        at::cuda::getCurrentCUDAStream().synchronize();
     }
     ~PagedEngine() { ffa_plan_destroy(plan); }
+    void bind_workspace(bool with_scores)
+    {
+        const size_t n = ffa_workspace_bytes(plan, with_scores);
+        workspace = torch::empty({(int64_t)n}, torch::TensorOptions().dtype(torch::kUInt8).device(device));
+        check(ffa_workspace_bind(plan, workspace.data_ptr(), n, at::cuda::getCurrentCUDAStream().stream()), "workspace");
+        has_scores = with_scores;
+    }
     PagedEngine(const PagedEngine&) = delete;
     PagedEngine& operator=(const PagedEngine&) = delete;
 
     torch::Tensor run(const torch::Tensor& q_, const torch::Tensor& k_, const torch::Tensor& v_, const torch::Tensor& table,
-                      double softmax_scale, int64_t t, const torch::Tensor* rows, c10::optional<torch::Tensor> out_opt)
+                      double softmax_scale, int64_t t, const torch::Tensor* rows, double p, c10::optional<torch::Tensor> out_opt)
     {
         const int64_t n = B * H * Dh;
+        TORCH_CHECK(p >= 0.0 && p <= 1.0, "PagedEngine: prob_thresh ", p, " outside [0, 1]");
         auto prep = [&](const torch::Tensor& x, const char* name) {
             TORCH_CHECK(x.is_cuda() && x.device() == device && dtype_code(x) == dtype && x.numel() == n, "PagedEngine: ", name,
                         " must hold batch*heads*head_dim = ", n, " elements of the pool's dtype on the pool's device");
@@ -304,21 +309,48 @@ struct PagedEngine {
         torch::Tensor out = out_opt.has_value() ? *out_opt : torch::empty({B, H, Dh}, q.options());
         TORCH_CHECK(out.is_cuda() && out.device() == device && dtype_code(out) == dtype && out.is_contiguous() && out.numel() == n,
                     "PagedEngine: out must be a contiguous tensor of batch*heads*head_dim elements on the pool's device");
-        check(ffa_attention_paged(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr<int>(),
-                                  (int)max_pages, (int)page_rows, out.data_ptr(), (float)softmax_scale, (int)t,
-                                  rows ? sl.data_ptr<int>() : nullptr, 1, at::cuda::getCurrentCUDAStream().stream()),
-              "paged attention");
+        uint32_t* mask_ptr = nullptr;
+        if (want_mask && p > 0.0) {
+            if (!kept_mask.defined())
+                kept_mask = torch::zeros({B, H, (max_pages * page_rows + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
+            mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
+        }
+        auto call = [&]() {
+            return ffa_attention_paged(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kp.data_ptr(), vp.data_ptr(),
+                                       table.data_ptr<int>(), (int)max_pages, (int)page_rows, out.data_ptr(), (float)softmax_scale,
+                                       (int)t, rows ? sl.data_ptr<int>() : nullptr, 1, (float)p, mask_ptr,
+                                       at::cuda::getCurrentCUDAStream().stream());
+        };
+        int rc = call();
+        if (rc == FFA_ERR_WORKSPACE && !has_scores) {
+            // a shape the fused pruning kernel cannot hold: grow the workspace by the score scratch, once
+            bind_workspace(true);
+            rc = call();
+        }
+        check(rc, "paged attention");
         return out;
     }
     torch::Tensor attention(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor table, double scale, int64_t t,
-                            c10::optional<torch::Tensor> out)
+                            double prob_thresh, c10::optional<torch::Tensor> out)
     {
-        return run(q, k, v, table, scale, t, nullptr, out);
+        return run(q, k, v, table, scale, t, nullptr, prob_thresh, out);
     }
     torch::Tensor attention_per_sample(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor table, double scale,
-                                       torch::Tensor rows, c10::optional<torch::Tensor> out)
+                                       torch::Tensor rows, double prob_thresh, c10::optional<torch::Tensor> out)
     {
-        return run(q, k, v, table, scale, 0, &rows, out);
+        return run(q, k, v, table, scale, 0, &rows, prob_thresh, out);
+    }
+    void set_mode(const std::string& m)
+    {
+        TORCH_CHECK(m == "exact" || m == "round_like_torch", "PagedEngine: mode must be 'exact' or 'round_like_torch'");
+        check(ffa_plan_set_mode(plan, m == "exact" ? FFA_MODE_EXACT : FFA_MODE_ROUND_LIKE_TORCH), "mode");
+    }
+    void set_prune_path(int path) { check(ffa_plan_set_prune_path(plan, path), "prune path"); }
+    void record_kept_mask(bool on) { want_mask = on; }
+    torch::Tensor get_kept_mask()
+    {
+        TORCH_CHECK(kept_mask.defined(), "PagedEngine: no kept mask recorded (record_kept_mask(True), then a call with prob_thresh > 0)");
+        return kept_mask;
     }
     int device_status()
     {
@@ -330,10 +362,11 @@ struct PagedEngine {
     }
 
     ffa_plan_t* plan = nullptr;
-    torch::Tensor kp, vp, workspace;
+    torch::Tensor kp, vp, workspace, kept_mask;
     c10::Device device{c10::kCUDA, 0};
     int64_t B = 0, H = 0, Dh = 0, page_rows = 0, max_pages = 0;
     int dtype = 0;
+    bool has_scores = false, want_mask = false;
 };
 
 }  // namespace
@@ -376,9 +409,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     py::class_<PagedEngine>(m, "PagedEngine")
         .def(py::init<torch::Tensor, torch::Tensor, int64_t, int64_t, bool>(), py::arg("k_pool"), py::arg("v_pool"), py::arg("batch"),
              py::arg("max_pages"), py::arg("use_default_kernel_launch") = false)
-        .def("attention", &PagedEngine::attention, "exact decode step, every sequence at row curr_timestep", py::arg("q"), py::arg("k"),
-             py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("curr_timestep"), py::arg("out") = py::none())
-        .def("attention_per_sample", &PagedEngine::attention_per_sample, "exact decode step, sequence b at row rows[b]", py::arg("q"),
-             py::arg("k"), py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("rows"), py::arg("out") = py::none())
+        .def("attention", &PagedEngine::attention, "decode step, every sequence at row curr_timestep", py::arg("q"), py::arg("k"),
+             py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("curr_timestep"), py::arg("prob_thresh") = 0.0,
+             py::arg("out") = py::none())
+        .def("attention_per_sample", &PagedEngine::attention_per_sample, "decode step, sequence b at row rows[b]", py::arg("q"),
+             py::arg("k"), py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("rows"),
+             py::arg("prob_thresh") = 0.0, py::arg("out") = py::none())
+        .def("set_mode", &PagedEngine::set_mode, "'exact' (default) or 'round_like_torch'")
+        .def("set_prune_path", &PagedEngine::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
+        .def("record_kept_mask", &PagedEngine::record_kept_mask)
+        .def("get_kept_mask", &PagedEngine::get_kept_mask)
         .def("device_status", &PagedEngine::device_status);
 }

@@ -4,7 +4,8 @@ The reference allocates `max_len` rows for every sequence at construction
 (torch_ffa_api.cpp:65-66); with many concurrent sequences of unknown final length that is
 mostly unused memory.  Here a pool of fixed-size pages ([pages, heads, page_rows, head_dim] for
 K and for V) is shared; every sequence has a row of the page table and gets a new page only
-when its next token crosses a page boundary.  Exact attention only (p = 0).
+when its next token crosses a page boundary.  Exact attention and the pruned step
+(prob_thresh > 0) both run over the pool.
 
     pool = PagePool(num_pages=4096, heads=32, head_dim=128, dtype=torch.bfloat16, device="cuda")
     seqs = PagedFastForwardAttn(pool, K, V, max_len=32768, lengths=prompt_lengths)   # K, V: [B, H, Lp, Dh]
@@ -82,12 +83,13 @@ class PagedFastForwardAttn:
             self.table[b, i] = page
 
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
-                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """One decode step: sequence b appends k, v at row lengths[b] and attends rows 0..lengths[b]."""
+                  prob_thresh: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One decode step: sequence b appends k, v at row lengths[b] and attends rows 0..lengths[b];
+        prob_thresh means what it means in FastForwardAttn.attention."""
         for b, n in enumerate(self.lengths):
             if n % self.pool.page_rows == 0:
                 self._ensure_page(b, n)
-        res = self.engine.attention_per_sample(q, k, v, self.table, softmax_scale, self.rows, out=out)
+        res = self.engine.attention_per_sample(q, k, v, self.table, softmax_scale, self.rows, prob_thresh, out=out)
         self.rows += 1
         self.lengths = [n + 1 for n in self.lengths]
         return res

@@ -141,16 +141,17 @@ int ffa_attention(ffa_plan_t* plan, const void* q, const void* k, const void* v,
                   void* out, float softmax_scale, int t, const int* seq_lengths, int right_or_no_padding,
                   float p, uint32_t* kept_mask, void* stream);
 
-/* ffa_attention on PAGED caches (exact mode, p == 0).  k_pool and v_pool are page pools laid
- * out [pages, heads, page_rows, head_dim]; page_table [batch, max_pages] (int32, device) names
- * the pool page that holds rows [i*page_rows, (i+1)*page_rows) of sequence b.  Only pages that
- * hold rows 0..row of a sequence are dereferenced, so sequences of different lengths share one
- * pool and a sequence takes memory as it grows.  page_rows is a multiple of 128 and
- * max_pages * page_rows equals the plan's max_len.  No counterpart in the reference, which
- * allocates max_len rows per sequence up front (torch_ffa_api.cpp:65-66). */
+/* ffa_attention on PAGED caches; p, kept_mask and the plan's mode mean what they mean there.
+ * k_pool and v_pool are page pools laid out [pages, heads, page_rows, head_dim]; page_table
+ * [batch, max_pages] (int32, device) names the pool page that holds rows
+ * [i*page_rows, (i+1)*page_rows) of sequence b.  Only pages that hold rows 0..row of a sequence
+ * are dereferenced, so sequences of different lengths share one pool and a sequence takes
+ * memory as it grows.  page_rows is a multiple of 128 and max_pages * page_rows equals the
+ * plan's max_len.  No counterpart in the reference, which allocates max_len rows per sequence
+ * up front (torch_ffa_api.cpp:65-66). */
 int ffa_attention_paged(ffa_plan_t* plan, const void* q, const void* k, const void* v, void* k_pool, void* v_pool,
                         const int* page_table, int max_pages, int page_rows, void* out, float softmax_scale, int t,
-                        const int* seq_lengths, int right_or_no_padding, void* stream);
+                        const int* seq_lengths, int right_or_no_padding, float p, uint32_t* kept_mask, void* stream);
 
 /* The exact (p == 0, no per-sample lengths) decode step with NO caller-provided workspace and
  * no allocation of any kind inside the call.  It has no counterpart in the reference; it
