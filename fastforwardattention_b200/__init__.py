@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import importlib
 
-__all__ = ["FastForwardAttn", "ShardedFastForwardAttn", "GraphedStep", "PagePool", "PagedFastForwardAttn", "launch_count"]
+__all__ = ["FastForwardAttn", "ShardedFastForwardAttn", "GraphedStep", "GraphedLayers", "PagePool", "PagedFastForwardAttn", "launch_count"]
 
 
 def _extension():
@@ -33,6 +33,10 @@ def __getattr__(name):
         from . import paged
 
         return getattr(paged, name)
+    if name == "GraphedLayers":
+        from .graphed import GraphedLayers
+
+        return GraphedLayers
     if name == "GraphedStep":
         from .graphed import GraphedStep
 

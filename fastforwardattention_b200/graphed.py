@@ -52,3 +52,69 @@ class GraphedStep:
         self.graph.replay()
         self.next_row += 1
         return self.out
+
+
+class GraphedLayers:
+    """Every layer's attention for one token -- and whatever the caller computes between the
+    layers -- recorded in ONE CUDA graph.
+
+    A decoder runs its layers one after another, each with its own KV cache, and the launch
+    and argument-checking cost of L separate calls is what bounds short-sequence decoding
+    (the reference's HF forks make one `attention` call per layer per token,
+    modeling_opt.py:201-226).  Here the caller hands over one engine per layer and a `body`:
+
+        def body(x, attend):                 # x: the static input tensor of a token
+            for i, layer in enumerate(layers):
+                q, k, v = layer.project(x)   # any torch ops
+                x = x + layer.out_proj(attend(i, q, k, v))    # attend -> [B, H, Dh]
+            return x
+
+        step = GraphedLayers(engines, softmax_scale, first_row=prompt_len, body=body, example_input=x0)
+        for token in range(n):
+            y = step(x)                      # a view of a static buffer, valid until the next call
+
+    `attend(i, q, k, v)` runs engine i with the row index read from device memory; the graph
+    ends with one increment of that index, shared by all layers.  `body` is traced once for a
+    warm-up (so that libraries it calls create their handles outside the capture) and once for
+    the capture; it must be free of host synchronisation and of data-dependent control flow.
+    The warm-up writes row `first_row` of every layer's cache, which the first real step
+    overwrites.
+    """
+
+    def __init__(self, engines, softmax_scale: float, first_row: int, body, example_input: torch.Tensor,
+                 prob_thresh: float = 0.0):
+        if not engines:
+            raise ValueError("need at least one engine")
+        shapes = {tuple(e.get_cache()[0].shape) for e in engines}
+        if len(shapes) != 1:
+            raise ValueError("all layers must share one cache shape")
+        kc = engines[0].get_cache()[0]
+        B, H, Lmax, Dh = kc.shape
+        if not 0 <= first_row < Lmax:
+            raise ValueError(f"first_row {first_row} outside [0, {Lmax})")
+        dev = kc.device
+        self.engines, self.max_len, self.next_row = list(engines), Lmax, first_row
+        self.x = example_input.detach().clone().to(dev)
+        self.rows = torch.full((B,), first_row, dtype=torch.int32, device=dev)
+        self.outs = [torch.zeros(B, H, Dh, dtype=kc.dtype, device=dev) for _ in engines]
+
+        def attend(i: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+            return self.engines[i].attention_per_sample(q, k, v, softmax_scale, self.rows, prob_thresh, out=self.outs[i])
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            body(self.x, attend)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"), torch.no_grad():
+            self.y = body(self.x, attend)
+            self.rows.add_(1)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if self.next_row >= self.max_len:
+            raise RuntimeError(f"the caches are full ({self.max_len} rows)")
+        self.x.copy_(x, non_blocking=True)
+        self.graph.replay()
+        self.next_row += 1
+        return self.y

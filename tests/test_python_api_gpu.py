@@ -180,6 +180,53 @@ def test_graphed_step_helper():
     assert ffa.device_status() == 0
 
 
+def test_graphed_layers_whole_token_in_one_graph():
+    """A toy decoder (three layers, fp32 projections between the attention calls) replayed from
+    one CUDA graph gives what the same layers give when called one by one."""
+    from fastforwardattention_b200 import FastForwardAttn, GraphedLayers
+
+    dt, B, H, Dh, Lp, n, NL = torch.float32, 2, 4, 64, 70, 4, 3
+    E = H * Dh
+    g = torch.Generator().manual_seed(31)
+    Ks = [torch.randn(B, H, Lp, Dh, generator=g) for _ in range(NL)]
+    Vs = [torch.randn(B, H, Lp, Dh, generator=g) for _ in range(NL)]
+    W = [[(torch.randn(E, E, generator=g) / E ** 0.5).cuda() for _ in range(4)] for _ in range(NL)]
+
+    def make_body(calls):
+        def body(x, attend):
+            for i in range(NL):
+                q, k, v = ((x @ W[i][j]).view(B, H, 1, Dh) for j in range(3))
+                calls.append(i)
+                x = x + attend(i, q, k, v).reshape(B, E) @ W[i][3]
+            return x
+        return body
+
+    graphed = [FastForwardAttn(Ks[i].cuda(), Vs[i].cuda(), Lp + n, False) for i in range(NL)]
+    eager = [FastForwardAttn(Ks[i].cuda(), Vs[i].cuda(), Lp + n, False) for i in range(NL)]
+    calls = []
+    step = GraphedLayers(graphed, Dh ** -0.5, first_row=Lp, body=make_body(calls), example_input=torch.zeros(B, E))
+    assert calls == [0, 1, 2] * 2                       # traced twice (warm-up + capture), never again
+    orcs = [O.DecodeOracle(Ks[i], Vs[i], Lp + n, compute_dtype=torch.float64) for i in range(NL)]
+    for t in range(n):
+        x = torch.randn(B, E, generator=g)
+        y = step(x.cuda()).clone()
+        rows = torch.full((B,), Lp + t, dtype=torch.int32, device="cuda")
+        want = make_body([])(x.cuda(), lambda i, q, k, v: eager[i].attention_per_sample(q, k, v, Dh ** -0.5, rows, 0))
+        assert torch.equal(y, want)                     # same kernels, same launch shapes
+        # and against the oracle, layer by layer, in float64
+        xr = x.double()
+        for i in range(NL):
+            Wd = [w.cpu().double() for w in W[i]]
+            q, k, v = ((xr @ Wd[j]).view(B, H, 1, Dh) for j in range(3))
+            a = orcs[i].step(q.float(), k.float(), v.float(), Dh ** -0.5, Lp + t)
+            xr = xr + a.reshape(B, E).double() @ Wd[3]
+        assert (y.cpu().double() - xr).abs().max().item() <= 2e-3 * xr.abs().max().item()
+    assert len(calls) == 2 * NL
+    with pytest.raises(RuntimeError, match="full"):
+        step(x.cuda())
+    assert all(e.device_status() == 0 for e in graphed)
+
+
 @pytest.mark.parametrize("dt", [torch.float16, torch.float32])
 def test_adopt_prefilled_caches_and_grow(dt):
     """Prefill writes K and V straight into the cache slabs (no copy at construction); the cache
