@@ -65,6 +65,10 @@ struct ffa_plan {
     float* partials;
     float* scores;
     int max_grid;
+    // output gather over peer memory
+    int peer_world, peer_rank;
+    void* peer_buf[FFA_MAX_PEERS];
+    uint32_t peer_seq;
 };
 
 namespace {
@@ -594,6 +598,122 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status)
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return cuda_fail(e, "status read");
     if (*status != 0) return fail(FFA_ERR_DEVICE, "device status word = %d", *status);
+    return FFA_OK;
+}
+
+// ---- output gather over peer memory -------------------------------------------------------------
+// Buffer of every rank: half 0 | half 1 | flags[FFA_MAX_PEERS]; a half is [B][world][H * Dh] elements.
+
+static size_t peer_half_bytes(const ffa_plan* p, int world)
+{
+    return align_up((size_t)p->B * world * p->H * p->Dh * elem_size(p->dtype), 256);
+}
+
+size_t ffa_peer_gather_bytes(const ffa_plan_t* plan, int world)
+{
+    if (plan == nullptr || world < 1 || world > FFA_MAX_PEERS) return 0;
+    return 2 * peer_half_bytes(plan, world) + 256;
+}
+
+int ffa_peer_mem_alloc(size_t bytes, void** ptr, unsigned char* handle)
+{
+    if (ptr == nullptr || handle == nullptr || bytes == 0) return fail(FFA_ERR_ARG, "null pointer or zero size");
+    static_assert(sizeof(cudaIpcMemHandle_t) == FFA_PEER_HANDLE_BYTES, "handle size");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "peer buffer allocation");
+    e = cudaMemset(p, 0, bytes);   // arrival flags start at zero
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(e, "peer buffer export");
+    }
+    std::memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return FFA_OK;
+}
+
+int ffa_peer_mem_open(const unsigned char* handle, void** ptr)
+{
+    if (ptr == nullptr || handle == nullptr) return fail(FFA_ERR_ARG, "null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    const cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e, "peer buffer import");
+    return FFA_OK;
+}
+
+int ffa_peer_mem_close(void* ptr)
+{
+    if (ptr == nullptr) return FFA_OK;
+    const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    return e == cudaSuccess ? FFA_OK : cuda_fail(e, "peer buffer close");
+}
+
+int ffa_peer_mem_free(void* ptr)
+{
+    if (ptr == nullptr) return FFA_OK;
+    const cudaError_t e = cudaFree(ptr);
+    return e == cudaSuccess ? FFA_OK : cuda_fail(e, "peer buffer free");
+}
+
+int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each,
+                           unsigned int steps_done)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (world == 0) {   // detach
+        plan->peer_world = 0;
+        return FFA_OK;
+    }
+    if (buffers == nullptr) return fail(FFA_ERR_ARG, "null buffer list");
+    if (world < 1 || world > FFA_MAX_PEERS) return fail(FFA_ERR_RANGE, "world %d outside [1, %d]", world, FFA_MAX_PEERS);
+    if (rank < 0 || rank >= world) return fail(FFA_ERR_RANGE, "rank %d outside [0, %d)", rank, world);
+    if (bytes_each < ffa_peer_gather_bytes(plan, world))
+        return fail(FFA_ERR_WORKSPACE, "peer buffers of %zu bytes, need %zu", bytes_each, ffa_peer_gather_bytes(plan, world));
+    for (int r = 0; r < world; ++r) {
+        if (buffers[r] == nullptr) return fail(FFA_ERR_ARG, "buffer of rank %d is null", r);
+        if ((reinterpret_cast<uintptr_t>(buffers[r]) & 255u) != 0) return fail(FFA_ERR_ARG, "buffer of rank %d is not 256-byte aligned", r);
+    }
+    for (int r = 0; r < world; ++r) plan->peer_buf[r] = buffers[r];
+    plan->peer_world = world, plan->peer_rank = rank, plan->peer_seq = steps_done;
+    return FFA_OK;
+}
+
+unsigned int ffa_peer_gather_steps(const ffa_plan_t* plan) { return plan == nullptr ? 0u : plan->peer_seq; }
+
+int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, int phases, unsigned int wait_limit_ms, const void** gathered,
+                    void* stream)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (plan->peer_world < 1) return fail(FFA_ERR_ARG, "no peer buffers attached (ffa_peer_gather_attach)");
+    if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
+    if (phases < 1 || phases > 3) return fail(FFA_ERR_ARG, "phases must be 1 (push), 2 (wait) or 3 (both)");
+    if ((phases & 1) && (out_local == nullptr || !aligned16(out_local))) return fail(FFA_ERR_ARG, "out_local must be a 16-byte aligned pointer");
+    if (wait_limit_ms == 0 || wait_limit_ms > 2000) return fail(FFA_ERR_RANGE, "wait_limit_ms must be in [1, 2000]");
+    if (phases & 1) ++plan->peer_seq;   // a push opens a new step; a lone wait refers to the latest push
+    if (plan->peer_seq == 0) return fail(FFA_ERR_ARG, "wait before the first push");
+    const int world = plan->peer_world;
+    const size_t half = peer_half_bytes(plan, world);
+    FfaPeerGatherParams G;
+    std::memset(&G, 0, sizeof(G));
+    G.out_local = out_local;
+    for (int r = 0; r < world; ++r) {
+        char* base = static_cast<char*>(plan->peer_buf[r]);
+        G.peer_half[r] = base + (plan->peer_seq & 1u) * half;
+        G.peer_flags[r] = reinterpret_cast<uint32_t*>(base + 2 * half);
+    }
+    G.local_flags = G.peer_flags[plan->peer_rank];
+    G.status = plan->status;
+    G.wait_limit_ns = (unsigned long long)wait_limit_ms * 1000000ull;
+    G.seq = plan->peer_seq;
+    G.world = world, G.rank = plan->peer_rank, G.B = plan->B;
+    G.row_bytes = plan->H * plan->Dh * elem_size(plan->dtype);
+    G.phases = phases;
+    const int r = ffa_k_peer_gather(G, static_cast<cudaStream_t>(stream));
+    if (r != 0) return cuda_fail(r, "peer gather launch");
+    g_launches.fetch_add(1);
+    if (gathered != nullptr) *gathered = G.peer_half[plan->peer_rank];
     return FFA_OK;
 }
 

@@ -36,6 +36,20 @@ struct FfaStepParams {
     int max_pages, page_rows;
 };
 
+// One all-gather of the step outputs over peer memory.  Every rank owns a buffer of two halves
+// [B][world * row_bytes] (used alternately) followed by `world` arrival flags.
+struct FfaPeerGatherParams {
+    const void* out_local;     // [B][row_bytes]: this rank's outputs
+    void* peer_half[8];        // the half in use this step, in every rank's buffer (own included)
+    uint32_t* peer_flags[8];   // the flag array of every rank's buffer
+    const uint32_t* local_flags;  // this rank's own flag array
+    int* status;               // device status word
+    unsigned long long wait_limit_ns;
+    uint32_t seq;              // step number, starts at 1; flags only grow
+    int world, rank, B, row_bytes;
+    int phases;                // bit 0: push the slice and raise the flags; bit 1: wait for the peers' flags
+};
+
 // dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.
 int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes);
 int ffa_k_cache_init(int dtype, int BH, int prompt_len, int src_len, int max_len, int head_dim, const void* k_src,
@@ -53,3 +67,5 @@ int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, in
 int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows);
 // diagnostic: a bounded wait that must time out (see ffa_selftest_wait_timeout)
 int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, cudaStream_t stream);
+// all-gather of the step outputs: one CTA per rank
+int ffa_k_peer_gather(const FfaPeerGatherParams& G, cudaStream_t stream);

@@ -16,7 +16,9 @@
 #include <torch/extension.h>
 
 #include <memory>
+#include <string>
 #include <utility>
+#include <vector>
 
 #include "ffa_c_api.h"
 
@@ -100,6 +102,10 @@ struct FastForwardAttn {
         ffa_plan_t* np = nullptr;
         check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)new_max_len, use_default, device.index(), &np), "plan");
         check(ffa_plan_set_mode(np, mode), "mode");
+        if (peer_world > 0) {
+            std::vector<void*> bufs(peer_ptrs.begin(), peer_ptrs.end());
+            check(ffa_peer_gather_attach(np, peer_world, peer_rank, bufs.data(), peer_bytes, ffa_peer_gather_steps(plan)), "peer gather");
+        }
         stream.synchronize();   // the old slabs may be freed once the copy is done
         ffa_plan_destroy(plan);
         plan = np, k_cache = nk, v_cache = nv, Lmax = new_max_len;
@@ -109,7 +115,11 @@ struct FastForwardAttn {
     }
     int64_t max_len() const { return Lmax; }
 
-    ~FastForwardAttn() { ffa_plan_destroy(plan); }
+    ~FastForwardAttn()
+    {
+        peer_gather_free();   // the owner keeps the engine alive while any peer may still gather
+        ffa_plan_destroy(plan);
+    }
     FastForwardAttn(const FastForwardAttn&) = delete;
     FastForwardAttn& operator=(const FastForwardAttn&) = delete;
 
@@ -242,12 +252,84 @@ struct FastForwardAttn {
         return s;
     }
 
+    // ---- all-gather of the outputs over peer memory (ffa_peer_gather_* of the C ABI) ----
+    // Allocates this rank's buffer; the returned 64-byte handle is what the other ranks open.
+    py::bytes peer_gather_alloc(int64_t world)
+    {
+        TORCH_CHECK(peer_own == nullptr, "FastForwardAttn: the peer buffer is already allocated");
+        c10::cuda::CUDAGuard guard(device);
+        const size_t n = ffa_peer_gather_bytes(plan, (int)world);
+        TORCH_CHECK(n > 0, "FastForwardAttn: world ", world, " outside [1, ", FFA_MAX_PEERS, "]");
+        unsigned char handle[FFA_PEER_HANDLE_BYTES];
+        check(ffa_peer_mem_alloc(n, &peer_own, handle), "peer buffer");
+        peer_bytes = n;
+        return py::bytes(reinterpret_cast<const char*>(handle), sizeof(handle));
+    }
+    int64_t peer_gather_ptr() const { return (int64_t)reinterpret_cast<uintptr_t>(peer_own); }
+    int64_t peer_mem_open(const std::string& handle)
+    {
+        TORCH_CHECK(handle.size() == FFA_PEER_HANDLE_BYTES, "FastForwardAttn: a peer handle has ", FFA_PEER_HANDLE_BYTES, " bytes");
+        c10::cuda::CUDAGuard guard(device);
+        void* p = nullptr;
+        check(ffa_peer_mem_open(reinterpret_cast<const unsigned char*>(handle.data()), &p), "peer buffer");
+        return (int64_t)reinterpret_cast<uintptr_t>(p);
+    }
+    void peer_mem_close(int64_t ptr)
+    {
+        c10::cuda::CUDAGuard guard(device);
+        check(ffa_peer_mem_close(reinterpret_cast<void*>((uintptr_t)ptr)), "peer buffer");
+    }
+    // ptrs: every rank's buffer in rank order (ptrs[rank] is this rank's own); close_on_free: the
+    // other ranks' pointers came from peer_mem_open and are closed by peer_gather_free
+    void peer_gather_attach(int64_t world, int64_t rank, std::vector<int64_t> ptrs, bool close_on_free)
+    {
+        TORCH_CHECK(peer_own != nullptr, "FastForwardAttn: peer_gather_alloc first");
+        TORCH_CHECK((int64_t)ptrs.size() == world && rank >= 0 && rank < world, "FastForwardAttn: need one buffer pointer per rank");
+        TORCH_CHECK(ptrs[rank] == peer_gather_ptr(), "FastForwardAttn: ptrs[rank] must be this rank's own buffer");
+        std::vector<void*> bufs;
+        for (int64_t x : ptrs) bufs.push_back(reinterpret_cast<void*>((uintptr_t)x));
+        check(ffa_peer_gather_attach(plan, (int)world, (int)rank, bufs.data(), peer_bytes, 0), "peer gather");
+        peer_ptrs = bufs, peer_world = (int)world, peer_rank = (int)rank, peer_close = close_on_free;
+    }
+    // out_local [B, H, Dh] -> [B, world*H, Dh] holding every rank's outputs.  The result aliases the
+    // peer buffer: it stays valid until this engine's next-but-one gather.
+    torch::Tensor peer_gather(const torch::Tensor& out_local, int64_t phases, int64_t wait_limit_ms)
+    {
+        TORCH_CHECK(peer_world > 0, "FastForwardAttn: peer_gather_attach first");
+        TORCH_CHECK(out_local.is_cuda() && out_local.device() == device && dtype_code(out_local) == dtype && out_local.is_contiguous() &&
+                        out_local.numel() == B * H * Dh,
+                    "FastForwardAttn: out_local must be a contiguous [batch, heads, head_dim] tensor of the cache's dtype and device");
+        c10::cuda::CUDAGuard guard(device);
+        const void* g = nullptr;
+        check(ffa_peer_gather(plan, out_local.data_ptr(), (int)phases, (unsigned)wait_limit_ms, &g, at::cuda::getCurrentCUDAStream().stream()),
+              "peer gather");
+        return torch::from_blob(const_cast<void*>(g), {B, (int64_t)peer_world * H, Dh}, out_local.options());
+    }
+    // Collective by contract: every rank has synchronised its device and passed a host barrier, so
+    // no peer can still store into this rank's buffer.
+    void peer_gather_free()
+    {
+        if (peer_own == nullptr) return;
+        c10::cuda::CUDAGuard guard(device);
+        ffa_peer_gather_attach(plan, 0, 0, nullptr, 0, 0);
+        if (peer_close)
+            for (int r = 0; r < peer_world; ++r)
+                if (r != peer_rank) ffa_peer_mem_close(peer_ptrs[r]);
+        ffa_peer_mem_free(peer_own);
+        peer_own = nullptr, peer_world = 0, peer_ptrs.clear();
+    }
+
     ffa_plan_t* plan = nullptr;
     torch::Tensor k_cache, v_cache, workspace, kept_mask;
     c10::Device device{c10::kCUDA, 0};
     int64_t B = 0, H = 0, Dh = 0, Lmax = 0;
     int dtype = 0, mode = FFA_MODE_EXACT;
     bool has_scores = false, want_mask = false, use_default = false;
+    void* peer_own = nullptr;
+    std::vector<void*> peer_ptrs;
+    size_t peer_bytes = 0;
+    int peer_world = 0, peer_rank = 0;
+    bool peer_close = false;
 };
 
 // Decode steps over PAGED caches (exact attention): the K and V pools are
@@ -405,7 +487,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("launch_shape", &FastForwardAttn::launch_shape, py::arg("t"))
         .def("record_kept_mask", &FastForwardAttn::record_kept_mask)
         .def("get_kept_mask", &FastForwardAttn::get_kept_mask)
-        .def("device_status", &FastForwardAttn::device_status, "synchronises; 0 when the kernels recorded no error");
+        .def("device_status", &FastForwardAttn::device_status, "synchronises; 0 when the kernels recorded no error")
+        .def("peer_gather_alloc", &FastForwardAttn::peer_gather_alloc, py::arg("world"))
+        .def("peer_gather_ptr", &FastForwardAttn::peer_gather_ptr)
+        .def("peer_mem_open", &FastForwardAttn::peer_mem_open, py::arg("handle"))
+        .def("peer_mem_close", &FastForwardAttn::peer_mem_close, py::arg("ptr"))
+        .def("peer_gather_attach", &FastForwardAttn::peer_gather_attach, py::arg("world"), py::arg("rank"), py::arg("ptrs"),
+             py::arg("close_on_free") = true)
+        .def("peer_gather", &FastForwardAttn::peer_gather, py::arg("out_local"), py::arg("phases") = 3, py::arg("wait_limit_ms") = 2000,
+             "all-gather of the outputs over peer memory: [B, H, Dh] -> [B, world*H, Dh]")
+        .def("peer_gather_free", &FastForwardAttn::peer_gather_free);
     py::class_<PagedEngine>(m, "PagedEngine")
         .def(py::init<torch::Tensor, torch::Tensor, int64_t, int64_t, bool>(), py::arg("k_pool"), py::arg("v_pool"), py::arg("batch"),
              py::arg("max_pages"), py::arg("use_default_kernel_launch") = false)

@@ -4,7 +4,9 @@ Every (batch, head) pair is an independent problem (the reference's grid is one 
 pair, attention.cu:1303), so rank r of N owns heads [r*H/N, (r+1)*H/N) for the whole
 generation: its slice of the prompt K/V, its KV-cache shard, its slice of every q/k/v.  No
 cache row ever crosses NVLink.  The only collective is one all-gather of the [B, H/N, Dh]
-outputs, issued when the caller asks for the full [B, H, Dh] tensor.
+outputs, issued when the caller asks for the full [B, H, Dh] tensor: through the process
+group (NCCL), or -- after enable_peer_gather() -- by the engine's own kernel, which stores
+every rank's slice straight into the peers' memory and needs no permutation afterwards.
 
 One process per GPU (torchrun); the process group decides the backend (NCCL on GPUs).
 """
@@ -54,6 +56,7 @@ class ShardedFastForwardAttn:
         self.B, self.H_local, _, self.Dh = K_local.shape
         self.H = self.H_local * self.world
         self._gathered = None
+        self._peer = False
 
     def get_cache(self):
         return self.engine.get_cache()
@@ -65,11 +68,63 @@ class ShardedFastForwardAttn:
         out = self.engine.attention(q_local, k_local, v_local, softmax_scale, curr_timestep, prob_thresh)
         return self.gather(out) if gather else out
 
+    def enable_peer_gather(self) -> bool:
+        """Switch gather() to the engine's peer-memory all-gather.  Collective: every rank of the
+        group calls it.  Each rank allocates one small device buffer, the ranks exchange the
+        buffers' inter-process handles through the group and map each other's memory.  Returns
+        False -- on every rank alike, and gather() keeps using the process group -- when any
+        rank could not allocate, export or map a buffer."""
+        if self.world == 1 or self._peer:
+            return self._peer
+        eng, handle = self.engine, None
+        try:
+            handle = bytes(eng.peer_gather_alloc(self.world))
+        except RuntimeError:
+            pass
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=self.group)
+        ptrs, ok = [], handle is not None and all(h is not None for h in handles)
+        if ok:
+            try:
+                for r, h in enumerate(handles):
+                    ptrs.append(eng.peer_gather_ptr() if r == self.rank else eng.peer_mem_open(h))
+            except RuntimeError:
+                ok = False
+        oks = [None] * self.world
+        dist.all_gather_object(oks, ok, group=self.group)
+        if all(oks):
+            eng.peer_gather_attach(self.world, self.rank, ptrs, True)
+            self._peer = True
+            return True
+        for r, p in enumerate(ptrs):
+            if r != self.rank:
+                eng.peer_mem_close(p)
+        dist.barrier(group=self.group)   # nobody still maps another rank's buffer
+        if handle is not None:
+            eng.peer_gather_free()
+        return False
+
+    def close(self) -> None:
+        """Collective: releases the peer-gather buffers.  Every rank finishes its queued work and
+        meets at a barrier first, because a buffer must outlive every store a peer aims at it."""
+        if not self._peer:
+            return
+        kc = self.engine.get_cache()[0]
+        if kc.is_cuda:
+            torch.cuda.synchronize(kc.device)
+        dist.barrier(group=self.group)
+        self.engine.peer_gather_free()
+        self._peer = False
+
     def gather(self, out_local: torch.Tensor) -> torch.Tensor:
-        """All-gather of the per-rank outputs into [B, H, Dh] (rank-major heads)."""
+        """All-gather of the per-rank outputs into [B, H, Dh] (rank-major heads).  After
+        enable_peer_gather() the result aliases a buffer that is reused by the next-but-one
+        gather; copy it to keep it longer."""
         if self.world == 1:
             return out_local
         out_local = out_local.contiguous()
+        if self._peer:
+            return self.engine.peer_gather(out_local)
         if self._gathered is None or self._gathered.dtype != out_local.dtype or self._gathered.device != out_local.device:
             self._gathered = torch.empty(self.world, self.B, self.H_local, self.Dh, dtype=out_local.dtype,
                                          device=out_local.device)

@@ -183,6 +183,40 @@ int ffa_attention_static_scratch(int dtype, int batch, int heads, int head_dim, 
  * clears it.  The reference only printf()s cudaGetLastError (attention.cu:1444-1451). */
 int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
 
+/* ---- All-gather of the step outputs over peer memory (heads sharded over the GPUs of a node).
+ * No counterpart in the reference, which runs on one GPU.  Every rank allocates one buffer of
+ * ffa_peer_gather_bytes(plan, world) bytes with ffa_peer_mem_alloc (device memory, zero-filled,
+ * plus a 64-byte handle another process of the node can open with ffa_peer_mem_open), collects
+ * the `world` buffer pointers in rank order (its own included) and attaches them to its plan
+ * (steps_done = 0 for fresh buffers; a plan that replaces another over the same buffers passes
+ * the old plan's ffa_peer_gather_steps, because arrival flags only grow; world = 0 detaches).
+ * ffa_peer_gather then stores this rank's out_local [batch, heads, head_dim] (heads = the
+ * plan's local head count) into every rank's buffer at heads [rank*heads, (rank+1)*heads),
+ * raises one arrival flag per peer, and waits -- for at most wait_limit_ms (1..2000), after
+ * which FFA_STATUS_WAIT_TIMEOUT is set in the status word and the kernel returns -- until
+ * every peer's slice of the same step has arrived.  *gathered is this rank's
+ * [batch, world*heads, head_dim] result; it stays valid until the rank's next-but-one call
+ * (two halves are used alternately), provided every rank makes the same sequence of calls.
+ * phases: 3 = both; 1 = store and signal only, 2 = wait only (a wait refers to the latest
+ * push) -- the split exists so that several ranks can be driven from ONE stream of one GPU,
+ * all pushes before all waits; a kernel that waits must never be queued ahead of the kernel
+ * that signals it on the same GPU.
+ * Teardown: no rank may free its buffer while a peer can still store into it; synchronise the
+ * device and pass a host barrier before ffa_peer_mem_close (the peers') / ffa_peer_mem_free
+ * (the own). */
+#define FFA_MAX_PEERS 8
+#define FFA_PEER_HANDLE_BYTES 64
+size_t ffa_peer_gather_bytes(const ffa_plan_t* plan, int world);
+int ffa_peer_mem_alloc(size_t bytes, void** ptr, unsigned char* handle /* [FFA_PEER_HANDLE_BYTES] */);
+int ffa_peer_mem_open(const unsigned char* handle, void** ptr);
+int ffa_peer_mem_close(void* ptr);
+int ffa_peer_mem_free(void* ptr);
+int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each,
+                           unsigned int steps_done);
+unsigned int ffa_peer_gather_steps(const ffa_plan_t* plan);
+int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, int phases, unsigned int wait_limit_ms,
+                    const void** gathered, void* stream);
+
 /* Diagnostic, no counterpart in the reference: launches one warp that waits, for at most
  * limit_ms (1..2000), on a copy barrier nothing completes.  The wait must give up, the kernel
  * must return normally, and the next ffa_device_status() must report FFA_STATUS_WAIT_TIMEOUT

@@ -133,3 +133,101 @@ def test_gather_fails_instead_of_hanging_when_a_rank_leaves():
         p.join(30)
     assert res[1] == "left"
     assert res[0].startswith("error after"), res
+
+
+class PeerStandIn(OracleEngine):
+    """OracleEngine plus the peer-gather surface of the extension class.  Memory cannot be shared
+    between CPU ranks here, so peer_gather itself goes through the group; what the test checks
+    is the set-up protocol around it."""
+    fail_on_rank = -1
+
+    def __init__(self, K, V, max_len, use_default):
+        super().__init__(K, V, max_len, use_default)
+        self.rank = dist.get_rank()
+        self.log = []
+
+    def peer_gather_alloc(self, world):
+        if self.rank == self.fail_on_rank:
+            raise RuntimeError("no memory for the peer buffer")
+        self.log.append(("alloc", world))
+        return bytes([self.rank]) * 64
+
+    def peer_gather_ptr(self):
+        return 1000 + self.rank
+
+    def peer_mem_open(self, handle):
+        assert len(handle) == 64 and len(set(handle)) == 1
+        self.log.append(("open", handle[0]))
+        return 2000 + handle[0]
+
+    def peer_mem_close(self, ptr):
+        self.log.append(("close", ptr))
+
+    def peer_gather_attach(self, world, rank, ptrs, close_on_free):
+        self.log.append(("attach", world, rank, tuple(ptrs), close_on_free))
+
+    def peer_gather(self, out_local):
+        self.log.append(("gather",))
+        parts = [torch.empty_like(out_local) for _ in range(dist.get_world_size())]
+        dist.all_gather(parts, out_local)
+        return torch.cat(parts, dim=1)
+
+    def peer_gather_free(self):
+        self.log.append(("free",))
+
+
+def _peer_worker(rank, world, port, q_out, fail_on_rank):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fastforwardattention_b200.sharded import ShardedFastForwardAttn, shard_heads
+        from oracle.ffa_oracle import DecodeOracle
+
+        PeerStandIn.fail_on_rank = fail_on_rank
+        g = torch.Generator().manual_seed(1)
+        B, H, Dh, Lp = 2, 4, 64, 5
+        K = torch.randn(B, H, Lp, Dh, generator=g)
+        V = torch.randn(B, H, Lp, Dh, generator=g)
+        full = DecodeOracle(K, V, Lp + 1)
+        eng = ShardedFastForwardAttn(shard_heads(K, rank, world, H), shard_heads(V, rank, world, H), Lp + 1,
+                                     False, engine_factory=PeerStandIn)
+        enabled = eng.enable_peer_gather()
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g) for _ in range(3))
+        want = full.step(q, k, v, 0.125, Lp)
+        got = eng.attention(*(shard_heads(x, rank, world, H) for x in (q, k, v)), 0.125, Lp, gather=True)
+        err = (got - want).abs().max().item()
+        eng.close()
+        q_out.put((rank, enabled, err, eng.engine.log))
+        q_out.close()
+        q_out.join_thread()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fail_on_rank", [-1, 1])
+def test_peer_gather_setup_protocol(fail_on_rank):
+    """Every rank maps every other rank's buffer, in rank order, with its own pointer in its own
+    place; if one rank cannot set up, all ranks fall back to the process group together."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q, fail_on_rank)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, enabled, err, log in res:
+        assert err < 1e-6
+        other = 1 - rank
+        if fail_on_rank < 0:
+            assert enabled
+            want_ptrs = (1000, 2001) if rank == 0 else (2000, 1001)
+            assert log == [("alloc", 2), ("open", other), ("attach", 2, rank, want_ptrs, True), ("gather",), ("free",)]
+        else:
+            assert not enabled
+            assert ("gather",) not in log and not any(e[0] == "attach" for e in log)
+            if rank != fail_on_rank:
+                assert log[0] == ("alloc", 2) and log[-1] == ("free",)     # its own buffer is released again

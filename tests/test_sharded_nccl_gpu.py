@@ -1,6 +1,7 @@
-"""Head-sharded decode on real GPUs: two ranks, one GPU each, NCCL.  Each rank runs the CUDA
-engine on its head shard; local outputs and the all-gathered tensor are checked against the
-oracle evaluated on all heads.  Needs two visible GPUs (skipped otherwise)."""
+"""Head-sharded decode on real GPUs: two ranks, one GPU each.  Each rank runs the CUDA engine on
+its head shard; local outputs and the all-gathered tensor (fp32: NCCL; fp16: the engine's own
+gather over peer memory) are checked against the oracle evaluated on all heads.  Needs two
+visible GPUs (skipped otherwise)."""
 import os
 import socket
 import sys
@@ -42,6 +43,9 @@ def _worker(rank, world, port, q_out):
             eng = ShardedFastForwardAttn(shard_heads(K, rank, world, H).to(dev), shard_heads(V, rank, world, H).to(dev),
                                          Lp + steps, False)
             lo, hi = head_range(H, rank, world)
+            peer = dt == torch.float16 and eng.enable_peer_gather()     # fp16: the engine's own gather; fp32: NCCL
+            if dt == torch.float16:
+                assert peer, "the peer-memory gather could not be set up"
             for i in range(steps):
                 q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
                 want = full.step(q, k, v, Dh ** -0.5, Lp + i)
@@ -54,6 +58,7 @@ def _worker(rank, world, port, q_out):
                 else:
                     assert torch.isfinite(got).all()
             assert eng.engine.device_status() == 0
+            eng.close()
         q_out.put((rank, worst))
     finally:
         dist.destroy_process_group()
