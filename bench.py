@@ -193,6 +193,8 @@ def main():
     ap.add_argument("--workload", default="long-32768", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: output all-gather by the engine's peer-memory kernel (default) or by NCCL")
     ap.add_argument("--launch", default="", help="tile_rows,stages,consumer_warps,ctas_per_sm override (tuning)")
     args = ap.parse_args()
     full = CONFIGS[args.workload]
@@ -234,6 +236,10 @@ def main():
             engines.append(FastForwardAttn(K, V, w.max_len, False))
         del K, V
     torch.cuda.empty_cache()
+    gather_kind = "none"
+    if world > 1:
+        peer_ok = args.gather == "peer" and all([s.enable_peer_gather() for s in sharded])
+        gather_kind = "peer-memory kernel" if peer_ok else "nccl all_gather_into_tensor"
     if args.launch:
         for e in engines:
             e.set_launch(*[int(x) for x in args.launch.split(",")])
@@ -361,7 +367,8 @@ def main():
                              "traffic": TRAFFIC_RATIO * per_launch_alg if (TRAFFIC_RATIO and w.p == 0) else None},
                 "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "steps/s",
                         "h2d_bytes_per_step": 3 * w.B * w.H * w.Dh * es, "d2h_bytes_per_step": out_h.numel() * es,
-                        "includes": "pinned-host q/k/v upload, attention, output all-gather (N>1), output download, sync"},
+                        "includes": "pinned-host q/k/v upload, attention, output all-gather (N>1), output download, sync",
+                        "gather": gather_kind},
                 "gpu_launches": int(launches), "launch_shape": dict(shape), "device_status": status,
                 "clocks": clocks.summary(wall0, wall1), "replicas": nrep}
         if world == 1 and not args.no_cpu_baseline:
@@ -372,6 +379,8 @@ def main():
                                     "sample": smp.describe(n)}
         print(json.dumps(line))
     if world > 1:
+        for sh in sharded:
+            sh.close()
         dist.destroy_process_group()
 
 
