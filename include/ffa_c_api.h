@@ -201,6 +201,7 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
  * push) -- the split exists so that several ranks can be driven from ONE stream of one GPU,
  * all pushes before all waits; a kernel that waits must never be queued ahead of the kernel
  * that signals it on the same GPU.
+ * The step number travels as a launch argument: do not record this call in a CUDA graph.
  * Teardown: no rank may free its buffer while a peer can still store into it; synchronise the
  * device and pass a host barrier before ffa_peer_mem_close (the peers') / ffa_peer_mem_free
  * (the own). */
