@@ -305,18 +305,27 @@ struct FastForwardAttn {
               "peer gather");
         return torch::from_blob(const_cast<void*>(g), {B, (int64_t)peer_world * H, Dh}, out_local.options());
     }
-    // Collective by contract: every rank has synchronised its device and passed a host barrier, so
-    // no peer can still store into this rank's buffer.
-    void peer_gather_free()
+    // Teardown is collective and has two steps with a host barrier before each: (1) every rank has
+    // synchronised its device, so no store is in flight -> peer_gather_detach unmaps the peers'
+    // buffers; (2) every rank has unmapped -> peer_gather_free releases this rank's own buffer (an
+    // exported allocation must outlive every mapping of it).
+    void peer_gather_detach()
     {
-        if (peer_own == nullptr) return;
+        if (peer_world == 0) return;
         c10::cuda::CUDAGuard guard(device);
         ffa_peer_gather_attach(plan, 0, 0, nullptr, 0, 0);
         if (peer_close)
             for (int r = 0; r < peer_world; ++r)
                 if (r != peer_rank) ffa_peer_mem_close(peer_ptrs[r]);
+        peer_world = 0, peer_ptrs.clear();
+    }
+    void peer_gather_free()
+    {
+        peer_gather_detach();
+        if (peer_own == nullptr) return;
+        c10::cuda::CUDAGuard guard(device);
         ffa_peer_mem_free(peer_own);
-        peer_own = nullptr, peer_world = 0, peer_ptrs.clear();
+        peer_own = nullptr;
     }
 
     ffa_plan_t* plan = nullptr;
@@ -496,7 +505,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
              py::arg("close_on_free") = true)
         .def("peer_gather", &FastForwardAttn::peer_gather, py::arg("out_local"), py::arg("phases") = 3, py::arg("wait_limit_ms") = 2000,
              "all-gather of the outputs over peer memory: [B, H, Dh] -> [B, world*H, Dh]")
-        .def("peer_gather_free", &FastForwardAttn::peer_gather_free);
+        .def("peer_gather_detach", &FastForwardAttn::peer_gather_detach, "unmap the peers' buffers (teardown step 1)")
+        .def("peer_gather_free", &FastForwardAttn::peer_gather_free, "release this rank's buffer (teardown step 2)");
     py::class_<PagedEngine>(m, "PagedEngine")
         .def(py::init<torch::Tensor, torch::Tensor, int64_t, int64_t, bool>(), py::arg("k_pool"), py::arg("v_pool"), py::arg("batch"),
              py::arg("max_pages"), py::arg("use_default_kernel_launch") = false)

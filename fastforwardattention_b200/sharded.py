@@ -106,12 +106,16 @@ class ShardedFastForwardAttn:
 
     def close(self) -> None:
         """Collective: releases the peer-gather buffers.  Every rank finishes its queued work and
-        meets at a barrier first, because a buffer must outlive every store a peer aims at it."""
+        meets at a barrier (no store can still be aimed at anyone's buffer), unmaps the peers'
+        buffers, meets again (an exported buffer must outlive every mapping of it), and frees
+        its own."""
         if not self._peer:
             return
         kc = self.engine.get_cache()[0]
         if kc.is_cuda:
             torch.cuda.synchronize(kc.device)
+        dist.barrier(group=self.group)
+        self.engine.peer_gather_detach()
         dist.barrier(group=self.group)
         self.engine.peer_gather_free()
         self._peer = False

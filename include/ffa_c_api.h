@@ -202,9 +202,10 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
  * all pushes before all waits; a kernel that waits must never be queued ahead of the kernel
  * that signals it on the same GPU.
  * The step number travels as a launch argument: do not record this call in a CUDA graph.
- * Teardown: no rank may free its buffer while a peer can still store into it; synchronise the
- * device and pass a host barrier before ffa_peer_mem_close (the peers') / ffa_peer_mem_free
- * (the own). */
+ * Teardown: no rank may unmap or free a buffer while a peer can still store into it, and an
+ * exported buffer must outlive every mapping of it: synchronise the device, pass a host
+ * barrier, ffa_peer_mem_close the peers' buffers, pass a second barrier, ffa_peer_mem_free the
+ * own. */
 #define FFA_MAX_PEERS 8
 #define FFA_PEER_HANDLE_BYTES 64
 size_t ffa_peer_gather_bytes(const ffa_plan_t* plan, int world);

@@ -172,6 +172,9 @@ class PeerStandIn(OracleEngine):
         dist.all_gather(parts, out_local)
         return torch.cat(parts, dim=1)
 
+    def peer_gather_detach(self):
+        self.log.append(("detach",))
+
     def peer_gather_free(self):
         self.log.append(("free",))
 
@@ -225,7 +228,7 @@ def test_peer_gather_setup_protocol(fail_on_rank):
         if fail_on_rank < 0:
             assert enabled
             want_ptrs = (1000, 2001) if rank == 0 else (2000, 1001)
-            assert log == [("alloc", 2), ("open", other), ("attach", 2, rank, want_ptrs, True), ("gather",), ("free",)]
+            assert log == [("alloc", 2), ("open", other), ("attach", 2, rank, want_ptrs, True), ("gather",), ("detach",), ("free",)]
         else:
             assert not enabled
             assert ("gather",) not in log and not any(e[0] == "attach" for e in log)
