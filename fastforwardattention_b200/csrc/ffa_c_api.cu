@@ -691,6 +691,11 @@ int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, int phases, unsigne
     if (phases < 1 || phases > 3) return fail(FFA_ERR_ARG, "phases must be 1 (push), 2 (wait) or 3 (both)");
     if ((phases & 1) && (out_local == nullptr || !aligned16(out_local))) return fail(FFA_ERR_ARG, "out_local must be a 16-byte aligned pointer");
     if (wait_limit_ms == 0 || wait_limit_ms > 2000) return fail(FFA_ERR_RANGE, "wait_limit_ms must be in [1, 2000]");
+    // the step number is a launch argument: a replayed graph would repeat it and every wait
+    // would pass at once on flags of an earlier step
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+        return fail(FFA_ERR_ARG, "the peer gather cannot be recorded in a CUDA graph");
     if (phases & 1) ++plan->peer_seq;   // a push opens a new step; a lone wait refers to the latest push
     if (plan->peer_seq == 0) return fail(FFA_ERR_ARG, "wait before the first push");
     const int world = plan->peer_world;

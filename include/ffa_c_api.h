@@ -201,7 +201,8 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
  * push) -- the split exists so that several ranks can be driven from ONE stream of one GPU,
  * all pushes before all waits; a kernel that waits must never be queued ahead of the kernel
  * that signals it on the same GPU.
- * The step number travels as a launch argument: do not record this call in a CUDA graph.
+ * The step number travels as a launch argument, so the call refuses (FFA_ERR_ARG) a stream that
+ * is being captured into a CUDA graph.
  * Teardown: no rank may unmap or free a buffer while a peer can still store into it, and an
  * exported buffer must outlive every mapping of it: synchronise the device, pass a host
  * barrier, ffa_peer_mem_close the peers' buffers, pass a second barrier, ffa_peer_mem_free the

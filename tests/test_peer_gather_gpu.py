@@ -114,4 +114,12 @@ def test_bad_arguments_raise():
     with pytest.raises(RuntimeError, match="phases"):
         e.peer_gather(o, 0, 100)
     assert torch.equal(e.peer_gather(o), o)           # a world of one gathers its own slice
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="CUDA graph"):
+        with torch.cuda.stream(side), torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            e.peer_gather(o)                          # a replay would repeat the step number
+    torch.cuda.synchronize()
+    assert torch.equal(e.peer_gather(o), o)           # the refusal left everything usable
     e.peer_gather_free()
