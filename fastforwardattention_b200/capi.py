@@ -18,7 +18,7 @@ SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_des
            "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
            "ffa_plan_get_prune_launch", "ffa_cache_copy", "ffa_attention_paged", "ffa_peer_gather_bytes",
            "ffa_peer_mem_alloc", "ffa_peer_mem_open", "ffa_peer_mem_close", "ffa_peer_mem_free", "ffa_peer_gather_attach",
-           "ffa_peer_gather_steps", "ffa_peer_gather"]
+           "ffa_peer_gather"]
 
 
 class Launch(C.Structure):
@@ -68,10 +68,8 @@ def lib() -> C.CDLL:
         L.ffa_peer_mem_open.argtypes = [C.c_char_p, C.POINTER(vp)]
         L.ffa_peer_mem_close.argtypes = [vp]
         L.ffa_peer_mem_free.argtypes = [vp]
-        L.ffa_peer_gather_attach.argtypes = [vp, i, i, C.POINTER(vp), sz, C.c_uint]
-        L.ffa_peer_gather_steps.argtypes = [vp]
-        L.ffa_peer_gather_steps.restype = C.c_uint
-        L.ffa_peer_gather.argtypes = [vp, vp, i, C.c_uint, C.POINTER(vp), vp]
+        L.ffa_peer_gather_attach.argtypes = [vp, i, i, C.POINTER(vp), sz]
+        L.ffa_peer_gather.argtypes = [vp, vp, vp, i, C.c_uint, vp]
         L.ffa_launch_count.restype = C.c_ulonglong
         L.ffa_last_error.restype = C.c_char_p
         _lib = L

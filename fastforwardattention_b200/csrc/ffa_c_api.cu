@@ -68,7 +68,6 @@ struct ffa_plan {
     // output gather over peer memory
     int peer_world, peer_rank;
     void* peer_buf[FFA_MAX_PEERS];
-    uint32_t peer_seq;
 };
 
 namespace {
@@ -602,7 +601,8 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status)
 }
 
 // ---- output gather over peer memory -------------------------------------------------------------
-// Buffer of every rank: half 0 | half 1 | flags[FFA_MAX_PEERS]; a half is [B][world][H * Dh] elements.
+// Staging buffer of every rank: half 0 | half 1 | flags[FFA_MAX_PEERS], step counter, ticket (256 bytes);
+// a half is [B][world][H * Dh] elements.
 
 static size_t peer_half_bytes(const ffa_plan* p, int world)
 {
@@ -658,8 +658,7 @@ int ffa_peer_mem_free(void* ptr)
     return e == cudaSuccess ? FFA_OK : cuda_fail(e, "peer buffer free");
 }
 
-int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each,
-                           unsigned int steps_done)
+int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
     if (world == 0) {   // detach
@@ -676,49 +675,33 @@ int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* b
         if ((reinterpret_cast<uintptr_t>(buffers[r]) & 255u) != 0) return fail(FFA_ERR_ARG, "buffer of rank %d is not 256-byte aligned", r);
     }
     for (int r = 0; r < world; ++r) plan->peer_buf[r] = buffers[r];
-    plan->peer_world = world, plan->peer_rank = rank, plan->peer_seq = steps_done;
+    plan->peer_world = world, plan->peer_rank = rank;
     return FFA_OK;
 }
 
-unsigned int ffa_peer_gather_steps(const ffa_plan_t* plan) { return plan == nullptr ? 0u : plan->peer_seq; }
-
-int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, int phases, unsigned int wait_limit_ms, const void** gathered,
-                    void* stream)
+int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, void* gathered, int phases, unsigned int wait_limit_ms, void* stream)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
     if (plan->peer_world < 1) return fail(FFA_ERR_ARG, "no peer buffers attached (ffa_peer_gather_attach)");
     if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
     if (phases < 1 || phases > 3) return fail(FFA_ERR_ARG, "phases must be 1 (push), 2 (wait) or 3 (both)");
     if ((phases & 1) && (out_local == nullptr || !aligned16(out_local))) return fail(FFA_ERR_ARG, "out_local must be a 16-byte aligned pointer");
+    if (gathered == nullptr || !aligned16(gathered)) return fail(FFA_ERR_ARG, "gathered must be a 16-byte aligned pointer");
     if (wait_limit_ms == 0 || wait_limit_ms > 2000) return fail(FFA_ERR_RANGE, "wait_limit_ms must be in [1, 2000]");
-    // the step number is a launch argument: a replayed graph would repeat it and every wait
-    // would pass at once on flags of an earlier step
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
-        return fail(FFA_ERR_ARG, "the peer gather cannot be recorded in a CUDA graph");
-    if (phases & 1) ++plan->peer_seq;   // a push opens a new step; a lone wait refers to the latest push
-    if (plan->peer_seq == 0) return fail(FFA_ERR_ARG, "wait before the first push");
     const int world = plan->peer_world;
-    const size_t half = peer_half_bytes(plan, world);
     FfaPeerGatherParams G;
     std::memset(&G, 0, sizeof(G));
-    G.out_local = out_local;
-    for (int r = 0; r < world; ++r) {
-        char* base = static_cast<char*>(plan->peer_buf[r]);
-        G.peer_half[r] = base + (plan->peer_seq & 1u) * half;
-        G.peer_flags[r] = reinterpret_cast<uint32_t*>(base + 2 * half);
-    }
-    G.local_flags = G.peer_flags[plan->peer_rank];
+    G.out_local = out_local, G.gathered = gathered;
+    for (int r = 0; r < world; ++r) G.peer_base[r] = plan->peer_buf[r];
+    G.half_bytes = peer_half_bytes(plan, world);
     G.status = plan->status;
     G.wait_limit_ns = (unsigned long long)wait_limit_ms * 1000000ull;
-    G.seq = plan->peer_seq;
     G.world = world, G.rank = plan->peer_rank, G.B = plan->B;
     G.row_bytes = plan->H * plan->Dh * elem_size(plan->dtype);
     G.phases = phases;
     const int r = ffa_k_peer_gather(G, static_cast<cudaStream_t>(stream));
     if (r != 0) return cuda_fail(r, "peer gather launch");
     g_launches.fetch_add(1);
-    if (gathered != nullptr) *gathered = G.peer_half[plan->peer_rank];
     return FFA_OK;
 }
 

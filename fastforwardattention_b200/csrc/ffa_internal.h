@@ -36,18 +36,17 @@ struct FfaStepParams {
     int max_pages, page_rows;
 };
 
-// One all-gather of the step outputs over peer memory.  Every rank owns a buffer of two halves
-// [B][world * row_bytes] (used alternately) followed by `world` arrival flags.
+// One all-gather of the step outputs over peer memory.  Every rank owns a staging buffer: two
+// halves [B][world * row_bytes] (used alternately), then flags[8], the step counter, a ticket.
 struct FfaPeerGatherParams {
     const void* out_local;     // [B][row_bytes]: this rank's outputs
-    void* peer_half[8];        // the half in use this step, in every rank's buffer (own included)
-    uint32_t* peer_flags[8];   // the flag array of every rank's buffer
-    const uint32_t* local_flags;  // this rank's own flag array
+    void* gathered;            // [B][world * row_bytes]: the result, this rank's own memory
+    void* peer_base[8];        // every rank's staging buffer (own included)
+    size_t half_bytes;
     int* status;               // device status word
     unsigned long long wait_limit_ns;
-    uint32_t seq;              // step number, starts at 1; flags only grow
     int world, rank, B, row_bytes;
-    int phases;                // bit 0: push the slice and raise the flags; bit 1: wait for the peers' flags
+    int phases;                // bit 0: push the slice and raise the flags; bit 1: wait for the peers' flags, collect
 };
 
 // dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.

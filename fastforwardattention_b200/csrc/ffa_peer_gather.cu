@@ -3,9 +3,17 @@
 // Heads are sharded over the GPUs of a node, so the only data that ever crosses NVLink is the
 // [batch, heads/N, head_dim] output of a step -- tens of kilobytes.  For a message that small a
 // collective library's launch and protocol cost is several times the wire time, so every rank
-// PUSHES its slice straight into each peer's buffer with 16-byte stores, raises one flag per
-// peer, and waits (bounded) for the flags of the slices it receives.  The destination is laid
-// out [batch, N * heads/N, head_dim], so the gathered tensor needs no permutation afterwards.
+// PUSHES its slice straight into a staging buffer of each peer with 16-byte stores, raises one
+// flag per peer, waits (bounded) for the flag of the slice it receives from that peer, and
+// copies the slice to its place in the caller's [batch, N * heads/N, head_dim] result -- no
+// permutation afterwards.
+//
+// Staging buffer of a rank: half 0 | half 1 | flags[8] | step counter | ticket.  A half is
+// [batch][N][heads/N * head_dim]; the two halves alternate by step so that a peer already in
+// step s+1 never overwrites what this rank still reads for step s (a peer cannot be two steps
+// ahead: its wait of step s+1 needs this rank's flag of step s+1).  Flags hold step numbers and
+// only grow.  The step number lives in the rank's own buffer and is advanced by the kernel
+// (last CTA out, through the ticket), so every launch argument is the same for every step.
 //
 // One CTA per peer.  Sending never waits, so no rank can block another; a wait that runs out
 // sets the time-out bit of the status word and the kernel returns normally.
@@ -35,36 +43,67 @@ constexpr int kGatherPushThreads = 256;
 __global__ void __launch_bounds__(kGatherPushThreads) ffa_peer_gather_kernel(const FfaPeerGatherParams G)
 {
     const int r = blockIdx.x, tid = threadIdx.x;   // this CTA talks to rank r
-    if (G.phases & 1) {
-        // slice of batch row b goes to bytes [(b * world + rank) * row_bytes, +row_bytes) of the destination
-        const int vec_per_row = G.row_bytes >> 4;
-        const long long total = (long long)G.B * vec_per_row;
+    const bool push = (G.phases & 1) != 0, wait = (G.phases & 2) != 0;
+    unsigned char* own = static_cast<unsigned char*>(G.peer_base[G.rank]);
+    uint32_t* own_tail = reinterpret_cast<uint32_t*>(own + 2 * G.half_bytes);   // flags[8], then counter, ticket
+    volatile uint32_t* counter = own_tail + 16;
+    // a push opens step counter + 1; a lone wait refers to the latest push
+    const uint32_t seq = *counter + (push ? 1u : 0u);
+    const size_t half_off = (size_t)(seq & 1u) * G.half_bytes;
+    const int vec_per_row = G.row_bytes >> 4;
+    const long long total = (long long)G.B * vec_per_row;
+    // the slice of batch row b sits at bytes [(b * world + rank) * row_bytes, +row_bytes)
+    auto slot = [&](long long i, int rank) -> size_t {
+        const long long b = i / vec_per_row;
+        return ((size_t)b * G.world + rank) * G.row_bytes + (size_t)(i - b * vec_per_row) * 16;
+    };
+
+    if (push) {
         const uint4* src = static_cast<const uint4*>(G.out_local);
-        unsigned char* dst = static_cast<unsigned char*>(G.peer_half[r]);
-        for (long long i = tid; i < total; i += kGatherPushThreads) {
-            const long long b = i / vec_per_row;
-            const int x = (int)(i - b * vec_per_row);
-            *reinterpret_cast<uint4*>(dst + ((size_t)b * G.world + G.rank) * G.row_bytes + (size_t)x * 16) = src[i];
-        }
-        if (r != G.rank) {
+        if (r == G.rank) {   // the own slice goes straight to the result
+            unsigned char* dst = static_cast<unsigned char*>(G.gathered);
+            for (long long i = tid; i < total; i += kGatherPushThreads) *reinterpret_cast<uint4*>(dst + slot(i, G.rank)) = src[i];
+        } else {
+            unsigned char* dst = static_cast<unsigned char*>(G.peer_base[r]) + half_off;
+            for (long long i = tid; i < total; i += kGatherPushThreads) *reinterpret_cast<uint4*>(dst + slot(i, G.rank)) = src[i];
             __threadfence_system();   // every thread's stores are performed at the peer before the flag
             __syncthreads();
-            if (tid == 0) st_release_sys(G.peer_flags[r] + G.rank, G.seq);
+            if (tid == 0) st_release_sys(reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(G.peer_base[r]) + 2 * G.half_bytes) + G.rank, seq);
         }
     }
-    if ((G.phases & 2) && r != G.rank && tid == 0) {
+    if (wait && r != G.rank) {
         // rank r's slice of this step has landed once its flag has reached this step's number
-        const unsigned long long t0 = global_timer_ns();
-        bool ok = false;
-        for (;;) {
-            if ((int32_t)(ld_acquire_sys(G.local_flags + r) - G.seq) >= 0) {
-                ok = true;
-                break;
+        if (tid == 0) {
+            const unsigned long long t0 = global_timer_ns();
+            bool ok = false;
+            for (;;) {
+                if ((int32_t)(ld_acquire_sys(own_tail + r) - seq) >= 0) {
+                    ok = true;
+                    break;
+                }
+                if (global_timer_ns() - t0 > G.wait_limit_ns) break;
+                __nanosleep(200);
             }
-            if (global_timer_ns() - t0 > G.wait_limit_ns) break;
-            __nanosleep(200);
+            if (!ok) atomicOr(G.status, kStatusWaitTimeout);
         }
-        if (!ok) atomicOr(G.status, kStatusWaitTimeout);
+        __syncthreads();
+        const unsigned char* src = own + half_off;
+        unsigned char* dst = static_cast<unsigned char*>(G.gathered);
+        for (long long i = tid; i < total; i += kGatherPushThreads) {
+            const size_t o = slot(i, r);
+            *reinterpret_cast<uint4*>(dst + o) = __ldcg(reinterpret_cast<const uint4*>(src + o));   // written by a peer: read at L2
+        }
+    }
+    if (push) {
+        // every CTA has read the counter by now; the last one out advances it
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t* ticket = own_tail + 17;
+            if (atomicAdd(ticket, 1u) == (uint32_t)G.world - 1u) {
+                *ticket = 0;
+                *counter = seq;
+            }
+        }
     }
 }
 

@@ -104,7 +104,7 @@ struct FastForwardAttn {
         check(ffa_plan_set_mode(np, mode), "mode");
         if (peer_world > 0) {
             std::vector<void*> bufs(peer_ptrs.begin(), peer_ptrs.end());
-            check(ffa_peer_gather_attach(np, peer_world, peer_rank, bufs.data(), peer_bytes, ffa_peer_gather_steps(plan)), "peer gather");
+            check(ffa_peer_gather_attach(np, peer_world, peer_rank, bufs.data(), peer_bytes), "peer gather");
         }
         stream.synchronize();   // the old slabs may be freed once the copy is done
         ffa_plan_destroy(plan);
@@ -288,22 +288,27 @@ struct FastForwardAttn {
         TORCH_CHECK(ptrs[rank] == peer_gather_ptr(), "FastForwardAttn: ptrs[rank] must be this rank's own buffer");
         std::vector<void*> bufs;
         for (int64_t x : ptrs) bufs.push_back(reinterpret_cast<void*>((uintptr_t)x));
-        check(ffa_peer_gather_attach(plan, (int)world, (int)rank, bufs.data(), peer_bytes, 0), "peer gather");
+        check(ffa_peer_gather_attach(plan, (int)world, (int)rank, bufs.data(), peer_bytes), "peer gather");
         peer_ptrs = bufs, peer_world = (int)world, peer_rank = (int)rank, peer_close = close_on_free;
     }
-    // out_local [B, H, Dh] -> [B, world*H, Dh] holding every rank's outputs.  The result aliases the
-    // peer buffer: it stays valid until this engine's next-but-one gather.
-    torch::Tensor peer_gather(const torch::Tensor& out_local, int64_t phases, int64_t wait_limit_ms)
+    // out_local [B, H, Dh] -> [B, world*H, Dh] holding every rank's outputs (a fresh tensor, or
+    // `out`).  Every launch argument is the same for every step, so the call can be recorded in a
+    // CUDA graph when `out` is given.
+    torch::Tensor peer_gather(const torch::Tensor& out_local, int64_t phases, int64_t wait_limit_ms, c10::optional<torch::Tensor> out_opt)
     {
         TORCH_CHECK(peer_world > 0, "FastForwardAttn: peer_gather_attach first");
         TORCH_CHECK(out_local.is_cuda() && out_local.device() == device && dtype_code(out_local) == dtype && out_local.is_contiguous() &&
                         out_local.numel() == B * H * Dh,
                     "FastForwardAttn: out_local must be a contiguous [batch, heads, head_dim] tensor of the cache's dtype and device");
         c10::cuda::CUDAGuard guard(device);
-        const void* g = nullptr;
-        check(ffa_peer_gather(plan, out_local.data_ptr(), (int)phases, (unsigned)wait_limit_ms, &g, at::cuda::getCurrentCUDAStream().stream()),
+        torch::Tensor out = out_opt.has_value() ? *out_opt : torch::empty({B, (int64_t)peer_world * H, Dh}, out_local.options());
+        TORCH_CHECK(out.is_cuda() && out.device() == device && dtype_code(out) == dtype && out.is_contiguous() &&
+                        out.numel() == (int64_t)peer_world * B * H * Dh,
+                    "FastForwardAttn: out must be a contiguous [batch, world*heads, head_dim] tensor of the cache's dtype and device");
+        check(ffa_peer_gather(plan, out_local.data_ptr(), out.data_ptr(), (int)phases, (unsigned)wait_limit_ms,
+                              at::cuda::getCurrentCUDAStream().stream()),
               "peer gather");
-        return torch::from_blob(const_cast<void*>(g), {B, (int64_t)peer_world * H, Dh}, out_local.options());
+        return out;
     }
     // Teardown is collective and has two steps with a host barrier before each: (1) every rank has
     // synchronised its device, so no store is in flight -> peer_gather_detach unmaps the peers'
@@ -313,7 +318,7 @@ struct FastForwardAttn {
     {
         if (peer_world == 0) return;
         c10::cuda::CUDAGuard guard(device);
-        ffa_peer_gather_attach(plan, 0, 0, nullptr, 0, 0);
+        ffa_peer_gather_attach(plan, 0, 0, nullptr, 0);
         if (peer_close)
             for (int r = 0; r < peer_world; ++r)
                 if (r != peer_rank) ffa_peer_mem_close(peer_ptrs[r]);
@@ -504,7 +509,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("peer_gather_attach", &FastForwardAttn::peer_gather_attach, py::arg("world"), py::arg("rank"), py::arg("ptrs"),
              py::arg("close_on_free") = true)
         .def("peer_gather", &FastForwardAttn::peer_gather, py::arg("out_local"), py::arg("phases") = 3, py::arg("wait_limit_ms") = 2000,
-             "all-gather of the outputs over peer memory: [B, H, Dh] -> [B, world*H, Dh]")
+             py::arg("out") = py::none(), "all-gather of the outputs over peer memory: [B, H, Dh] -> [B, world*H, Dh]")
         .def("peer_gather_detach", &FastForwardAttn::peer_gather_detach, "unmap the peers' buffers (teardown step 1)")
         .def("peer_gather_free", &FastForwardAttn::peer_gather_free, "release this rank's buffer (teardown step 2)");
     py::class_<PagedEngine>(m, "PagedEngine")

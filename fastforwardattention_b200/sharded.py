@@ -121,9 +121,7 @@ class ShardedFastForwardAttn:
         self._peer = False
 
     def gather(self, out_local: torch.Tensor) -> torch.Tensor:
-        """All-gather of the per-rank outputs into [B, H, Dh] (rank-major heads).  After
-        enable_peer_gather() the result aliases a buffer that is reused by the next-but-one
-        gather; copy it to keep it longer."""
+        """All-gather of the per-rank outputs into [B, H, Dh] (rank-major heads)."""
         if self.world == 1:
             return out_local
         out_local = out_local.contiguous()

@@ -184,25 +184,23 @@ int ffa_attention_static_scratch(int dtype, int batch, int heads, int head_dim, 
 int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
 
 /* ---- All-gather of the step outputs over peer memory (heads sharded over the GPUs of a node).
- * No counterpart in the reference, which runs on one GPU.  Every rank allocates one buffer of
- * ffa_peer_gather_bytes(plan, world) bytes with ffa_peer_mem_alloc (device memory, zero-filled,
- * plus a 64-byte handle another process of the node can open with ffa_peer_mem_open), collects
- * the `world` buffer pointers in rank order (its own included) and attaches them to its plan
- * (steps_done = 0 for fresh buffers; a plan that replaces another over the same buffers passes
- * the old plan's ffa_peer_gather_steps, because arrival flags only grow; world = 0 detaches).
+ * No counterpart in the reference, which runs on one GPU.  Every rank allocates one staging
+ * buffer of ffa_peer_gather_bytes(plan, world) bytes with ffa_peer_mem_alloc (device memory,
+ * zero-filled, plus a 64-byte handle another process of the node can open with
+ * ffa_peer_mem_open), collects the `world` buffer pointers in rank order (its own included)
+ * and attaches them to its plan (world = 0 detaches).
  * ffa_peer_gather then stores this rank's out_local [batch, heads, head_dim] (heads = the
- * plan's local head count) into every rank's buffer at heads [rank*heads, (rank+1)*heads),
- * raises one arrival flag per peer, and waits -- for at most wait_limit_ms (1..2000), after
- * which FFA_STATUS_WAIT_TIMEOUT is set in the status word and the kernel returns -- until
- * every peer's slice of the same step has arrived.  *gathered is this rank's
- * [batch, world*heads, head_dim] result; it stays valid until the rank's next-but-one call
- * (two halves are used alternately), provided every rank makes the same sequence of calls.
- * phases: 3 = both; 1 = store and signal only, 2 = wait only (a wait refers to the latest
- * push) -- the split exists so that several ranks can be driven from ONE stream of one GPU,
- * all pushes before all waits; a kernel that waits must never be queued ahead of the kernel
- * that signals it on the same GPU.
- * The step number travels as a launch argument, so the call refuses (FFA_ERR_ARG) a stream that
- * is being captured into a CUDA graph.
+ * plan's local head count) into every peer's staging buffer, raises one arrival flag per peer,
+ * waits -- for at most wait_limit_ms (1..2000), after which FFA_STATUS_WAIT_TIMEOUT is set in
+ * the status word and the kernel returns -- until every peer's slice of the same step has
+ * arrived, and writes gathered [batch, world*heads, head_dim] (this rank's own memory; rank r's
+ * heads at [r*heads, (r+1)*heads)).  Every rank must make the same sequence of calls.  The
+ * step number lives in device memory and is advanced by the kernel, so all launch arguments
+ * are the same for every step and the call may be recorded in a CUDA graph.
+ * phases: 3 = both; 1 = store and signal only, 2 = wait and collect only (refers to the latest
+ * push; same `gathered`) -- the split exists so that several ranks can be driven from ONE
+ * stream of one GPU, all pushes before all waits; a kernel that waits must never be queued
+ * ahead of the kernel that signals it on the same GPU.
  * Teardown: no rank may unmap or free a buffer while a peer can still store into it, and an
  * exported buffer must outlive every mapping of it: synchronise the device, pass a host
  * barrier, ffa_peer_mem_close the peers' buffers, pass a second barrier, ffa_peer_mem_free the
@@ -214,11 +212,9 @@ int ffa_peer_mem_alloc(size_t bytes, void** ptr, unsigned char* handle /* [FFA_P
 int ffa_peer_mem_open(const unsigned char* handle, void** ptr);
 int ffa_peer_mem_close(void* ptr);
 int ffa_peer_mem_free(void* ptr);
-int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each,
-                           unsigned int steps_done);
-unsigned int ffa_peer_gather_steps(const ffa_plan_t* plan);
-int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, int phases, unsigned int wait_limit_ms,
-                    const void** gathered, void* stream);
+int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each);
+int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, void* gathered, int phases, unsigned int wait_limit_ms,
+                    void* stream);
 
 /* Diagnostic, no counterpart in the reference: launches one warp that waits, for at most
  * limit_ms (1..2000), on a copy barrier nothing completes.  The wait must give up, the kernel

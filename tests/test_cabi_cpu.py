@@ -95,19 +95,18 @@ def test_peer_gather_arguments_without_gpu():
     assert L.ffa_peer_gather_bytes(None, 2) == 0
     need = L.ffa_peer_gather_bytes(p, 2)
     bufs = (C.c_void_p * 2)(0x10000, 0x20000)
-    assert L.ffa_peer_gather_attach(p, 2, 2, bufs, need, 0) == -3 and b"rank" in L.ffa_last_error()
-    assert L.ffa_peer_gather_attach(p, 9, 0, bufs, need, 0) == -3
-    assert L.ffa_peer_gather_attach(p, 2, 0, bufs, need - 1, 0) == -6 and b"need" in L.ffa_last_error()
-    assert L.ffa_peer_gather_attach(p, 2, 0, (C.c_void_p * 2)(0x10000, 0), need, 0) == -4
-    assert L.ffa_peer_gather_attach(p, 2, 0, (C.c_void_p * 2)(0x10000, 0x20010), need, 0) == -4
-    assert L.ffa_peer_gather_attach(p, 2, 0, None, need, 0) == -4
+    assert L.ffa_peer_gather_attach(p, 2, 2, bufs, need) == -3 and b"rank" in L.ffa_last_error()
+    assert L.ffa_peer_gather_attach(p, 9, 0, bufs, need) == -3
+    assert L.ffa_peer_gather_attach(p, 2, 0, bufs, need - 1) == -6 and b"need" in L.ffa_last_error()
+    assert L.ffa_peer_gather_attach(p, 2, 0, (C.c_void_p * 2)(0x10000, 0), need) == -4
+    assert L.ffa_peer_gather_attach(p, 2, 0, (C.c_void_p * 2)(0x10000, 0x20010), need) == -4
+    assert L.ffa_peer_gather_attach(p, 2, 0, None, need) == -4
+    assert L.ffa_peer_gather(p, 0x30000, 0x40000, 3, 100, None) == -4 and b"attach" in L.ffa_last_error()
+    assert L.ffa_peer_gather_attach(p, 2, 1, bufs, need) == 0
+    assert L.ffa_peer_gather(p, 0x30000, 0x40000, 3, 100, None) == -6       # no workspace: nothing is launched
+    assert L.ffa_peer_gather_attach(p, 0, 0, None, 0) == 0                   # detach
+    assert L.ffa_peer_gather(p, 0x30000, 0x40000, 3, 100, None) == -4
     g = C.c_void_p()
-    assert L.ffa_peer_gather(p, 0x30000, 3, 100, C.byref(g), None) == -4 and b"attach" in L.ffa_last_error()
-    assert L.ffa_peer_gather_attach(p, 2, 1, bufs, need, 41) == 0
-    assert L.ffa_peer_gather_steps(p) == 41
-    assert L.ffa_peer_gather(p, 0x30000, 3, 100, C.byref(g), None) == -6      # no workspace: nothing is launched
-    assert L.ffa_peer_gather_attach(p, 0, 0, None, 0, 0) == 0                  # detach
-    assert L.ffa_peer_gather(p, 0x30000, 3, 100, C.byref(g), None) == -4
     assert L.ffa_peer_mem_alloc(0, C.byref(g), C.create_string_buffer(64)) == -4
     assert L.ffa_peer_mem_open(None, C.byref(g)) == -4
     assert L.ffa_peer_mem_close(None) == 0 and L.ffa_peer_mem_free(None) == 0

@@ -37,22 +37,17 @@ def test_every_rank_receives_every_slice(world, dt, Dh, H):
     K, V, engines = _ranks(world, dt, B, H, Dh, Lp, Lp + steps, g)
     orc = O.DecodeOracle(K, V, Lp + steps, compute_dtype=torch.float64)
     tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dt]
-    previous = None
     for i in range(steps):
         q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
         outs = [e.attention(q[:, r * per:(r + 1) * per].contiguous().cuda(), k[:, r * per:(r + 1) * per].contiguous().cuda(),
                             v[:, r * per:(r + 1) * per].contiguous().cuda(), Dh ** -0.5, Lp + i, 1e-3 if i == 3 else 0.0)
                 for r, e in enumerate(engines)]
-        for e, o in zip(engines, outs):
-            e.peer_gather(o, phases=1)                 # all pushes ...
-        got = [e.peer_gather(o, phases=2) for e, o in zip(engines, outs)]   # ... before any wait
+        got = [e.peer_gather(o, phases=1) for e, o in zip(engines, outs)]          # all pushes ...
+        got = [e.peer_gather(o, phases=2, out=x) for e, o, x in zip(engines, outs, got)]   # ... before any wait
         want = torch.cat(outs, dim=1)                  # rank-major heads
         for r in range(world):
             assert got[r].shape == (B, H, Dh)
             assert torch.equal(got[r], want), (i, r)
-        if previous is not None:                       # the result of the step before is still intact
-            assert all(torch.equal(a, b) for a, b in zip(previous[0], previous[1]))
-        previous = (got, [want.clone() for _ in range(world)])
         if i != 3:
             ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
             assert (got[0].cpu().double() - ref).abs().max().item() <= tol
@@ -84,8 +79,8 @@ def test_wait_for_a_silent_peer_runs_out_and_reports():
     e1.peer_gather(o1, phases=3, wait_limit_ms=100)    # rank 0's flag is already there
     for t in (Lp + 1,):
         o0, o1 = e0.attention(q, q, q, 0.125, t, 0.0), e1.attention(q, q, q, 0.125, t, 0.0)
-        e0.peer_gather(o0, phases=1), e1.peer_gather(o1, phases=1)
-        g0, g1 = e0.peer_gather(o0, phases=2), e1.peer_gather(o1, phases=2)
+        g0, g1 = e0.peer_gather(o0, phases=1), e1.peer_gather(o1, phases=1)
+        g0, g1 = e0.peer_gather(o0, phases=2, out=g0), e1.peer_gather(o1, phases=2, out=g1)
         assert torch.equal(g0, torch.cat([o0, o1], dim=1)) and torch.equal(g1, g0)
     assert e0.device_status() == 0 and e1.device_status() == 0
 
@@ -114,12 +109,37 @@ def test_bad_arguments_raise():
     with pytest.raises(RuntimeError, match="phases"):
         e.peer_gather(o, 0, 100)
     assert torch.equal(e.peer_gather(o), o)           # a world of one gathers its own slice
+    e.peer_gather_free()
+
+
+def test_gather_replayed_from_a_cuda_graph():
+    """The step number lives in device memory, so a push and a wait recorded once can be
+    replayed for every step (two ranks on one GPU: one graph holds both pushes, then both
+    waits)."""
+    g = torch.Generator().manual_seed(45)
+    dt, B, H, Dh, Lp = torch.bfloat16, 2, 4, 128, 30
+    K, V, (e0, e1) = _ranks(2, dt, B, H, Dh, Lp, Lp + 1, g)
+    o0 = torch.zeros(B, 2, Dh, dtype=dt, device="cuda")
+    o1 = torch.zeros_like(o0)
+    g0 = torch.zeros(B, H, Dh, dtype=dt, device="cuda")
+    g1 = torch.zeros_like(g0)
+
+    def both():
+        e0.peer_gather(o0, phases=1, out=g0), e1.peer_gather(o1, phases=1, out=g1)
+        e0.peer_gather(o0, phases=2, out=g0), e1.peer_gather(o1, phases=2, out=g1)
+
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        both()                                         # step 1, eagerly
+    torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
-    with pytest.raises(RuntimeError, match="CUDA graph"):
-        with torch.cuda.stream(side), torch.cuda.graph(graph, capture_error_mode="thread_local"):
-            e.peer_gather(o)                          # a replay would repeat the step number
-    torch.cuda.synchronize()
-    assert torch.equal(e.peer_gather(o), o)           # the refusal left everything usable
-    e.peer_gather_free()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        both()
+    for step in range(5):                              # steps 2..6 from the graph: both halves, flags growing
+        o0.copy_(torch.randn(B, 2, Dh, generator=g).to(dt))
+        o1.copy_(torch.randn(B, 2, Dh, generator=g).to(dt))
+        graph.replay()
+        want = torch.cat([o0, o1], dim=1)
+        assert torch.equal(g0, want) and torch.equal(g1, want), step
+    assert e0.device_status() == 0 and e1.device_status() == 0
