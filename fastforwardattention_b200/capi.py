@@ -18,7 +18,7 @@ SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_des
            "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
            "ffa_plan_get_prune_launch", "ffa_cache_copy", "ffa_attention_paged", "ffa_peer_gather_bytes",
            "ffa_peer_mem_alloc", "ffa_peer_mem_open", "ffa_peer_mem_close", "ffa_peer_mem_free", "ffa_peer_gather_attach",
-           "ffa_peer_gather"]
+           "ffa_peer_gather", "ffa_plan_set_cluster_merge"]
 
 
 class Launch(C.Structure):
@@ -54,6 +54,7 @@ def lib() -> C.CDLL:
         L.ffa_plan_set_launch.argtypes = [vp, C.POINTER(Launch)]
         L.ffa_plan_set_mode.argtypes = [vp, i]
         L.ffa_plan_set_prune_path.argtypes = [vp, i]
+        L.ffa_plan_set_cluster_merge.argtypes = [vp, i]
         L.ffa_workspace_bytes.argtypes = [vp, i]
         L.ffa_workspace_bytes.restype = sz
         L.ffa_workspace_bind.argtypes = [vp, vp, sz, vp]

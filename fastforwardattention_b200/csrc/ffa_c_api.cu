@@ -41,6 +41,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kMaxCtasPerSm = 8;
+constexpr int kMaxClusterCtas = 8;   // portable thread-block cluster size
 constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident CTA
 // below this many tiles per CTA slot the work list is cut on (batch, head) boundaries (measured:
 // bf16 x 128, batch 32 x 32 heads: 2 K tokens 154.9 vs 159.3 us, 1 K 81.8 vs 88.3 us, 512 45.6 vs
@@ -52,6 +53,7 @@ constexpr long long kAlignedBelowUnitsPerSlot = 200;
 struct ffa_plan {
     int dtype, B, H, Dh, Lmax, use_default, device, mode;
     int prune_path;  // 0 = choose, 1 = fused cluster kernel only, 2 = two kernels only
+    int cluster_merge;  // 1 = merge split pairs inside a thread-block cluster when the cut allows it
     bool offline;    // planning only: created from given device properties, never launches
     int sms, smem_per_cta, smem_per_sm;
     bool forced;
@@ -220,6 +222,9 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
     if (!grid_forced && units < kAlignedBelowUnitsPerSlot * grid) {
         if (BH <= grid) {
             long long c = grid / BH;
+            // up to 8 CTAs per pair can merge inside a thread-block cluster (no partials in global
+            // memory); a few more than 8 are not worth losing that
+            if (p->cluster_merge && tensors == 2 && c > kMaxClusterCtas && c < kMaxClusterCtas + 4) c = kMaxClusterCtas;
             if (c > upb) c = upb;
             parts = (int)c, grid = BH * c;
         } else {
@@ -363,6 +368,7 @@ int ffa_plan_create(int dtype, int batch, int heads, int head_dim, int max_len, 
     std::memset(p, 0, sizeof(*p));
     p->dtype = dtype, p->B = batch, p->H = heads, p->Dh = head_dim, p->Lmax = max_len;
     p->use_default = use_default_launch != 0, p->device = device, p->mode = FFA_MODE_EXACT;
+    p->cluster_merge = 1;
     p->sms = sms, p->smem_per_cta = smem_cta, p->smem_per_sm = smem_sm;
     p->max_grid = sms * kMaxCtasPerSm;
     *plan = p;
@@ -383,6 +389,7 @@ int ffa_plan_create_offline(int dtype, int batch, int heads, int head_dim, int m
     std::memset(p, 0, sizeof(*p));
     p->dtype = dtype, p->B = batch, p->H = heads, p->Dh = head_dim, p->Lmax = max_len;
     p->use_default = use_default_launch != 0, p->device = -1, p->mode = FFA_MODE_EXACT;
+    p->cluster_merge = 1;
     p->sms = sms, p->smem_per_cta = smem_per_cta, p->smem_per_sm = smem_per_sm;
     p->max_grid = sms * kMaxCtasPerSm;
     p->offline = true;
@@ -428,6 +435,13 @@ int ffa_plan_set_prune_path(ffa_plan_t* plan, int path)
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
     if (path < 0 || path > 2) return fail(FFA_ERR_ARG, "prune path must be 0 (choose), 1 (fused) or 2 (two kernels)");
     plan->prune_path = path;
+    return FFA_OK;
+}
+
+int ffa_plan_set_cluster_merge(ffa_plan_t* plan, int on)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    plan->cluster_merge = on != 0;
     return FFA_OK;
 }
 
@@ -527,6 +541,9 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     P.parts_per_bh = L.parts_per_bh;
     const int threads = 32 * (L.consumer_warps + 1);
     if (!twopass) {
+        // the C CTAs of a pair merge inside a thread-block cluster when every CTA owns exactly one part
+        if (plan->cluster_merge && L.parts_per_bh >= 2 && L.parts_per_bh <= kMaxClusterCtas && (long long)L.grid == BH * L.parts_per_bh)
+            P.cluster = L.parts_per_bh;
         r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, threads, L.smem_bytes, st);
         if (r != 0) return cuda_fail(r, "attention launch");
         g_launches.fetch_add(1);

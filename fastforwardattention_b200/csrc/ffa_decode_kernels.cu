@@ -123,7 +123,8 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
     const int rowb = head_dim * elem_size(dtype);
     const int lpr = lanes_per_row(rowb);
     const int ng = consumer_warps * 32 / lpr;
-    return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16;
+    // ring, group reduction area, barriers, flags, the CTA's partial for the cluster merge
+    return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16 + (head_dim + 4) * 4;
 }
 
 int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows)
@@ -191,6 +192,19 @@ int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int th
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
+        if (P.cluster > 1) {   // the CTAs that share a (batch, head) as one thread-block cluster
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3((unsigned)P.grid, 1, 1);
+            cfg.blockDim = dim3((unsigned)threads, 1, 1);
+            cfg.dynamicSmemBytes = (size_t)smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = (unsigned)P.cluster, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr, cfg.numAttrs = 1;
+            return (int)cudaLaunchKernelEx(&cfg, ffa_stream_kernel<T, DH, kPassOne>, P);
+        }
         ffa_stream_kernel<T, DH, kPassOne><<<P.grid, threads, smem, stream>>>(P);
         return (int)cudaGetLastError();
     });

@@ -105,6 +105,26 @@ __device__ __forceinline__ float fast_exp2(float x)
     return y;
 }
 
+// thread-block clusters: rank, barrier over all threads of all CTAs, a float of a peer CTA's shared memory
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_smem_f32(const void* own_smem_ptr, uint32_t peer_rank)
+{
+    uint32_t peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_smem_ptr)), "r"(peer_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
 // ------------------------------------------------------------------------------------------
 // Element traits: a 16-byte vector holds EPV elements; unpack to fp32, round from fp32
 // ------------------------------------------------------------------------------------------

@@ -28,7 +28,8 @@ struct FfaStepParams {
     float* scores;     // [B*H, Lmax] fp32 scores (two-pass modes)
     uint32_t* kept_mask;  // [B*H, mask_words] or null
     int mask_words;
-    // fused pruning kernel: CTAs per (batch, head) cluster, cache rows per CTA (multiple of 32)
+    // thread-block cluster size: CTAs per (batch, head) (fused pruning kernel; streaming kernel when
+    // it merges split pairs inside a cluster, 0 otherwise); fused pruning: cache rows per CTA (multiple of 32)
     int cluster, chunk_rows;
     // paged caches (exact path only): k_cache / v_cache are page pools [pages, H, page_rows, Dh] and
     // page_table [B, max_pages] names the page of every page_rows rows of a sequence; null = contiguous

@@ -209,25 +209,6 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
 constexpr int kFusedThreads = 160;   // 1 copy warp + 4 compute warps
 constexpr int kFusedListCap = 512;   // rows pruned and gathered per round (multiple of 32)
 
-__device__ __forceinline__ uint32_t cluster_rank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_peer_smem_f32(const void* own_smem_ptr, uint32_t peer_rank)
-{
-    uint32_t peer;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_smem_ptr)), "r"(peer_rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
-    return v;
-}
-
 template <typename T, int DH>
 __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const FfaStepParams P)
 {

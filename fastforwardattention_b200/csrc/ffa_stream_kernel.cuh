@@ -9,7 +9,8 @@ namespace ffa_dev {
 // ------------------------------------------------------------------------------------------
 // Shared memory: [stages][K tile | V tile] ring (score pass: K tile only), then the group
 // reduction area [NG][DH + 4] (rows 16-byte aligned; max and sum in the tail), then
-// full/empty barriers, then two flags.
+// full/empty barriers, then two flags, then the CTA's partial result [DH + 2] for the merge
+// inside a thread-block cluster.
 // Warp 0 issues the copies (one elected lane); warps 1.. compute.  A lane group of LPR lanes
 // owns a row: 16-byte shared-memory reads, fp32 FMAs, butterfly sum.  Each group keeps its
 // own online-softmax state, so the row loop has no CTA-level synchronisation at all.
@@ -35,6 +36,13 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
     float* red = reinterpret_cast<float*>(smem + (size_t)S * stage_bytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(red + NG * RS);
     volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead, [1] last-arriver
+    // Cluster merge (one-pass, few pairs): the C CTAs that share a (batch, head) are one thread-block
+    // cluster; each leaves its partial (weighted sum, max, sum) in its own shared memory and CTA 0
+    // of the cluster combines them through distributed shared memory -- no partials in global
+    // memory, no fence, no arrival counter.  The launcher guarantees grid = B*H*C, so a CTA owns
+    // exactly one part of exactly one pair.
+    float* clp = reinterpret_cast<float*>(const_cast<int*>(flags) + 4);
+    const bool cl = PASS == kPassOne && P.cluster > 1;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
     const uint32_t ring = smem_u32(smem);
 
@@ -46,6 +54,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         flags[0] = 0, flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (cl && threadIdx.x < DH + 2) clp[threadIdx.x] = threadIdx.x == DH ? -CUDART_INF_F : 0.f;   // "nothing seen"
     __syncthreads();
 
     const int upb = P.units_per_bh;
@@ -335,12 +344,15 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 if (whole) {
                     if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
                     else P.stats[2 * bh] = M, P.stats[2 * bh + 1] = L;
+                } else if (cl) {
+                    clp[d] = A;
+                    if (d == 0) clp[DH] = M, clp[DH + 1] = L;
                 } else {
                     if (PASS == kPassOne) part[d] = A;
                     if (d == 0) part[DH] = M, part[DH + 1] = L;
                 }
             }
-            if (!whole) {
+            if (!whole && !cl) {
                 // cross-CTA merge without waiting: whoever arrives last does it
                 __threadfence();
                 named_bar_sync(1, nct);
@@ -377,6 +389,27 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         }
     }
     __syncthreads();
+    if (cl) {
+        const int C = P.cluster;
+        cluster_sync_all();   // every CTA's partial is in its shared memory
+        if (cluster_rank() == 0) {
+            const int bh = blockIdx.x / C;
+            T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+            float MM = -CUDART_INF_F;
+            for (int c = 0; c < C; ++c) MM = fmaxf(MM, ld_peer_smem_f32(clp + DH, c));
+            for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+                float A = 0.f, L = 0.f;
+                for (int c = 0; c < C; ++c) {   // rank order: deterministic
+                    const float mc = ld_peer_smem_f32(clp + DH, c);
+                    const float w = mc == -CUDART_INF_F ? 0.f : (kPrecise ? expf(mc - MM) : fast_exp2(mc - MM));
+                    A = fmaf(w, ld_peer_smem_f32(clp + d, c), A);
+                    L = fmaf(w, ld_peer_smem_f32(clp + DH + 1, c), L);
+                }
+                Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+            }
+        }
+        cluster_sync_all();   // peers keep their shared memory alive until CTA 0 has read it
+    }
     if (threadIdx.x == 0 && flags[0]) atomicOr(P.status, kStatusWaitTimeout);
 }
 

@@ -222,6 +222,7 @@ struct FastForwardAttn {
         check(ffa_plan_set_mode(plan, mode), "mode");
     }
     void set_prune_path(int path) { check(ffa_plan_set_prune_path(plan, path), "prune path"); }
+    void set_cluster_merge(bool on) { check(ffa_plan_set_cluster_merge(plan, on ? 1 : 0), "cluster merge"); }
     void set_launch(int tile_rows, int stages, int consumer_warps, int ctas_per_sm, int grid)
     {
         ffa_launch_t l{tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0, 0};
@@ -496,6 +497,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
              py::arg("out") = py::none())
         .def("set_mode", &FastForwardAttn::set_mode, "'exact' (default) or 'round_like_torch'")
         .def("set_prune_path", &FastForwardAttn::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
+        .def("set_cluster_merge", &FastForwardAttn::set_cluster_merge, "merge split pairs inside a thread-block cluster (default on)")
         .def("set_launch", &FastForwardAttn::set_launch, py::arg("tile_rows") = 0, py::arg("stages") = 0,
              py::arg("consumer_warps") = 0, py::arg("ctas_per_sm") = 0, py::arg("grid") = 0)
         .def("launch_shape", &FastForwardAttn::launch_shape, py::arg("t"))

@@ -112,6 +112,10 @@ int ffa_plan_set_mode(ffa_plan_t* plan, int mode);
  * memory.  The reference does both phases in one CTA per (batch, head) (attention.cu:1077-1257),
  * which is what caps its sequence length. */
 int ffa_plan_set_prune_path(ffa_plan_t* plan, int path);
+/* Exact steps whose (batch, head) pairs are split over 2..8 CTAs merge the splits inside a
+ * thread-block cluster through distributed shared memory (on = 1, the default) or through
+ * partial results in global memory and an arrival counter (on = 0; kept for comparison). */
+int ffa_plan_set_cluster_merge(ffa_plan_t* plan, int on);
 /* The fused pruning launch the planner picks for step t: CTAs per (batch, head) cluster, cache
  * rows per CTA, tile rows, grid and dynamic shared memory; all zero when the two-launch path
  * would run instead. */

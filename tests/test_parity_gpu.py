@@ -452,3 +452,32 @@ def test_results_are_bitwise_reproducible(p, path):
         outs.append(eng.attention(2 * q, k, v, Dh ** -0.5, Lp, p=p).cpu())
         assert eng.status() == 0
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+@pytest.mark.parametrize("dt,B,H,Dh,Lp", [(torch.float32, 1, 32, 64, 999), (torch.float16, 1, 16, 256, 2047),
+                                          (torch.bfloat16, 4, 32, 128, 2047), (torch.float16, 2, 3, 80, 500),
+                                          (torch.float32, 1, 1, 128, 4000), (torch.bfloat16, 1, 2, 64, 7)])
+def test_cluster_merge_equals_merge_through_global_memory(dt, B, H, Dh, Lp):
+    """Few (batch, head) pairs: the CTAs that share a pair merge inside a thread-block cluster
+    through distributed shared memory.  Same partials, same order of operations as the merge
+    through global memory and an arrival counter, so the two give the same bits; both are
+    checked against the oracle."""
+    from fastforwardattention_b200 import FastForwardAttn
+
+    g, K, V = small_case(dt, B, H, Dh, Lp, Lp + 2, 77 + Dh)
+    orc = O.DecodeOracle(K, V, Lp + 2, compute_dtype=torch.float64)
+    a = FastForwardAttn(K.cuda(), V.cuda(), Lp + 2, False)
+    b = FastForwardAttn(K.cuda(), V.cuda(), Lp + 2, False)
+    b.set_cluster_merge(False)
+    parts = a.launch_shape(Lp)["parts_per_bh"]
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dt]
+    for i in range(2):
+        q, k, v = qkv(g, B, H, Dh, dt)
+        oa = a.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, Lp + i, 0.0)
+        ob = b.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, Lp + i, 0.0)
+        assert torch.equal(oa, ob), (parts, i)
+        ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
+        assert (oa.cpu().double() - ref).abs().max().item() <= tol
+    assert a.device_status() == 0 and b.device_status() == 0
+    if B * H <= 32 and Lp >= 500:
+        assert 2 <= parts <= 8                          # these shapes do run as clusters

@@ -65,6 +65,17 @@ def test_benchmark_configurations_get_the_measured_shapes():
     # the analytic rule ignores the refinements
     L, p = offline(capi.F32, 1, 32, 64, 1000, use_default=1)
     assert launch(L, p, 999).ctas_per_sm == 2
+    # 16 pairs on 148 SMs: 9 CTAs per pair would fit, 8 are taken so that a pair is one thread-block cluster;
+    # without the cluster merge the ninth is used
+    L, p = offline(capi.F16, 1, 16, 256, 2048)
+    l = launch(L, p, 2047)
+    assert (l.grid, l.parts_per_bh) == (128, 8)
+    capi.check(L.ffa_plan_set_cluster_merge(p, 0))
+    l = launch(L, p, 2047)
+    assert (l.grid, l.parts_per_bh) == (144, 9)
+    # 8 pairs: 18 CTAs per pair is far beyond a cluster; the split stays and merges through global memory
+    L, p = offline(capi.BF16, 2, 4, 128, 8192)
+    assert launch(L, p, 8191).parts_per_bh == 18
 
 
 def test_forced_shape_is_respected_and_clamped():
