@@ -222,10 +222,10 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
     if (!grid_forced && units < kAlignedBelowUnitsPerSlot * grid) {
         if (BH <= grid) {
             long long c = grid / BH;
-            // up to 8 CTAs per pair can merge inside a thread-block cluster (no partials in global
-            // memory); a few more than 8 are not worth losing that
-            if (p->cluster_merge && tensors == 2 && c > kMaxClusterCtas && c < kMaxClusterCtas + 4) c = kMaxClusterCtas;
+            // up to 8 CTAs per pair merge inside a thread-block cluster (no partials in global memory);
+            // more than 8 run as whole clusters of 8, whose leaders merge through global memory
             if (c > upb) c = upb;
+            if (p->cluster_merge && tensors == 2 && c > kMaxClusterCtas) c = c / kMaxClusterCtas * kMaxClusterCtas;
             parts = (int)c, grid = BH * c;
         } else {
             const int need = (int)((BH + p->sms - 1) / p->sms);
@@ -542,8 +542,11 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     const int threads = 32 * (L.consumer_warps + 1);
     if (!twopass) {
         // the C CTAs of a pair merge inside a thread-block cluster when every CTA owns exactly one part
-        if (plan->cluster_merge && L.parts_per_bh >= 2 && L.parts_per_bh <= kMaxClusterCtas && (long long)L.grid == BH * L.parts_per_bh)
-            P.cluster = L.parts_per_bh;
+        // (pairs with more than 8 parts: whole clusters of 8, the cluster leaders merge through global memory)
+        if (plan->cluster_merge && L.parts_per_bh >= 2 && (long long)L.grid == BH * L.parts_per_bh) {
+            if (L.parts_per_bh <= kMaxClusterCtas) P.cluster = L.parts_per_bh;
+            else if (L.parts_per_bh % kMaxClusterCtas == 0) P.cluster = kMaxClusterCtas;
+        }
         r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, threads, L.smem_bytes, st);
         if (r != 0) return cuda_fail(r, "attention launch");
         g_launches.fetch_add(1);

@@ -4,6 +4,31 @@
 
 namespace ffa_dev {
 
+// Combines `count` partials (weighted sum [DH], running max, running sum; stride DH + 2 floats)
+// that other CTAs left in global memory, in slot order, and writes the normalised output
+// (one-pass) or the pair's (max, sum) (score pass).  Called by all `nthreads` threads of the
+// CTA that arrived last.
+template <typename T, int DH, int PASS, bool kPrecise>
+__device__ __forceinline__ void merge_partials(const float* pbase, int count, T* outp, float* stats2, int tid, int nthreads)
+{
+    auto expo = [&](float x) -> float { return PASS == kPassScore ? __expf(x) : (kPrecise ? expf(x) : fast_exp2(x)); };
+    const int nd = PASS == kPassOne ? DH : 1;
+    float MM = -CUDART_INF_F;
+    for (int k = 0; k < count; ++k) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
+    for (int d = tid; d < nd; d += nthreads) {
+        float A = 0.f, L = 0.f;
+        for (int k = 0; k < count; ++k) {
+            const float* pk = pbase + (size_t)k * (DH + 2);
+            const float mk = __ldcg(pk + DH);
+            const float w = mk == -CUDART_INF_F ? 0.f : expo(mk - MM);
+            if (PASS == kPassOne) A = fmaf(w, __ldcg(pk + d), A);
+            L = fmaf(w, __ldcg(pk + DH + 1), L);
+        }
+        if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+        else stats2[0] = MM, stats2[1] = L;
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Streaming kernel (one-pass attention, or the score pass of the two-pass modes)
 // ------------------------------------------------------------------------------------------
@@ -365,21 +390,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 named_bar_sync(1, nct);
                 if (flags[1]) {
                     __threadfence();
-                    const float* pbase = P.partials + (size_t)(c_first + bh) * (DH + 2);
-                    float MM = -CUDART_INF_F;
-                    for (int k = 0; k < count; ++k) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
-                    for (int d = ctid; d < nd; d += nct) {
-                        float A = 0.f, L = 0.f;
-                        for (int k = 0; k < count; ++k) {
-                            const float* pk = pbase + (size_t)k * (DH + 2);
-                            const float mk = __ldcg(pk + DH);
-                            const float w = mk == -CUDART_INF_F ? 0.f : expo(mk - MM);
-                            if (PASS == kPassOne) A = fmaf(w, __ldcg(pk + d), A);
-                            L = fmaf(w, __ldcg(pk + DH + 1), L);
-                        }
-                        if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
-                        else P.stats[2 * bh] = MM, P.stats[2 * bh + 1] = L;
-                    }
+                    merge_partials<T, DH, PASS, kPrecise>(P.partials + (size_t)(c_first + bh) * (DH + 2), count, outp, P.stats + 2 * bh, ctid, nct);
                     if (ctid == 0) P.tickets[bh] = 0;  // ready for the next launch on this stream
                 }
             }
@@ -390,25 +401,46 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
     }
     __syncthreads();
     if (cl) {
-        const int C = P.cluster;
+        // A pair's C = Q * K CTAs are K clusters of Q.  Inside a cluster: distributed shared memory.
+        // Across the K cluster leaders (K > 1: very few pairs): partials in global memory and the
+        // arrival counter, as in the non-cluster path, with K instead of C partials to combine.
+        const int C = P.parts_per_bh, Q = P.cluster, K = C / Q;
+        const int bh = blockIdx.x / C, kc = (blockIdx.x - bh * C) / Q;
+        const bool leader = cluster_rank() == 0;
+        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+        float* part = P.partials + ((size_t)bh * K + kc) * (DH + 2);
         cluster_sync_all();   // every CTA's partial is in its shared memory
-        if (cluster_rank() == 0) {
-            const int bh = blockIdx.x / C;
-            T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+        if (leader) {
             float MM = -CUDART_INF_F;
-            for (int c = 0; c < C; ++c) MM = fmaxf(MM, ld_peer_smem_f32(clp + DH, c));
+            for (int c = 0; c < Q; ++c) MM = fmaxf(MM, ld_peer_smem_f32(clp + DH, c));
             for (int d = threadIdx.x; d < DH; d += blockDim.x) {
                 float A = 0.f, L = 0.f;
-                for (int c = 0; c < C; ++c) {   // rank order: deterministic
+                for (int c = 0; c < Q; ++c) {   // rank order: deterministic
                     const float mc = ld_peer_smem_f32(clp + DH, c);
                     const float w = mc == -CUDART_INF_F ? 0.f : (kPrecise ? expf(mc - MM) : fast_exp2(mc - MM));
                     A = fmaf(w, ld_peer_smem_f32(clp + d, c), A);
                     L = fmaf(w, ld_peer_smem_f32(clp + DH + 1, c), L);
                 }
-                Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+                if (K == 1) {
+                    Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+                } else {
+                    part[d] = A;
+                    if (d == 0) part[DH] = MM, part[DH + 1] = L;
+                }
             }
         }
-        cluster_sync_all();   // peers keep their shared memory alive until CTA 0 has read it
+        cluster_sync_all();   // peers kept their shared memory alive until the leader had read it
+        if (leader && K > 1) {
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) flags[1] = (atomicAdd(P.tickets + bh, 1) == K - 1);
+            __syncthreads();
+            if (flags[1]) {
+                __threadfence();
+                merge_partials<T, DH, PASS, kPrecise>(P.partials + (size_t)bh * K * (DH + 2), K, outp, nullptr, threadIdx.x, blockDim.x);
+                if (threadIdx.x == 0) P.tickets[bh] = 0;
+            }
+        }
     }
     if (threadIdx.x == 0 && flags[0]) atomicOr(P.status, kStatusWaitTimeout);
 }

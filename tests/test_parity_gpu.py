@@ -456,12 +456,15 @@ def test_results_are_bitwise_reproducible(p, path):
 
 @pytest.mark.parametrize("dt,B,H,Dh,Lp", [(torch.float32, 1, 32, 64, 999), (torch.float16, 1, 16, 256, 2047),
                                           (torch.bfloat16, 4, 32, 128, 2047), (torch.float16, 2, 3, 80, 500),
-                                          (torch.float32, 1, 1, 128, 4000), (torch.bfloat16, 1, 2, 64, 7)])
+                                          (torch.float32, 1, 1, 128, 4000), (torch.bfloat16, 1, 2, 64, 7),
+                                          (torch.bfloat16, 2, 4, 128, 8191), (torch.float16, 1, 4, 64, 20000)])
 def test_cluster_merge_equals_merge_through_global_memory(dt, B, H, Dh, Lp):
     """Few (batch, head) pairs: the CTAs that share a pair merge inside a thread-block cluster
     through distributed shared memory.  Same partials, same order of operations as the merge
     through global memory and an arrival counter, so the two give the same bits; both are
-    checked against the oracle."""
+    checked against the oracle.  With very few pairs a pair is several clusters of 8 whose leaders
+    then merge through global memory: one more level, so equal within rounding instead of
+    bit-identical."""
     from fastforwardattention_b200 import FastForwardAttn
 
     g, K, V = small_case(dt, B, H, Dh, Lp, Lp + 2, 77 + Dh)
@@ -475,9 +478,12 @@ def test_cluster_merge_equals_merge_through_global_memory(dt, B, H, Dh, Lp):
         q, k, v = qkv(g, B, H, Dh, dt)
         oa = a.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, Lp + i, 0.0)
         ob = b.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, Lp + i, 0.0)
-        assert torch.equal(oa, ob), (parts, i)
+        if parts <= 8:
+            assert torch.equal(oa, ob), (parts, i)
+        else:
+            assert parts % 8 == 0 and (oa.float() - ob.float()).abs().max().item() <= tol
         ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
         assert (oa.cpu().double() - ref).abs().max().item() <= tol
     assert a.device_status() == 0 and b.device_status() == 0
     if B * H <= 32 and Lp >= 500:
-        assert 2 <= parts <= 8                          # these shapes do run as clusters
+        assert 2 <= parts <= 8 or parts % 8 == 0        # these shapes do run as clusters

@@ -73,9 +73,11 @@ def test_benchmark_configurations_get_the_measured_shapes():
     capi.check(L.ffa_plan_set_cluster_merge(p, 0))
     l = launch(L, p, 2047)
     assert (l.grid, l.parts_per_bh) == (144, 9)
-    # 8 pairs: 18 CTAs per pair is far beyond a cluster; the split stays and merges through global memory
+    # 8 pairs: 18 CTAs per pair would fit; 16 are taken = two whole clusters of 8 per pair, whose
+    # leaders merge through global memory
     L, p = offline(capi.BF16, 2, 4, 128, 8192)
-    assert launch(L, p, 8191).parts_per_bh == 18
+    l = launch(L, p, 8191)
+    assert (l.grid, l.parts_per_bh) == (128, 16)
 
 
 def test_forced_shape_is_respected_and_clamped():
