@@ -19,6 +19,7 @@ constexpr int kPassOne = 0;
 constexpr int kPassScore = 1;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bounded barrier wait: 2 s, then give up
 constexpr uint32_t kDrainPolls = 1u << 20;
+constexpr int kMaxClusterCtas = 8;   // portable thread-block cluster size
 constexpr int kStatusWaitTimeout = 1;
 constexpr int kStatusBadLength = 2;
 constexpr int kGatherThreads = 256;

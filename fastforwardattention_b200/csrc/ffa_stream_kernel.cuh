@@ -411,15 +411,27 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         float* part = P.partials + ((size_t)bh * K + kc) * (DH + 2);
         cluster_sync_all();   // every CTA's partial is in its shared memory
         if (leader) {
-            float MM = -CUDART_INF_F;
-            for (int c = 0; c < Q; ++c) MM = fmaxf(MM, ld_peer_smem_f32(clp + DH, c));
+            // all remote reads of a thread are issued before the first is used: one trip, not Q
             for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+                float mc[kMaxClusterCtas], lc[kMaxClusterCtas], ac[kMaxClusterCtas];
+#pragma unroll
+                for (int c = 0; c < kMaxClusterCtas; ++c) {
+                    mc[c] = -CUDART_INF_F, lc[c] = 0.f, ac[c] = 0.f;
+                    if (c < Q) {
+                        mc[c] = ld_peer_smem_f32(clp + DH, c);
+                        lc[c] = ld_peer_smem_f32(clp + DH + 1, c);
+                        ac[c] = ld_peer_smem_f32(clp + d, c);
+                    }
+                }
+                float MM = -CUDART_INF_F;
+#pragma unroll
+                for (int c = 0; c < kMaxClusterCtas; ++c) MM = fmaxf(MM, mc[c]);
                 float A = 0.f, L = 0.f;
-                for (int c = 0; c < Q; ++c) {   // rank order: deterministic
-                    const float mc = ld_peer_smem_f32(clp + DH, c);
-                    const float w = mc == -CUDART_INF_F ? 0.f : (kPrecise ? expf(mc - MM) : fast_exp2(mc - MM));
-                    A = fmaf(w, ld_peer_smem_f32(clp + d, c), A);
-                    L = fmaf(w, ld_peer_smem_f32(clp + DH + 1, c), L);
+#pragma unroll
+                for (int c = 0; c < kMaxClusterCtas; ++c) {   // rank order: deterministic
+                    const float w = mc[c] == -CUDART_INF_F ? 0.f : (kPrecise ? expf(mc[c] - MM) : fast_exp2(mc[c] - MM));
+                    A = fmaf(w, ac[c], A);
+                    L = fmaf(w, lc[c], L);
                 }
                 if (K == 1) {
                     Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
