@@ -42,6 +42,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 constexpr int kMaxCtasPerSm = 8;
 constexpr int kMaxClusterCtas = 8;   // portable thread-block cluster size
+constexpr int kMaxClustersPerPair = 12;
 constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident CTA
 // below this many tiles per CTA slot the work list is cut on (batch, head) boundaries (measured:
 // bf16 x 128, batch 32 x 32 heads: 2 K tokens 154.9 vs 159.3 us, 1 K 81.8 vs 88.3 us, 512 45.6 vs
@@ -225,7 +226,12 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
             // up to 8 CTAs per pair merge inside a thread-block cluster (no partials in global memory);
             // more than 8 run as whole clusters of 8, whose leaders merge through global memory
             if (c > upb) c = upb;
-            if (p->cluster_merge && tensors == 2 && c > kMaxClusterCtas) c = c / kMaxClusterCtas * kMaxClusterCtas;
+            if (p->cluster_merge && tensors == 2 && c > kMaxClusterCtas) {
+                c = c / kMaxClusterCtas * kMaxClusterCtas;
+                // the leaders' merge is serial in the number of clusters (bf16 x 128, 4 pairs at 32 K
+                // tokens: 13 clusters per pair 20.2 us, 18 clusters 27.9 us)
+                if (c > kMaxClustersPerPair * kMaxClusterCtas) c = kMaxClustersPerPair * kMaxClusterCtas;
+            }
             parts = (int)c, grid = BH * c;
         } else {
             const int need = (int)((BH + p->sms - 1) / p->sms);

@@ -472,16 +472,16 @@ def test_cluster_merge_equals_merge_through_global_memory(dt, B, H, Dh, Lp):
     a = FastForwardAttn(K.cuda(), V.cuda(), Lp + 2, False)
     b = FastForwardAttn(K.cuda(), V.cuda(), Lp + 2, False)
     b.set_cluster_merge(False)
-    parts = a.launch_shape(Lp)["parts_per_bh"]
+    parts, parts_b = a.launch_shape(Lp)["parts_per_bh"], b.launch_shape(Lp)["parts_per_bh"]
     tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dt]
     for i in range(2):
         q, k, v = qkv(g, B, H, Dh, dt)
         oa = a.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, Lp + i, 0.0)
         ob = b.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, Lp + i, 0.0)
-        if parts <= 8:
+        if parts <= 8 and parts == parts_b:
             assert torch.equal(oa, ob), (parts, i)
-        else:
-            assert parts % 8 == 0 and (oa.float() - ob.float()).abs().max().item() <= tol
+        else:   # another cut (9 parts -> 8) or one more merge level: equal within rounding
+            assert (oa.float() - ob.float()).abs().max().item() <= tol
         ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
         assert (oa.cpu().double() - ref).abs().max().item() <= tol
     assert a.device_status() == 0 and b.device_status() == 0
