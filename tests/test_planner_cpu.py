@@ -78,6 +78,10 @@ def test_benchmark_configurations_get_the_measured_shapes():
     L, p = offline(capi.BF16, 2, 4, 128, 8192)
     l = launch(L, p, 8191)
     assert (l.grid, l.parts_per_bh) == (128, 16)
+    # 4 pairs at 32 K tokens: at most 12 clusters of 8 per pair
+    L, p = offline(capi.BF16, 1, 4, 128, 32768)
+    l = launch(L, p, 32767)
+    assert (l.grid, l.parts_per_bh) == (384, 96)
 
 
 def test_forced_shape_is_respected_and_clamped():
