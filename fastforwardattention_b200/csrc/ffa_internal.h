@@ -48,6 +48,7 @@ struct FfaPeerGatherParams {
     unsigned long long wait_limit_ns;
     int world, rank, B, row_bytes;
     int phases;                // bit 0: push the slice and raise the flags; bit 1: wait for the peers' flags, collect
+    int slices;                // CTAs per peer (set by the launcher)
 };
 
 // dtype codes as in ffa_c_api.h.  Return a cudaError_t as int.
@@ -67,5 +68,5 @@ int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, in
 int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows);
 // diagnostic: a bounded wait that must time out (see ffa_selftest_wait_timeout)
 int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, cudaStream_t stream);
-// all-gather of the step outputs: one CTA per rank
-int ffa_k_peer_gather(const FfaPeerGatherParams& G, cudaStream_t stream);
+// all-gather of the step outputs: a few CTAs per rank
+int ffa_k_peer_gather(FfaPeerGatherParams G, cudaStream_t stream);

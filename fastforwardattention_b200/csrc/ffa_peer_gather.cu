@@ -8,14 +8,14 @@
 // copies the slice to its place in the caller's [batch, N * heads/N, head_dim] result -- no
 // permutation afterwards.
 //
-// Staging buffer of a rank: half 0 | half 1 | flags[8] | step counter | ticket.  A half is
+// Staging buffer of a rank: half 0 | half 1 | flags[8], step counter, tickets (256 bytes).  A half is
 // [batch][N][heads/N * head_dim]; the two halves alternate by step so that a peer already in
 // step s+1 never overwrites what this rank still reads for step s (a peer cannot be two steps
 // ahead: its wait of step s+1 needs this rank's flag of step s+1).  Flags hold step numbers and
 // only grow.  The step number lives in the rank's own buffer and is advanced by the kernel
 // (last CTA out, through the ticket), so every launch argument is the same for every step.
 //
-// One CTA per peer.  Sending never waits, so no rank can block another; a wait that runs out
+// A few CTAs per peer (one per 16 KB of slice).  Sending never waits, so no rank can block another; a wait that runs out
 // sets the time-out bit of the status word and the kernel returns normally.
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -39,19 +39,47 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
 }
 
 constexpr int kGatherPushThreads = 256;
+constexpr int kVecPerThread = 4;      // 16-byte vectors a thread moves per phase, all loads before the first store
+constexpr int kMaxSlices = 16;        // CTAs per peer
 
+// tail of a staging buffer, in 32-bit words: arrival flags, step counter, the ticket that advances it,
+// one ticket per peer that elects the CTA raising that peer's flag
+constexpr int kTailFlags = 0, kTailCounter = 16, kTailTicket = 17, kTailPushTickets = 24;
+
+// Moves vectors [lo, hi) of a [B][row_bytes] slice: `from` and `to` map a vector index to its address.
+template <typename From, typename To>
+__device__ __forceinline__ void move_vectors(long long lo, long long hi, int tid, From from, To to)
+{
+    for (long long base = lo + tid; base < hi; base += (long long)kGatherPushThreads * kVecPerThread) {
+        uint4 v[kVecPerThread];
+#pragma unroll
+        for (int k = 0; k < kVecPerThread; ++k) {
+            const long long i = base + (long long)k * kGatherPushThreads;
+            if (i < hi) v[k] = from(i);
+        }
+#pragma unroll
+        for (int k = 0; k < kVecPerThread; ++k) {
+            const long long i = base + (long long)k * kGatherPushThreads;
+            if (i < hi) *to(i) = v[k];
+        }
+    }
+}
+
+// grid = world * slices: CTA (r, sl) moves slice sl of what this rank exchanges with rank r.
 __global__ void __launch_bounds__(kGatherPushThreads) ffa_peer_gather_kernel(const FfaPeerGatherParams G)
 {
-    const int r = blockIdx.x, tid = threadIdx.x;   // this CTA talks to rank r
+    const int r = blockIdx.x / G.slices, sl = blockIdx.x - r * G.slices, tid = threadIdx.x;
     const bool push = (G.phases & 1) != 0, wait = (G.phases & 2) != 0;
     unsigned char* own = static_cast<unsigned char*>(G.peer_base[G.rank]);
-    uint32_t* own_tail = reinterpret_cast<uint32_t*>(own + 2 * G.half_bytes);   // flags[8], then counter, ticket
-    volatile uint32_t* counter = own_tail + 16;
+    uint32_t* own_tail = reinterpret_cast<uint32_t*>(own + 2 * G.half_bytes);
+    volatile uint32_t* counter = own_tail + kTailCounter;
     // a push opens step counter + 1; a lone wait refers to the latest push
     const uint32_t seq = *counter + (push ? 1u : 0u);
     const size_t half_off = (size_t)(seq & 1u) * G.half_bytes;
     const int vec_per_row = G.row_bytes >> 4;
     const long long total = (long long)G.B * vec_per_row;
+    const long long per = (total + G.slices - 1) / G.slices;
+    const long long lo = min(total, (long long)sl * per), hi = min(total, lo + per);
     // the slice of batch row b sits at bytes [(b * world + rank) * row_bytes, +row_bytes)
     auto slot = [&](long long i, int rank) -> size_t {
         const long long b = i / vec_per_row;
@@ -62,13 +90,24 @@ __global__ void __launch_bounds__(kGatherPushThreads) ffa_peer_gather_kernel(con
         const uint4* src = static_cast<const uint4*>(G.out_local);
         if (r == G.rank) {   // the own slice goes straight to the result
             unsigned char* dst = static_cast<unsigned char*>(G.gathered);
-            for (long long i = tid; i < total; i += kGatherPushThreads) *reinterpret_cast<uint4*>(dst + slot(i, G.rank)) = src[i];
+            move_vectors(lo, hi, tid, [&](long long i) { return src[i]; },
+                         [&](long long i) { return reinterpret_cast<uint4*>(dst + slot(i, G.rank)); });
         } else {
-            unsigned char* dst = static_cast<unsigned char*>(G.peer_base[r]) + half_off;
-            for (long long i = tid; i < total; i += kGatherPushThreads) *reinterpret_cast<uint4*>(dst + slot(i, G.rank)) = src[i];
+            unsigned char* peer = static_cast<unsigned char*>(G.peer_base[r]);
+            unsigned char* dst = peer + half_off;
+            move_vectors(lo, hi, tid, [&](long long i) { return src[i]; },
+                         [&](long long i) { return reinterpret_cast<uint4*>(dst + slot(i, G.rank)); });
             __threadfence_system();   // every thread's stores are performed at the peer before the flag
             __syncthreads();
-            if (tid == 0) st_release_sys(reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(G.peer_base[r]) + 2 * G.half_bytes) + G.rank, seq);
+            if (tid == 0) {
+                // the CTA that finishes last raises the flag, after everybody's stores
+                uint32_t* ticket = own_tail + kTailPushTickets + r;
+                if (atomicAdd(ticket, 1u) == (uint32_t)G.slices - 1u) {
+                    *ticket = 0;
+                    __threadfence_system();
+                    st_release_sys(reinterpret_cast<uint32_t*>(peer + 2 * G.half_bytes) + kTailFlags + G.rank, seq);
+                }
+            }
         }
     }
     if (wait && r != G.rank) {
@@ -77,7 +116,7 @@ __global__ void __launch_bounds__(kGatherPushThreads) ffa_peer_gather_kernel(con
             const unsigned long long t0 = global_timer_ns();
             bool ok = false;
             for (;;) {
-                if ((int32_t)(ld_acquire_sys(own_tail + r) - seq) >= 0) {
+                if ((int32_t)(ld_acquire_sys(own_tail + kTailFlags + r) - seq) >= 0) {
                     ok = true;
                     break;
                 }
@@ -89,17 +128,15 @@ __global__ void __launch_bounds__(kGatherPushThreads) ffa_peer_gather_kernel(con
         __syncthreads();
         const unsigned char* src = own + half_off;
         unsigned char* dst = static_cast<unsigned char*>(G.gathered);
-        for (long long i = tid; i < total; i += kGatherPushThreads) {
-            const size_t o = slot(i, r);
-            *reinterpret_cast<uint4*>(dst + o) = __ldcg(reinterpret_cast<const uint4*>(src + o));   // written by a peer: read at L2
-        }
+        move_vectors(lo, hi, tid, [&](long long i) { return __ldcg(reinterpret_cast<const uint4*>(src + slot(i, r))); },   // written by a peer: read at L2
+                     [&](long long i) { return reinterpret_cast<uint4*>(dst + slot(i, r)); });
     }
     if (push) {
         // every CTA has read the counter by now; the last one out advances it
         __syncthreads();
         if (tid == 0) {
-            uint32_t* ticket = own_tail + 17;
-            if (atomicAdd(ticket, 1u) == (uint32_t)G.world - 1u) {
+            uint32_t* ticket = own_tail + kTailTicket;
+            if (atomicAdd(ticket, 1u) == (uint32_t)(G.world * G.slices) - 1u) {
                 *ticket = 0;
                 *counter = seq;
             }
@@ -109,8 +146,11 @@ __global__ void __launch_bounds__(kGatherPushThreads) ffa_peer_gather_kernel(con
 
 }  // namespace
 
-int ffa_k_peer_gather(const FfaPeerGatherParams& G, cudaStream_t stream)
+int ffa_k_peer_gather(FfaPeerGatherParams G, cudaStream_t stream)
 {
-    ffa_peer_gather_kernel<<<G.world, kGatherPushThreads, 0, stream>>>(G);
+    const long long vectors = (long long)G.B * (G.row_bytes >> 4);
+    long long slices = (vectors + kGatherPushThreads * kVecPerThread - 1) / (kGatherPushThreads * kVecPerThread);
+    G.slices = (int)(slices < 1 ? 1 : slices > kMaxSlices ? kMaxSlices : slices);
+    ffa_peer_gather_kernel<<<G.world * G.slices, kGatherPushThreads, 0, stream>>>(G);
     return (int)cudaGetLastError();
 }
