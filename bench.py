@@ -340,13 +340,35 @@ def main():
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    # ---- leg 3: the same step with no staging copies: the kernels read q/k/v from pinned host memory
+    # and write the (gathered) result to pinned host memory in place ----
+    in_place_ms = None
+    if world == 1 or gather_kind == "peer-memory kernel":
+        def in_place_step(s):
+            q, k, v = qkv_h[s][0], qkv_h[s][1], qkv_h[s][2]
+            if world > 1:
+                o = engines[s % nrep].attention(q, k, v, w.scale, t_of(s), w.p)
+                engines[s % nrep].peer_gather(o, out=out_h)
+            else:
+                engines[s % nrep].attention(q, k, v, w.scale, t_of(s), w.p, out=out_h)
+            torch.cuda.current_stream().synchronize()
+
+        for s in range(min(3, args.warmup)):
+            in_place_step(s)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            in_place_step(args.warmup + i)
+        e1.record()
+        barrier()
+        in_place_ms = e0.elapsed_time(e1)
     status = max(e.device_status() for e in engines)
 
     # ---- max over ranks ----
-    times = torch.tensor([loop_ms, e2e_ms, sum(kernel_ms)], dtype=torch.float64, device=dev)
+    times = torch.tensor([loop_ms, e2e_ms, sum(kernel_ms), in_place_ms or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    loop_ms, e2e_ms, ksum_ms = times.tolist()
+    loop_ms, e2e_ms, ksum_ms, in_place_ms = times.tolist()
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -368,7 +390,11 @@ def main():
                 "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "steps/s",
                         "h2d_bytes_per_step": 3 * w.B * w.H * w.Dh * es, "d2h_bytes_per_step": out_h.numel() * es,
                         "includes": "pinned-host q/k/v upload, attention, output all-gather (N>1), output download, sync",
-                        "gather": gather_kind},
+                        "gather": gather_kind,
+                        "in_place": None if not in_place_ms else {
+                            "value": args.steps / (in_place_ms * 1e-3), "unit": "steps/s",
+                            "what": "same step without staging copies: kernels read q/k/v from, and write the result to, "
+                                    "pinned host memory over PCIe"}},
                 "gpu_launches": int(launches), "launch_shape": dict(shape), "device_status": status,
                 "clocks": clocks.summary(wall0, wall1), "replicas": nrep}
         if world == 1 and not args.no_cpu_baseline:

@@ -131,15 +131,21 @@ struct FastForwardAttn {
         has_scores = with_scores;
     }
 
+    // memory the engine's kernels can address: its own device, or pinned (page-locked) host memory
+    bool reachable(const torch::Tensor& x) const { return (x.is_cuda() && x.device() == device) || (x.is_cpu() && x.is_pinned()); }
+
     torch::Tensor run(const torch::Tensor& q_, const torch::Tensor& k_, const torch::Tensor& v_, torch::Tensor& kc,
                       torch::Tensor& vc, double softmax_scale, int64_t t, const torch::Tensor* seq_lengths,
                       bool right_or_no_padding, double p, c10::optional<torch::Tensor> out_opt)
     {
         const int64_t n = B * H * Dh;
+        // q, k, v (and out) may also live in pinned host memory: the kernel then reads (writes) them
+        // in place over PCIe, which saves the staging copies of a host-driven decode loop
         auto prep = [&](const torch::Tensor& x, const char* name) {
-            TORCH_CHECK(x.is_cuda() && x.device() == device, "FastForwardAttn: ", name, " is not on the engine's device");
+            TORCH_CHECK(reachable(x), "FastForwardAttn: ", name, " is not on the engine's device (nor in pinned host memory)");
             TORCH_CHECK(dtype_code(x) == dtype, "FastForwardAttn: ", name, " has a different dtype than the cache");
             TORCH_CHECK(x.numel() == n, "FastForwardAttn: ", name, " must hold batch*heads*head_dim = ", n, " elements, got ", x.numel());
+            TORCH_CHECK(x.is_cuda() || x.is_contiguous(), "FastForwardAttn: ", name, " in pinned host memory must be contiguous");
             return x.contiguous();
         };
         torch::Tensor q = prep(q_, "q"), k = prep(k_, "k"), v = prep(v_, "v");
@@ -161,10 +167,11 @@ struct FastForwardAttn {
         torch::Tensor out;
         if (out_opt.has_value()) {
             out = *out_opt;
-            TORCH_CHECK(out.is_cuda() && out.device() == device && dtype_code(out) == dtype && out.is_contiguous() && out.numel() == n,
-                        "FastForwardAttn: out must be a contiguous tensor of batch*heads*head_dim elements on the engine's device");
+            TORCH_CHECK(reachable(out) && dtype_code(out) == dtype && out.is_contiguous() && out.numel() == n,
+                        "FastForwardAttn: out must be a contiguous tensor of batch*heads*head_dim elements on the engine's device "
+                        "(or in pinned host memory)");
         } else {
-            out = torch::empty({B, H, Dh}, q.options());
+            out = torch::empty({B, H, Dh}, kc.options());
         }
         uint32_t* mask_ptr = nullptr;
         if (want_mask && p > 0.0) {
@@ -303,9 +310,9 @@ struct FastForwardAttn {
                     "FastForwardAttn: out_local must be a contiguous [batch, heads, head_dim] tensor of the cache's dtype and device");
         c10::cuda::CUDAGuard guard(device);
         torch::Tensor out = out_opt.has_value() ? *out_opt : torch::empty({B, (int64_t)peer_world * H, Dh}, out_local.options());
-        TORCH_CHECK(out.is_cuda() && out.device() == device && dtype_code(out) == dtype && out.is_contiguous() &&
-                        out.numel() == (int64_t)peer_world * B * H * Dh,
-                    "FastForwardAttn: out must be a contiguous [batch, world*heads, head_dim] tensor of the cache's dtype and device");
+        TORCH_CHECK(reachable(out) && dtype_code(out) == dtype && out.is_contiguous() && out.numel() == (int64_t)peer_world * B * H * Dh,
+                    "FastForwardAttn: out must be a contiguous [batch, world*heads, head_dim] tensor of the cache's dtype on the engine's "
+                    "device (or in pinned host memory)");
         check(ffa_peer_gather(plan, out_local.data_ptr(), out.data_ptr(), (int)phases, (unsigned)wait_limit_ms,
                               at::cuda::getCurrentCUDAStream().stream()),
               "peer gather");

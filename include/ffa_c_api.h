@@ -136,6 +136,8 @@ int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* st
  *   seq_lengths != NULL, right_or_no_padding : row = seq_lengths[b] (per-sample lengths);
  *   seq_lengths != NULL, !right_or_no_padding: row = t, keys < seq_lengths[b] are masked
  *                                              (left padding).
+ * q, k, v and out may also point into pinned (page-locked, device-addressable) host memory: the
+ * kernels read and write them in place, which saves a host-driven loop its staging copies.
  * p is the pruning threshold as a fraction of the largest probability; p == 0 is exact
  * attention.  kept_mask, if not NULL and p > 0, receives one bit per cache row,
  * [batch*heads, ceil(max_len/32)] words, bit set = row contributed to the output.

@@ -264,3 +264,31 @@ def test_adopt_prefilled_caches_and_grow(dt):
     with pytest.raises(RuntimeError, match="must exceed"):
         ffa.grow(10)
     assert ffa.device_status() == 0
+
+
+@pytest.mark.parametrize("p", [0.0, 1e-3])
+def test_pinned_host_inputs_and_output_are_used_in_place(p):
+    """q, k, v and out in pinned host memory: no staging copies, the kernels read and write
+    them over PCIe.  Same bits as with device tensors."""
+    from fastforwardattention_b200 import FastForwardAttn
+
+    dt, B, H, Dh, Lp = torch.float16, 2, 8, 128, 600
+    g = torch.Generator().manual_seed(51)
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    a = FastForwardAttn(K.cuda(), V.cuda(), Lp + 3, False)
+    b = FastForwardAttn(K.cuda(), V.cuda(), Lp + 3, False)
+    qkv = torch.randn(3, 3, B, H, 1, Dh, generator=g).to(dt).pin_memory()      # [step, q/k/v, ...]
+    out_h = torch.empty(B, H, Dh, dtype=dt).pin_memory()
+    for i in range(3):
+        want = a.attention(qkv[i, 0].cuda(), qkv[i, 1].cuda(), qkv[i, 2].cuda(), Dh ** -0.5, Lp + i, p)
+        got = b.attention(qkv[i, 0], qkv[i, 1], qkv[i, 2], Dh ** -0.5, Lp + i, p, out=out_h)
+        assert got.data_ptr() == out_h.data_ptr()
+        torch.cuda.synchronize()
+        assert torch.equal(out_h, want.cpu())
+    assert torch.equal(a.get_cache()[0], b.get_cache()[0]) and torch.equal(a.get_cache()[1], b.get_cache()[1])
+    with pytest.raises(RuntimeError, match="pinned host memory"):
+        b.attention(torch.zeros(B, H, 1, Dh, dtype=dt), qkv[0, 1], qkv[0, 2], 0.1, Lp, 0.0)     # pageable: refused
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        b.attention(qkv[0, 0].transpose(0, 1), qkv[0, 1], qkv[0, 2], 0.1, Lp, 0.0)
+    assert a.device_status() == 0 and b.device_status() == 0
