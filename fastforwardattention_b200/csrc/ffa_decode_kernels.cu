@@ -203,9 +203,14 @@ int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int th
             attr.id = cudaLaunchAttributeClusterDimension;
             attr.val.clusterDim.x = (unsigned)P.cluster, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
             cfg.attrs = &attr, cfg.numAttrs = 1;
-            return (int)cudaLaunchKernelEx(&cfg, ffa_stream_kernel<T, DH, kPassOne>, P);
+            if (cudaLaunchKernelEx(&cfg, ffa_stream_kernel<T, DH, kPassOne>, P) == cudaSuccess) return 0;
+            // a cluster shape this device cannot co-schedule: the same cut runs without clusters,
+            // the parts merging through global memory
+            (void)cudaGetLastError();
         }
-        ffa_stream_kernel<T, DH, kPassOne><<<P.grid, threads, smem, stream>>>(P);
+        FfaStepParams Q = P;
+        Q.cluster = 0;
+        ffa_stream_kernel<T, DH, kPassOne><<<Q.grid, threads, smem, stream>>>(Q);
         return (int)cudaGetLastError();
     });
 }
