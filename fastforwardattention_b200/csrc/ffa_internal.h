@@ -31,7 +31,7 @@ struct FfaStepParams {
     // thread-block cluster size: CTAs per (batch, head) (fused pruning kernel; streaming kernel when
     // it merges split pairs inside a cluster, 0 otherwise); fused pruning: cache rows per CTA (multiple of 32)
     int cluster, chunk_rows;
-    // paged caches (exact path only): k_cache / v_cache are page pools [pages, H, page_rows, Dh] and
+    // paged caches: k_cache / v_cache are page pools [pages, H, page_rows, Dh] and
     // page_table [B, max_pages] names the page of every page_rows rows of a sequence; null = contiguous
     const int* page_table;
     int max_pages, page_rows;

@@ -354,7 +354,7 @@ struct FastForwardAttn {
     bool peer_close = false;
 };
 
-// Decode steps over PAGED caches (exact attention): the K and V pools are
+// Decode steps over PAGED caches (exact or pruned): the K and V pools are
 // [pages, heads, page_rows, head_dim]; a page table [batch, max_pages] maps every page_rows rows of a
 // sequence to a pool page.  The pools and the table belong to the caller (see paged.py for an
 // allocator); this class holds the plan and the workspace.  The reference has nothing like it:
