@@ -487,3 +487,43 @@ def test_cluster_merge_equals_merge_through_global_memory(dt, B, H, Dh, Lp):
     assert a.device_status() == 0 and b.device_status() == 0
     if B * H <= 32 and Lp >= 500:
         assert 2 <= parts <= 8 or parts % 8 == 0        # these shapes do run as clusters
+
+
+@pytest.mark.parametrize("dt,B,H,Dh,L", [(torch.bfloat16, 1, 4, 128, 131072), (torch.float16, 1, 2, 64, 500000),
+                                         (torch.float32, 1, 1, 256, 200000)])
+def test_very_long_sequences_exact_and_pruned(dt, B, H, Dh, L):
+    """Far beyond the reference's ~8 K-token limit (its scores live in 48 KB of shared memory,
+    attention.cu:660-688): 128 K to 500 K tokens, few pairs, so a pair is spread over many
+    clusters.  Exact step against an fp64 evaluation; pruned step (fused kernel where a slice's
+    scores fit in shared memory, two kernels where they do not) against the restated rule."""
+    from fastforwardattention_b200 import FastForwardAttn
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(L + Dh)
+    K = torch.randn(B, H, L - 2, Dh, generator=g, device=dev).to(dt)
+    V = torch.randn(B, H, L - 2, Dh, generator=g, device=dev).to(dt)
+    ffa = FastForwardAttn(K, V, L, False)
+    ffa.record_kept_mask(True)
+    Kc, Vc = K.cpu(), V.cpu()
+    del K, V
+    gc = torch.Generator().manual_seed(3)
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dt]
+    for i, p in enumerate((0.0, 1e-2)):
+        t = L - 2 + i
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=gc).to(dt) for _ in range(3))
+        q = 3.0 * q
+        got = ffa.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5, t, p).cpu()
+        Kc, Vc = torch.cat([Kc, k], dim=2), torch.cat([Vc, v], dim=2)
+        if p == 0.0:
+            ref = O.attention_reference(q.view(B * H, 1, Dh), Kc.view(B * H, t + 1, Dh), Vc.view(B * H, t + 1, Dh), Dh ** -0.5,
+                                        torch.float64, chunk=1)
+            assert (got.view(B * H, Dh).double() - ref).abs().max().item() <= tol
+        else:
+            want, kept, info = O.pruned_attention(q.view(B * H, Dh), Kc.view(B * H, t + 1, Dh), Vc.view(B * H, t + 1, Dh), Dh ** -0.5, p)
+            m = ffa.get_kept_mask().cpu().view(B * H, -1).to(torch.int64) & 0xFFFFFFFF
+            mine = ((m[:, :, None] >> torch.arange(32)[None, None, :]) & 1).reshape(B * H, -1)[:, : t + 1].bool()
+            diff = int((mine != kept).sum())
+            assert diff <= info["borderline"], (diff, info)
+            assert 0 < int(kept.sum()) < kept.numel()
+            assert (got.view(B * H, Dh).double() - want.double()).abs().max().item() <= tol + 0.05 * diff
+    assert ffa.device_status() == 0
