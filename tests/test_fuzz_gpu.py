@@ -37,6 +37,22 @@ def test_random_configuration(seed):
     Dh = rng.choice([64, 80, 128, 256])
     B, H = rng.randint(1, 5), rng.randint(1, 6)
     Lmax = rng.choice([1, 2, 9, 33, 100, 257, 700, 1300])
+    run_random_steps(seed, rng, dt, Dh, B, H, Lmax, force_launch=rng.random() < 0.6)
+
+
+@pytest.mark.parametrize("seed", range(100, 116))
+def test_random_few_pairs_long_caches(seed):
+    """One to eight (batch, head) pairs over thousands of rows, planner's own launch shape: a pair
+    is spread over one or several thread-block clusters, in all three length modes."""
+    rng = random.Random(seed)
+    dt = rng.choice(DTS)
+    Dh = rng.choice([64, 80, 128, 256])
+    B, H = rng.randint(1, 2), rng.randint(1, 4)
+    Lmax = rng.choice([3000, 9000, 20000])
+    run_random_steps(seed, rng, dt, Dh, B, H, Lmax, force_launch=False)
+
+
+def run_random_steps(seed, rng, dt, Dh, B, H, Lmax, force_launch):
     mode = rng.choice(["uniform", "left", "per_sample"])
     p = rng.choice([0.0, 0.0, 1e-3, 0.05])
     path = rng.choice([0, 1, 2])
@@ -45,7 +61,7 @@ def test_random_configuration(seed):
     Vc = torch.randn(B, H, Lmax, Dh, generator=g).to(dt)
     eng = CAbiEngine(Kc, Vc, Lmax)     # whole cache pre-filled; steps overwrite their row
     eng.set_prune_path(path)
-    if rng.random() < 0.6:
+    if force_launch:
         eng.set_launch(tile_rows=rng.choice([8, 16, 32, 64]), stages=rng.choice([2, 3, 4]),
                        consumer_warps=rng.choice([1, 2, 4, 8]), ctas_per_sm=rng.choice([1, 2, 4]),
                        grid=rng.choice([0, 0, 1, 7]))
