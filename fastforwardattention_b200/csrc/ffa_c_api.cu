@@ -55,6 +55,9 @@ struct ffa_plan {
     int dtype, B, H, Dh, Lmax, use_default, device, mode;
     int prune_path;  // 0 = choose, 1 = fused cluster kernel only, 2 = two kernels only
     int cluster_merge;  // 1 = merge split pairs inside a thread-block cluster when the cut allows it
+    // answers of the occupancy query for cluster launches, keyed by (threads, shared memory, cluster size)
+    struct { int threads, smem, cluster, clusters; } occ[8];
+    int occ_n;
     bool offline;    // planning only: created from given device properties, never launches
     int sms, smem_per_cta, smem_per_sm;
     bool forced;
@@ -155,7 +158,7 @@ Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int
     return s;
 }
 
-int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, bool pow2_tiles = false)
+int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, bool pow2_tiles = false, int max_parts = 0)
 {
     const int rowb = p->Dh * elem_size(p->dtype);
     const long long BH = (long long)p->B * p->H;
@@ -226,6 +229,7 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
             // up to 8 CTAs per pair merge inside a thread-block cluster (no partials in global memory);
             // more than 8 run as whole clusters of 8, whose leaders merge through global memory
             if (c > upb) c = upb;
+            if (max_parts > 0 && c > max_parts) c = max_parts;
             if (p->cluster_merge && tensors == 2 && c > kMaxClusterCtas) {
                 c = c / kMaxClusterCtas * kMaxClusterCtas;
                 // the leaders' merge is serial in the number of clusters (bf16 x 128, 4 pairs at 32 K
@@ -290,6 +294,46 @@ bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out
     P->grid = (int)(BH * best_c);
     *smem_out = best_smem;
     return true;
+}
+
+// cudaOccupancyMaxActiveClusters for the one-pass kernel, remembered per launch shape (the query
+// costs tens of microseconds); 0 when the device will not say
+int max_active_clusters(ffa_plan* p, int threads, int smem, int cluster)
+{
+    for (int i = 0; i < p->occ_n; ++i)
+        if (p->occ[i].threads == threads && p->occ[i].smem == smem && p->occ[i].cluster == cluster) return p->occ[i].clusters;
+    int n = 0;
+    if (ffa_k_max_active_clusters(p->dtype, p->Dh, threads, smem, cluster, &n) != 0) {
+        (void)cudaGetLastError();
+        n = 0;
+    }
+    const int slot = p->occ_n < 8 ? p->occ_n++ : (threads + smem + cluster) % 8;
+    p->occ[slot].threads = threads, p->occ[slot].smem = smem, p->occ[slot].cluster = cluster, p->occ[slot].clusters = n;
+    return n;
+}
+
+// Decides how the parts of the one-pass launch L are grouped into thread-block clusters (0: not at
+// all), and takes fewer parts per pair when the device cannot keep all clusters resident at once:
+// clusters are placed inside one GPC each, so fewer of them fit than CTA slots / size suggest, and
+// a grid that does not fit runs in two waves (bf16 x 128, 192 pairs at 2 K tokens: 3 CTAs per pair
+// 48.0 us, 2 per pair 36.7 us).
+int fit_clusters(ffa_plan* plan, int cap, bool paged, ffa_launch_t* L, int* cluster)
+{
+    const long long BH = (long long)plan->B * plan->H;
+    for (int tries = 0; tries < 8; ++tries) {
+        *cluster = 0;
+        if (plan->cluster_merge && L->parts_per_bh >= 2 && (long long)L->grid == BH * L->parts_per_bh) {
+            if (L->parts_per_bh <= kMaxClusterCtas) *cluster = L->parts_per_bh;
+            else if (L->parts_per_bh % kMaxClusterCtas == 0) *cluster = kMaxClusterCtas;
+        }
+        if (*cluster == 0 || plan->forced || plan->offline) break;
+        const int fit = max_active_clusters(plan, 32 * (L->consumer_warps + 1), L->smem_bytes, *cluster);
+        if (fit <= 0 || (long long)L->grid / *cluster <= fit) break;
+        const int fewer = L->parts_per_bh <= kMaxClusterCtas ? L->parts_per_bh - 1 : L->parts_per_bh - kMaxClusterCtas;
+        const int r = fit_launch(plan, cap, 2, L, paged, fewer);
+        if (r != FFA_OK) return r;
+    }
+    return FFA_OK;
 }
 
 // rows the unit list must cover for this call: t when every sample is at row t, max_len - 1
@@ -425,7 +469,10 @@ int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch)
 {
     if (plan == nullptr || launch == nullptr) return fail(FFA_ERR_ARG, "null pointer");
     if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
-    return fit_launch(plan, t, 2, launch);
+    const int r = fit_launch(plan, t, 2, launch);
+    if (r != FFA_OK) return r;
+    int cluster = 0;
+    return fit_clusters(const_cast<ffa_plan_t*>(plan), t, false, launch, &cluster);   // fills the plan's occupancy cache
 }
 
 int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch)
@@ -545,14 +592,16 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
     P.units_per_bh = cap / L.tile_rows + 1;
     P.parts_per_bh = L.parts_per_bh;
-    const int threads = 32 * (L.consumer_warps + 1);
+    int threads = 32 * (L.consumer_warps + 1);
     if (!twopass) {
         // the C CTAs of a pair merge inside a thread-block cluster when every CTA owns exactly one part
         // (pairs with more than 8 parts: whole clusters of 8, the cluster leaders merge through global memory)
-        if (plan->cluster_merge && L.parts_per_bh >= 2 && (long long)L.grid == BH * L.parts_per_bh) {
-            if (L.parts_per_bh <= kMaxClusterCtas) P.cluster = L.parts_per_bh;
-            else if (L.parts_per_bh % kMaxClusterCtas == 0) P.cluster = kMaxClusterCtas;
-        }
+        r = fit_clusters(plan, cap, paged, &L, &P.cluster);
+        if (r != FFA_OK) return r;
+        P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
+        P.units_per_bh = cap / L.tile_rows + 1;
+        P.parts_per_bh = L.parts_per_bh;
+        threads = 32 * (L.consumer_warps + 1);
         r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, threads, L.smem_bytes, st);
         if (r != 0) return cuda_fail(r, "attention launch");
         g_launches.fetch_add(1);

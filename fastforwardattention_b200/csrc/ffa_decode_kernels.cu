@@ -215,6 +215,24 @@ int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int th
     });
 }
 
+int ffa_k_max_active_clusters(int dtype, int head_dim, int threads, int smem, int cluster, int* clusters)
+{
+    return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
+        using T = decltype(t);
+        constexpr int DH = decltype(dh)::value;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)cluster, 1, 1);
+        cfg.blockDim = dim3((unsigned)threads, 1, 1);
+        cfg.dynamicSmemBytes = (size_t)smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = (unsigned)cluster, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr, cfg.numAttrs = 1;
+        return (int)cudaOccupancyMaxActiveClusters(clusters, ffa_stream_kernel<T, DH, kPassOne>, &cfg);
+    });
+}
+
 int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, int smem, cudaStream_t stream)
 {
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {

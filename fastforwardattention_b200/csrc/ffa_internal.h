@@ -57,6 +57,8 @@ int ffa_k_cache_init(int dtype, int BH, int prompt_len, int src_len, int max_len
                      const void* v_src, void* k_cache, void* v_cache, int sms, cudaStream_t stream);
 // p == 0, exact mode: one launch.
 int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int threads, int smem, cudaStream_t stream);
+// how many clusters of `cluster` CTAs of the one-pass kernel the device keeps resident at once
+int ffa_k_max_active_clusters(int dtype, int head_dim, int threads, int smem, int cluster, int* clusters);
 // p > 0 or round-like-torch: score pass then value pass, two launches.
 int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const FfaStepParams& Pv, int threads,
                          int smem_k, int smem_v, cudaStream_t stream);
