@@ -238,6 +238,7 @@ struct FastForwardAttn {
     }
     py::dict launch_shape(int64_t t)
     {
+        c10::cuda::CUDAGuard guard(device);   // the planner may ask this device about cluster occupancy
         ffa_launch_t l;
         check(ffa_plan_get_launch(plan, (int)t, &l), "launch shape");
         py::dict d;
