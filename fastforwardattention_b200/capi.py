@@ -1,7 +1,7 @@
 """ctypes view of libffa_b200.so (include/ffa_c_api.h) for hosts without the torch extension.
 
-This is the binding a non-torch caller writes; the tests and the benchmark use it to drive
-the C ABI directly with raw device pointers.  No computation happens in Python.
+This is the binding a non-torch caller writes; the GPU parity tests drive the C ABI through
+it with raw device pointers (the benchmark goes through the torch extension instead).  No computation happens in Python.
 """
 from __future__ import annotations
 
@@ -15,7 +15,7 @@ MODE_EXACT, MODE_ROUND_LIKE_TORCH = 0, 1
 
 SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_destroy", "ffa_plan_get_launch",
            "ffa_plan_set_launch", "ffa_plan_set_mode", "ffa_workspace_bytes", "ffa_workspace_bind", "ffa_attention",
-           "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
+           "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_static_scratch_status", "ffa_static_scratch_selftest_wait_timeout", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
            "ffa_plan_get_prune_launch", "ffa_cache_copy", "ffa_attention_paged", "ffa_peer_gather_bytes",
            "ffa_peer_mem_alloc", "ffa_peer_mem_open", "ffa_peer_mem_close", "ffa_peer_mem_free", "ffa_peer_gather_attach",
            "ffa_peer_gather", "ffa_plan_set_cluster_merge"]
@@ -63,6 +63,8 @@ def lib() -> C.CDLL:
         L.ffa_device_status.argtypes = [vp, vp, C.POINTER(i)]
         L.ffa_attention_static_scratch.argtypes = [i, i, i, i, i, vp, vp, vp, vp, vp, vp, f, i, vp, vp, C.c_char_p, sz]
         L.ffa_selftest_wait_timeout.argtypes = [vp, C.c_uint, vp]
+        L.ffa_static_scratch_status.argtypes = [vp, C.POINTER(i)]
+        L.ffa_static_scratch_selftest_wait_timeout.argtypes = [C.c_uint, vp]
         L.ffa_peer_gather_bytes.argtypes = [vp, i]
         L.ffa_peer_gather_bytes.restype = sz
         L.ffa_peer_mem_alloc.argtypes = [sz, C.POINTER(vp), C.c_char_p]

@@ -122,7 +122,7 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
     return s;
 }
 
-// Refinements measured with `python -m fastforwardattention_b200.tune` on B200 (CUDA-graph
+// Refinements measured on B200 with launch-shape sweeps through ffa_plan_set_launch (CUDA-graph
 // timing, replicas rotating so that every launch streams from HBM), keyed by row bytes and by
 // the bytes one decode step streams:
 //   < 48 MB  (OPT-1.3B fp32 batch 1, 16 MB: 12.9 us vs 17.3 us)  one CTA per SM when there are few
@@ -332,15 +332,19 @@ int fit_clusters(ffa_plan* plan, int cap, bool paged, ffa_launch_t* L, int* clus
         const int fewer = L->parts_per_bh <= kMaxClusterCtas ? L->parts_per_bh - 1 : L->parts_per_bh - kMaxClusterCtas;
         const int r = fit_launch(plan, cap, 2, L, paged, fewer);
         if (r != FFA_OK) return r;
+        *cluster = 0;   // describes the previous L; recomputed at the top of the next try
     }
+    // out of tries right after a refit: the launch runs without clusters (parts merge through global memory)
+    if (*cluster > 1 && (L->parts_per_bh % *cluster != 0 || (long long)L->grid != BH * L->parts_per_bh)) *cluster = 0;
     return FFA_OK;
 }
 
-// rows the unit list must cover for this call: t when every sample is at row t, max_len - 1
-// when rows come from per-sample lengths the host cannot see
+// rows the unit list must cover for this call: every sample is at row t, or -- with per-sample
+// lengths, which the host cannot see -- at a row no greater than the bound t the caller states
 int cap_rows_for(const ffa_plan* p, int t, const int* seq_lengths, int right_or_no_padding)
 {
-    return (seq_lengths != nullptr && right_or_no_padding) ? p->Lmax - 1 : t;
+    (void)p, (void)seq_lengths, (void)right_or_no_padding;
+    return t;
 }
 
 }  // namespace

@@ -221,7 +221,9 @@ struct RowGeom {
 };
 
 // Per-sample view of the cache for this step (attention.cu:805-817).  `row` is where the new
-// token goes and the number of cached rows attended; keys below `first` are masked.
+// token goes and the number of cached rows attended; keys below `first` are masked.  With
+// per-sample lengths P.t is the host's upper bound on every length: the work list covers rows
+// 0..P.t only, so a longer sample is refused (and reported), never silently cut short.
 struct SampleRange {
     int first, row;
     bool ok;
@@ -235,7 +237,7 @@ __device__ __forceinline__ SampleRange sample_range(const FfaStepParams& P, int 
         if (P.right_or_no_padding) r.row = s;
         else r.first = s;
     }
-    r.ok = r.row >= 0 && r.row < P.Lmax;
+    r.ok = r.row >= 0 && r.row < P.Lmax && r.row <= P.t;
     if (!r.ok) r.row = 0;
     r.first = min(max(r.first, 0), r.row);
     return r;

@@ -12,7 +12,8 @@
 //
 // Consequences of sharing one array:
 //   * it keeps the previous call's contents, so every call first clears the part that must
-//     start at zero (status word and arrival counters) on the caller's stream;
+//     start at zero (the arrival counters) on the caller's stream; the status word is NOT
+//     cleared by a call -- error bits stay until ffa_static_scratch_status reads and clears them;
 //   * two calls whose kernels overlap on the same GPU (different streams, or different host
 //     threads) race on it -- keep calls on one GPU stream-ordered;
 //   * sizes that do not fit are rejected, nothing is grown.
@@ -61,7 +62,72 @@ int report(char* buf, size_t len, int code, const char* fmt, ...)
 int head_dim_index(int d) { return d == 64 ? 0 : d == 80 ? 1 : d == 128 ? 2 : d == 256 ? 3 : -1; }
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// One-time set-up for the current device: the array's device address and the device's limits.
+// Returns 0 and fills *out, or a cudaError_t; *what names the call that failed.
+int device_state(int* dev_out, DeviceState* out, const char** what)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    *what = "cudaGetDevice";
+    if (e != cudaSuccess) return (int)e;
+    *what = "device ordinal beyond the supported 64";
+    if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState& d = g_dev[dev];
+    if (!d.ready) {
+        unsigned char* ptr = nullptr;
+        *what = "cudaGetSymbolAddress(static scratch)";
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_ffa_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (ptr == nullptr) return (int)cudaErrorInvalidSymbol;
+        *what = "device attribute query";
+        e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.smem_cta, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+        if (e != cudaSuccess) return (int)e;
+        d.scratch = ptr;
+        d.ready = true;
+    }
+    *dev_out = dev, *out = d;
+    return 0;
+}
+
 }  // namespace
+
+// Reads the status word the static-scratch calls on the current device OR their FFA_STATUS_*
+// bits into (calls made with device_status == NULL), then clears it: one 4-byte copy to the
+// caller's host int and one 4-byte clear, both on `stream`, then a stream synchronisation.
+// Allocates nothing.  Returns FFA_OK with *status == 0 when clean, FFA_ERR_DEVICE when a bit was set.
+extern "C" int ffa_static_scratch_status(void* stream, int* status)
+{
+    if (status == nullptr) return FFA_ERR_ARG;
+    int dev = 0;
+    DeviceState st;
+    const char* what = "";
+    if (device_state(&dev, &st, &what) != 0) return FFA_ERR_CUDA;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(status, st.scratch, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(st.scratch, 0, sizeof(int), s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return FFA_ERR_CUDA;
+    return *status != 0 ? FFA_ERR_DEVICE : FFA_OK;
+}
+
+// Diagnostic twin of ffa_selftest_wait_timeout for the static array: one warp waits, for at most
+// limit_ms, on a copy barrier nothing completes, gives up, and ORs FFA_STATUS_WAIT_TIMEOUT into the
+// static status word -- what a static-scratch decode step does when a bulk copy never lands.
+// Nothing faults or hangs; the next ffa_static_scratch_status must report the bit.
+extern "C" int ffa_static_scratch_selftest_wait_timeout(unsigned int limit_ms, void* stream)
+{
+    if (limit_ms == 0 || limit_ms > 2000) return FFA_ERR_RANGE;
+    int dev = 0;
+    DeviceState st;
+    const char* what = "";
+    if (device_state(&dev, &st, &what) != 0) return FFA_ERR_CUDA;
+    const int r = ffa_k_wait_selftest(reinterpret_cast<int*>(st.scratch), (unsigned long long)limit_ms * 1000000ull, nullptr,
+                                      static_cast<cudaStream_t>(stream));
+    return r == 0 ? FFA_OK : FFA_ERR_CUDA;
+}
 
 extern "C" int ffa_attention_static_scratch(int dtype, int batch, int heads, int head_dim, int max_len, const void* q,
                                             const void* k, const void* v, void* k_cache, void* v_cache, void* out,
@@ -81,33 +147,20 @@ extern "C" int ffa_attention_static_scratch(int dtype, int batch, int heads, int
 
     // ---- one-time set-up for the current device ----
     int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return fail(FFA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-    if (dev < 0 || dev >= kMaxDevices) return fail(FFA_ERR_ARG, "device ordinal %d not supported (max %d)", dev, kMaxDevices - 1);
     DeviceState st;
+    const char* what = "";
+    int ce = device_state(&dev, &st, &what);
+    if (ce != 0) return fail(FFA_ERR_CUDA, "%s: %s", what, cudaGetErrorString((cudaError_t)ce));
     {
         std::lock_guard<std::mutex> lock(g_mu);
-        DeviceState& d = g_dev[dev];
-        if (!d.ready) {
-            unsigned char* ptr = nullptr;
-            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_ffa_static_scratch);
-            if (e != cudaSuccess || ptr == nullptr)
-                return fail(FFA_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
-            e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
-            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.smem_cta, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
-            if (e != cudaSuccess) return fail(FFA_ERR_CUDA, "device attribute query: %s", cudaGetErrorString(e));
-            d.scratch = ptr;
-            d.ready = true;
-        }
         const unsigned bit = 1u << (dtype * 4 + dhi);
-        if (!(d.prepared & bit)) {
-            const int r = ffa_k_prepare(dtype, head_dim, d.smem_cta);
+        if (!(g_dev[dev].prepared & bit)) {
+            const int r = ffa_k_prepare(dtype, head_dim, st.smem_cta);
             if (r != 0) return fail(FFA_ERR_CUDA, "kernel preparation: %s", cudaGetErrorString((cudaError_t)r));
-            d.prepared |= bit;
+            g_dev[dev].prepared |= bit;
         }
-        st = d;
     }
+    cudaError_t e = cudaSuccess;
 
     // ---- launch shape: the engine's fixed rule (16 KB tiles, 4 compute warps, 2 CTAs/SM, 2 stages) ----
     const int es = dtype == FFA_DTYPE_F32 ? 4 : 2, rowb = head_dim * es;
@@ -137,8 +190,9 @@ extern "C" int ffa_attention_static_scratch(int dtype, int batch, int heads, int
                     "batch*heads = %lld with head_dim %d needs %zu bytes of scratch; the static scratch holds %zu "
                     "(use ffa_attention with a caller-allocated workspace)", BH, head_dim, need, kStaticScratchBytes);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // the array still holds the previous call's state: status word and arrival counters start at zero
-    e = cudaMemsetAsync(st.scratch, 0, partials_off, s);
+    // the array still holds the previous call's state: the arrival counters must start at zero (the
+    // status word is left alone so that error bits survive until ffa_static_scratch_status reads them)
+    e = cudaMemsetAsync(st.scratch + tickets_off, 0, partials_off - tickets_off, s);
     if (e != cudaSuccess) return fail(FFA_ERR_CUDA, "scratch clear: %s", cudaGetErrorString(e));
 
     FfaStepParams P;

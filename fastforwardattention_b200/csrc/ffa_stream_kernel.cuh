@@ -79,7 +79,8 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         flags[0] = 0, flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (cl && threadIdx.x < DH + 2) clp[threadIdx.x] = threadIdx.x == DH ? -CUDART_INF_F : 0.f;   // "nothing seen"
+    if (cl)
+        for (int i = threadIdx.x; i < DH + 2; i += blockDim.x) clp[i] = i == DH ? -CUDART_INF_F : 0.f;   // "nothing seen"
     __syncthreads();
 
     const int upb = P.units_per_bh;

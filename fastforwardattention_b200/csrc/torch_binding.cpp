@@ -86,8 +86,10 @@ struct FastForwardAttn {
         at::cuda::getCurrentCUDAStream().synchronize();
     }
 
-    // Grows both caches to new_max_len rows (contents kept), re-plans and re-binds the workspace.
-    // Tensors handed out by get_cache() before the call keep pointing at the old slabs.
+    // Grows both caches to new_max_len rows (contents kept), re-plans and re-binds the workspace; mode,
+    // pruning path, cluster merge and any launch override carry over.  Tensors handed out by
+    // get_cache() before the call keep pointing at the old slabs, and a CUDA graph recorded before
+    // it holds the old slabs' and workspace's addresses: record it again after growing.
     void grow(int64_t new_max_len)
     {
         TORCH_CHECK(new_max_len > Lmax && new_max_len < (int64_t(1) << 31), "FastForwardAttn.grow: new length ", new_max_len,
@@ -102,6 +104,9 @@ struct FastForwardAttn {
         ffa_plan_t* np = nullptr;
         check(ffa_plan_create(dtype, (int)B, (int)H, (int)Dh, (int)new_max_len, use_default, device.index(), &np), "plan");
         check(ffa_plan_set_mode(np, mode), "mode");
+        check(ffa_plan_set_prune_path(np, prune_path), "prune path");
+        check(ffa_plan_set_cluster_merge(np, cluster_merge ? 1 : 0), "cluster merge");
+        if (launch_forced) check(ffa_plan_set_launch(np, &forced_launch), "launch override");
         if (peer_world > 0) {
             std::vector<void*> bufs(peer_ptrs.begin(), peer_ptrs.end());
             check(ffa_peer_gather_attach(np, peer_world, peer_rank, bufs.data(), peer_bytes), "peer gather");
@@ -109,8 +114,8 @@ struct FastForwardAttn {
         stream.synchronize();   // the old slabs may be freed once the copy is done
         ffa_plan_destroy(plan);
         plan = np, k_cache = nk, v_cache = nv, Lmax = new_max_len;
-        kept_mask = torch::Tensor();
-        bind_workspace(false);
+        kept_mask = torch::Tensor();   // one bit per row of the old length; re-created on the next recorded call
+        bind_workspace(has_scores);
         stream.synchronize();
     }
     int64_t max_len() const { return Lmax; }
@@ -214,10 +219,14 @@ struct FastForwardAttn {
     }
     // c_ffa_api.h:17-20 semantics (per-sample lengths, right padding); not exported by the
     // reference's Python class, exported here so the mode is reachable from Python
+    // max_row: what the host knows about the lengths (every seq_lengths[b] <= max_row); the work is
+    // laid out for rows 0..max_row.  -1 = nothing known = max_len - 1.
     torch::Tensor attention_per_sample(torch::Tensor q, torch::Tensor k, torch::Tensor v, double softmax_scale,
-                                       torch::Tensor seq_lengths, double prob_thresh, c10::optional<torch::Tensor> out)
+                                       torch::Tensor seq_lengths, double prob_thresh, c10::optional<torch::Tensor> out,
+                                       int64_t max_row)
     {
-        return run(q, k, v, k_cache, v_cache, softmax_scale, 0, &seq_lengths, true, prob_thresh, out);
+        TORCH_CHECK(max_row >= -1 && max_row < Lmax, "FastForwardAttn: max_row ", max_row, " outside [-1, ", Lmax, ")");
+        return run(q, k, v, k_cache, v_cache, softmax_scale, max_row < 0 ? Lmax - 1 : max_row, &seq_lengths, true, prob_thresh, out);
     }
 
     std::pair<torch::Tensor, torch::Tensor> get_cache() { return std::make_pair(k_cache, v_cache); }
@@ -228,13 +237,22 @@ struct FastForwardAttn {
         mode = m == "exact" ? FFA_MODE_EXACT : FFA_MODE_ROUND_LIKE_TORCH;
         check(ffa_plan_set_mode(plan, mode), "mode");
     }
-    void set_prune_path(int path) { check(ffa_plan_set_prune_path(plan, path), "prune path"); }
-    void set_cluster_merge(bool on) { check(ffa_plan_set_cluster_merge(plan, on ? 1 : 0), "cluster merge"); }
+    void set_prune_path(int path)
+    {
+        check(ffa_plan_set_prune_path(plan, path), "prune path");
+        prune_path = path;
+    }
+    void set_cluster_merge(bool on)
+    {
+        check(ffa_plan_set_cluster_merge(plan, on ? 1 : 0), "cluster merge");
+        cluster_merge = on;
+    }
     void set_launch(int tile_rows, int stages, int consumer_warps, int ctas_per_sm, int grid)
     {
         ffa_launch_t l{tile_rows, stages, consumer_warps, ctas_per_sm, grid, 0, 0};
         const bool any = tile_rows > 0 || stages > 0 || consumer_warps > 0 || ctas_per_sm > 0 || grid > 0;
         check(ffa_plan_set_launch(plan, any ? &l : nullptr), "launch override");
+        launch_forced = any, forced_launch = l;
     }
     py::dict launch_shape(int64_t t)
     {
@@ -346,8 +364,9 @@ struct FastForwardAttn {
     torch::Tensor k_cache, v_cache, workspace, kept_mask;
     c10::Device device{c10::kCUDA, 0};
     int64_t B = 0, H = 0, Dh = 0, Lmax = 0;
-    int dtype = 0, mode = FFA_MODE_EXACT;
-    bool has_scores = false, want_mask = false, use_default = false;
+    int dtype = 0, mode = FFA_MODE_EXACT, prune_path = 0;
+    bool has_scores = false, want_mask = false, use_default = false, cluster_merge = true, launch_forced = false;
+    ffa_launch_t forced_launch{};
     void* peer_own = nullptr;
     std::vector<void*> peer_ptrs;
     size_t peer_bytes = 0;
@@ -440,10 +459,13 @@ struct PagedEngine {
     {
         return run(q, k, v, table, scale, t, nullptr, prob_thresh, out);
     }
+    // max_row: the host's upper bound on rows[b] (-1: nothing known = the last row of the last page)
     torch::Tensor attention_per_sample(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor table, double scale,
-                                       torch::Tensor rows, double prob_thresh, c10::optional<torch::Tensor> out)
+                                       torch::Tensor rows, double prob_thresh, c10::optional<torch::Tensor> out, int64_t max_row)
     {
-        return run(q, k, v, table, scale, 0, &rows, prob_thresh, out);
+        TORCH_CHECK(max_row >= -1 && max_row < max_pages * page_rows, "PagedEngine: max_row ", max_row, " outside [-1, ",
+                    max_pages * page_rows, ")");
+        return run(q, k, v, table, scale, max_row < 0 ? max_pages * page_rows - 1 : max_row, &rows, prob_thresh, out);
     }
     void set_mode(const std::string& m)
     {
@@ -502,7 +524,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("attention_per_sample", &FastForwardAttn::attention_per_sample,
              "decode step with per-sample cache lengths (right padding): sample b appends at row seq_lengths[b]", py::arg("q"),
              py::arg("k"), py::arg("v"), py::arg("softmax_scale"), py::arg("seq_lengths"), py::arg("prob_thresh") = 0.0,
-             py::arg("out") = py::none())
+             py::arg("out") = py::none(), py::arg("max_row") = -1)
         .def("set_mode", &FastForwardAttn::set_mode, "'exact' (default) or 'round_like_torch'")
         .def("set_prune_path", &FastForwardAttn::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
         .def("set_cluster_merge", &FastForwardAttn::set_cluster_merge, "merge split pairs inside a thread-block cluster (default on)")
@@ -530,7 +552,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
              py::arg("out") = py::none())
         .def("attention_per_sample", &PagedEngine::attention_per_sample, "decode step, sequence b at row rows[b]", py::arg("q"),
              py::arg("k"), py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("rows"),
-             py::arg("prob_thresh") = 0.0, py::arg("out") = py::none())
+             py::arg("prob_thresh") = 0.0, py::arg("out") = py::none(), py::arg("max_row") = -1)
         .def("set_mode", &PagedEngine::set_mode, "'exact' (default) or 'round_like_torch'")
         .def("set_prune_path", &PagedEngine::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
         .def("record_kept_mask", &PagedEngine::record_kept_mask)

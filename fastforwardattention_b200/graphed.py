@@ -11,10 +11,24 @@ of a step independent of the token position, so the step can be captured once:
 
 The graph holds: the attention launch on the engine's own caches and the increment of the
 row counter.  q, k and v are copied into static buffers before every replay.
+
+The engine lays its work out for an upper bound on the row index that the host states at
+launch time.  A graph therefore covers a bucket of rows (bound 127, 255, 511, ... up to the
+cache length) and is recorded again, lazily, when the generation enters the next bucket -- a
+dozen recordings over a whole generation, each a few hundred microseconds -- so that a mostly
+empty cache does not leave most CTAs without rows.
 """
 from __future__ import annotations
 
 import torch
+
+
+def row_bucket(row: int, max_len: int) -> int:
+    """Upper bound of the bucket of rows that `row` falls in: 2^k - 1 >= max(row, 127), capped at max_len - 1."""
+    bound = 127
+    while bound < row:
+        bound = 2 * bound + 1
+    return min(bound, max_len - 1)
 
 
 class GraphedStep:
@@ -31,25 +45,37 @@ class GraphedStep:
         self.out = torch.zeros(B, H, Dh, dtype=dt, device=dev)
         self.rows = torch.full((B,), first_row, dtype=torch.int32, device=dev)
         self.next_row = first_row
+        self.scale, self.p = softmax_scale, prob_thresh
         # warm-up on a side stream (lazy initialisation must not happen inside the capture);
         # it writes row `first_row` with zeros, which the first real step overwrites
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            ffa.attention_per_sample(self.q, self.k, self.v, softmax_scale, self.rows, prob_thresh, out=self.out)
+            ffa.attention_per_sample(self.q, self.k, self.v, softmax_scale, self.rows, prob_thresh, out=self.out,
+                                     max_row=row_bucket(first_row, Lmax))
         torch.cuda.current_stream(dev).wait_stream(side)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
-            ffa.attention_per_sample(self.q, self.k, self.v, softmax_scale, self.rows, prob_thresh, out=self.out)
-            self.rows.add_(1)
+        self.graphs = {}
+        self._graph_for(first_row)
+
+    def _graph_for(self, row: int) -> torch.cuda.CUDAGraph:
+        bound = row_bucket(row, self.max_len)
+        graph = self.graphs.get(bound)
+        if graph is None:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.ffa.attention_per_sample(self.q, self.k, self.v, self.scale, self.rows, self.p, out=self.out, max_row=bound)
+                self.rows.add_(1)
+            self.graphs[bound] = graph
+        return graph
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         if self.next_row >= self.max_len:
             raise RuntimeError(f"the cache is full ({self.max_len} rows)")
+        graph = self._graph_for(self.next_row)
         self.q.copy_(q.view_as(self.q), non_blocking=True)
         self.k.copy_(k.view_as(self.k), non_blocking=True)
         self.v.copy_(v.view_as(self.v), non_blocking=True)
-        self.graph.replay()
+        graph.replay()
         self.next_row += 1
         return self.out
 
@@ -75,10 +101,11 @@ class GraphedLayers:
 
     `attend(i, q, k, v)` runs engine i with the row index read from device memory; the graph
     ends with one increment of that index, shared by all layers.  `body` is traced once for a
-    warm-up (so that libraries it calls create their handles outside the capture) and once for
-    the capture; it must be free of host synchronisation and of data-dependent control flow.
-    The warm-up writes row `first_row` of every layer's cache, which the first real step
-    overwrites.
+    warm-up (so that libraries it calls create their handles outside the capture) and once per
+    bucket of rows for a capture (see the module text); it must be free of host
+    synchronisation and of data-dependent control flow, and must return the same kind of
+    result every time.  The warm-up writes row `first_row` of every layer's cache, which the
+    first real step overwrites.
     """
 
     def __init__(self, engines, softmax_scale: float, first_row: int, body, example_input: torch.Tensor,
@@ -97,24 +124,38 @@ class GraphedLayers:
         self.x = example_input.detach().clone().to(dev)
         self.rows = torch.full((B,), first_row, dtype=torch.int32, device=dev)
         self.outs = [torch.zeros(B, H, Dh, dtype=kc.dtype, device=dev) for _ in engines]
-
-        def attend(i: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-            return self.engines[i].attention_per_sample(q, k, v, softmax_scale, self.rows, prob_thresh, out=self.outs[i])
+        self.body, self.scale, self.p = body, softmax_scale, prob_thresh
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side), torch.no_grad():
-            body(self.x, attend)
+            body(self.x, self._attend(row_bucket(first_row, Lmax)))
         torch.cuda.current_stream(dev).wait_stream(side)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"), torch.no_grad():
-            self.y = body(self.x, attend)
-            self.rows.add_(1)
+        self.graphs = {}
+        self._graph_for(first_row)
+
+    def _attend(self, bound: int):
+        def attend(i: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+            return self.engines[i].attention_per_sample(q, k, v, self.scale, self.rows, self.p, out=self.outs[i], max_row=bound)
+
+        return attend
+
+    def _graph_for(self, row: int):
+        bound = row_bucket(row, self.max_len)
+        entry = self.graphs.get(bound)
+        if entry is None:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"), torch.no_grad():
+                y = self.body(self.x, self._attend(bound))
+                self.rows.add_(1)
+            entry = self.graphs[bound] = (graph, y)
+        return entry
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if self.next_row >= self.max_len:
             raise RuntimeError(f"the caches are full ({self.max_len} rows)")
+        graph, y = self._graph_for(self.next_row)
         self.x.copy_(x, non_blocking=True)
-        self.graph.replay()
+        graph.replay()
         self.next_row += 1
-        return self.y
+        return y

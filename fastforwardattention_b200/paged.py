@@ -89,7 +89,8 @@ class PagedFastForwardAttn:
         for b, n in enumerate(self.lengths):
             if n % self.pool.page_rows == 0:
                 self._ensure_page(b, n)
-        res = self.engine.attention_per_sample(q, k, v, self.table, softmax_scale, self.rows, prob_thresh, out=out)
+        res = self.engine.attention_per_sample(q, k, v, self.table, softmax_scale, self.rows, prob_thresh, out=out,
+                                               max_row=max(self.lengths))
         self.rows += 1
         self.lengths = [n + 1 for n in self.lengths]
         return res

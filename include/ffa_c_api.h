@@ -49,7 +49,7 @@ enum {
 /* Bits of the device status word (ffa_device_status). */
 enum {
     FFA_STATUS_WAIT_TIMEOUT = 1, /* a bounded wait on a copy barrier ran out */
-    FFA_STATUS_BAD_LENGTH = 2    /* a per-sample length was outside [0, max_len) */
+    FFA_STATUS_BAD_LENGTH = 2    /* a per-sample length was outside [0, max_len) or above the stated bound */
 };
 
 typedef struct ffa_plan ffa_plan_t;
@@ -133,7 +133,13 @@ int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* st
 /* One decode step.  q, k, v: batch*heads*head_dim contiguous elements in (batch, head, dim)
  * order.  Writes k and v into row `row` of the caches and out[batch, heads, head_dim], where
  *   seq_lengths == NULL                      : row = t for every sample, all keys visible;
- *   seq_lengths != NULL, right_or_no_padding : row = seq_lengths[b] (per-sample lengths);
+ *   seq_lengths != NULL, right_or_no_padding : row = seq_lengths[b] (per-sample lengths); t is then
+ *                                              the host's upper bound on every seq_lengths[b]: the
+ *                                              work is laid out for rows 0..t, so a tight bound keeps
+ *                                              all CTAs busy when the cache is mostly empty; pass
+ *                                              max_len - 1 when nothing is known.  A sample whose
+ *                                              length exceeds t is skipped and reported as
+ *                                              FFA_STATUS_BAD_LENGTH, never cut short;
  *   seq_lengths != NULL, !right_or_no_padding: row = t, keys < seq_lengths[b] are masked
  *                                              (left padding).
  * q, k, v and out may also point into pinned (page-locked, device-addressable) host memory: the
@@ -172,18 +178,29 @@ int ffa_attention_paged(ffa_plan_t* plan, const void* q, const void* k, const vo
  *     256 + 4*batch*heads + 4*(grid + batch*heads)*(head_dim + 2) bytes, grid <= 2 CTAs per SM;
  *     e.g. batch*heads = 1024 at head_dim 128 needs 0.7 MiB); use ffa_attention beyond that;
  *   - the array is shared by every call on that GPU and keeps the previous call's contents;
- *     each call clears the counters and status word on `stream` before launching, and calls
- *     whose kernels overlap on one GPU (other streams, other host threads) race -- keep them
+ *     each call clears the arrival counters on `stream` before launching, and calls whose
+ *     kernels overlap on one GPU (other streams, other host threads) race -- keep them
  *     stream-ordered;
  *   - the first call on each device performs a one-time set-up (device address of the array,
  *     device queries, kernel attributes); make that first call outside any stream capture.
  * Arguments as for ffa_attention.  device_status: optional DEVICE int the kernel ORs its
- * FFA_STATUS_* bits into (caller-owned, caller-cleared); NULL keeps them in the static
- * array.  error_text: optional HOST buffer that receives the reason for a non-zero return. */
+ * FFA_STATUS_* bits into (caller-owned, caller-cleared); with NULL the bits accumulate in a
+ * status word inside the static array, which no call clears and ffa_static_scratch_status
+ * reads.  error_text: optional HOST buffer that receives the reason for a non-zero return. */
 int ffa_attention_static_scratch(int dtype, int batch, int heads, int head_dim, int max_len, const void* q,
                                  const void* k, const void* v, void* k_cache, void* v_cache, void* out,
                                  float softmax_scale, int t, int* device_status, void* stream, char* error_text,
                                  size_t error_text_len);
+
+/* Companion of ffa_attention_static_scratch (no counterpart in the reference either): copies the
+ * static array's status word of the current device to the HOST int *status, clears the word,
+ * synchronises `stream`.  Allocates nothing.  FFA_OK when *status == 0, FFA_ERR_DEVICE when a
+ * FFA_STATUS_* bit was set by any static-scratch call since the last read. */
+int ffa_static_scratch_status(void* stream, int* status);
+/* Diagnostic for that status word, like ffa_selftest_wait_timeout below: one warp waits at most
+ * limit_ms (1..2000) on a copy barrier nothing completes, gives up and records
+ * FFA_STATUS_WAIT_TIMEOUT in the static status word.  Nothing faults or hangs. */
+int ffa_static_scratch_selftest_wait_timeout(unsigned int limit_ms, void* stream);
 
 /* Synchronises the stream and returns the device status word (0 = clean) in *status, then
  * clears it.  The reference only printf()s cudaGetLastError (attention.cu:1444-1451). */

@@ -31,3 +31,29 @@ def load_golden(name):
         i += 1
     return {"dtype": dt, "K": _t(z["K"], dt), "V": _t(z["V"], dt), "scale": float(z["scale"]),
             "prompt": int(z["prompt"]), "steps": steps}
+
+
+ULP = {torch.float32: 2.0 ** -23, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
+
+
+def max_err(a, b):
+    return (a.double().cpu() - b.double().cpu()).abs().max().item()
+
+
+def assert_close_ulp(got, ref64, dtype, what, ulps=1.0, floor=None):
+    """|got - ref| <= ulps * ulp(|ref|) + floor, element-wise; ref is the fp64 value."""
+    floor = floor if floor is not None else {torch.float32: 1e-6, torch.float16: 2e-4, torch.bfloat16: 2e-4}[dtype]
+    err = (got.double().cpu() - ref64).abs()
+    bound = ulps * ULP[dtype] * ref64.abs() + floor
+    bad = err > bound
+    assert not bad.any(), f"{what}: {int(bad.sum())} elements off, worst {err.max().item():.3e}"
+
+
+def same_dtype_gate(got, same, ref64, dtype, what):
+    """The stated gate against the same-dtype torch function, widened only by that
+    function's own measured distance from the fp64 value of the same inputs."""
+    noise = max_err(same, ref64)
+    err = max_err(got, same)
+    assert err <= max(TOL[dtype], 1.25 * noise + ULP[dtype] * ref64.abs().max().item()), \
+        f"{what}: err vs same-dtype torch {err:.3e}, oracle noise {noise:.3e}"
+    return err, noise

@@ -79,7 +79,8 @@ def run_random_steps(seed, rng, dt, Dh, B, H, Lmax, force_launch):
                                 right_or_no_padding=False, want_mask=p > 0)
         else:
             rows, first = [rng.randint(0, Lmax - 1) for _ in range(B)], [0] * B
-            got = eng.attention(q, k, v, scale, 0, p=p, seq_lengths=torch.tensor(rows, dtype=torch.int32),
+            bound = rng.choice([max(rows), Lmax - 1])   # what the host knows about the lengths: tight or nothing
+            got = eng.attention(q, k, v, scale, bound, p=p, seq_lengths=torch.tensor(rows, dtype=torch.int32),
                                 right_or_no_padding=True, want_mask=p > 0)
         outs, kepts, border = oracle_step(q, Kc, Vc, k, v, scale, rows, first, p, dt)
         tol = {torch.float32: 2e-6, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dt]

@@ -17,35 +17,9 @@ from fastforwardattention_b200 import capi
 from fastforwardattention_b200.workloads import CONFIGS, Workload, device_prompt_kv, prompt_kv, step_qkv
 from oracle import ffa_oracle as O
 from tests.cabi_engine import CAbiEngine
-from tests.helpers import TOL, golden_names, load_golden
+from tests.helpers import TOL, ULP, assert_close_ulp, golden_names, load_golden, max_err, same_dtype_gate
 
 pytestmark = pytest.mark.gpu
-
-ULP = {torch.float32: 2.0 ** -23, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
-
-
-def max_err(a, b):
-    return (a.double().cpu() - b.double().cpu()).abs().max().item()
-
-
-def assert_close_ulp(got, ref64, dtype, what, ulps=1.0, floor=None):
-    """|got - ref| <= ulps * ulp(|ref|) + floor, element-wise; ref is the fp64 value."""
-    floor = floor if floor is not None else {torch.float32: 1e-6, torch.float16: 2e-4, torch.bfloat16: 2e-4}[dtype]
-    err = (got.double().cpu() - ref64).abs()
-    bound = ulps * ULP[dtype] * ref64.abs() + floor
-    bad = err > bound
-    assert not bad.any(), f"{what}: {int(bad.sum())} elements off, worst {err.max().item():.3e}"
-
-
-def same_dtype_gate(got, same, ref64, dtype, what):
-    """The stated gate against the same-dtype torch function, widened only by that
-    function's own measured distance from the fp64 value of the same inputs."""
-    noise = max_err(same, ref64)
-    err = max_err(got, same)
-    assert err <= max(TOL[dtype], 1.25 * noise + ULP[dtype] * ref64.abs().max().item()), \
-        f"{what}: err vs same-dtype torch {err:.3e}, oracle noise {noise:.3e}"
-    return err, noise
-
 
 # ------------------------------------------------------------------------------------------
 # golden fixtures (outputs of the reference's own function text)
@@ -317,7 +291,7 @@ def test_per_sample_lengths_right_padding(dt):
     eng = CAbiEngine(K, V, Lmax)
     eng.set_launch(tile_rows=16)
     q, k, v = qkv(g, B, H, Dh, dt)
-    got = eng.attention(q, k, v, Dh ** -0.5, 0, seq_lengths=lens, right_or_no_padding=True)
+    got = eng.attention(q, k, v, Dh ** -0.5, Lmax - 1, seq_lengths=lens, right_or_no_padding=True)
     for b in range(B):
         L = int(lens[b])
         Kb = torch.cat([K[b, :, :L], k[b]], dim=1)
@@ -329,8 +303,25 @@ def test_per_sample_lengths_right_padding(dt):
     assert eng.status() == 0
     # a length outside the cache is reported, not written
     bad = torch.tensor([0, 17, 100, 5], dtype=torch.int32)
-    eng.attention(q, k, v, Dh ** -0.5, 0, seq_lengths=bad, right_or_no_padding=True)
+    eng.attention(q, k, v, Dh ** -0.5, Lmax - 1, seq_lengths=bad, right_or_no_padding=True)
     assert eng.status() & 2
+    # a tight bound on the lengths (what a host that tracks them passes) gives the same result ...
+    short = torch.tensor([0, 17, 30, 9], dtype=torch.int32)
+    eng2 = CAbiEngine(K, V, Lmax)
+    a = eng2.attention(q, k, v, Dh ** -0.5, 30, seq_lengths=short, right_or_no_padding=True)
+    eng3 = CAbiEngine(K, V, Lmax)
+    b = eng3.attention(q, k, v, Dh ** -0.5, Lmax - 1, seq_lengths=short, right_or_no_padding=True)
+    for bb in range(B):
+        L = int(short[bb])
+        ref = O.attention_reference(q[bb], torch.cat([K[bb, :, :L], k[bb]], dim=1), torch.cat([V[bb, :, :L], v[bb]], dim=1),
+                                    Dh ** -0.5, torch.float64)
+        assert_close_ulp(a[bb], ref, dt, f"tight bound, sample {bb}")
+        assert_close_ulp(b[bb], ref, dt, f"loose bound, sample {bb}")
+    assert eng2.status() == 0 and eng3.status() == 0
+    # ... and a length above the stated bound is refused and reported, never cut short
+    eng2.attention(q, k, v, Dh ** -0.5, 29, seq_lengths=short, right_or_no_padding=True)
+    assert eng2.status() & 2
+    assert torch.equal(eng2.k_cache[2, :, 31:].cpu(), K[2, :, 31:])
 
 
 # ------------------------------------------------------------------------------------------

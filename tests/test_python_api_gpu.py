@@ -180,6 +180,33 @@ def test_graphed_step_helper():
     assert ffa.device_status() == 0
 
 
+def test_graphed_step_in_a_mostly_empty_cache_crosses_row_buckets():
+    """The graph is recorded for a bucket of rows (the engine lays its work out for the bucket's upper
+    bound, not for the whole cache) and again when the generation enters the next bucket."""
+    from fastforwardattention_b200 import FastForwardAttn, GraphedStep
+    from fastforwardattention_b200.graphed import row_bucket
+
+    assert [row_bucket(r, 4096) for r in (0, 127, 128, 255, 256, 4000)] == [127, 127, 255, 255, 511, 4095]
+    assert row_bucket(10, 50) == 49
+    dt = torch.float16
+    g = torch.Generator().manual_seed(13)
+    B, H, Dh, Lp, n, Lmax = 2, 4, 64, 120, 14, 4096
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    ffa = FastForwardAttn(K.cuda(), V.cuda(), Lmax, False)
+    step = GraphedStep(ffa, Dh ** -0.5, first_row=Lp)
+    orc = O.DecodeOracle(K, V, Lp + n, compute_dtype=torch.float64)
+    for i in range(n):
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        out = step(q.cuda(), k.cuda(), v.cuda())
+        ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
+        assert (out.cpu().double() - ref).abs().max().item() <= 1e-3, i
+    assert sorted(step.graphs) == [127, 255]
+    assert ffa.device_status() == 0
+    kc, _ = ffa.get_cache()
+    assert torch.equal(kc[:, :, Lp + n - 1].cpu(), k[:, :, 0])
+
+
 def test_graphed_layers_whole_token_in_one_graph():
     """A toy decoder (three layers, fp32 projections between the attention calls) replayed from
     one CUDA graph gives what the same layers give when called one by one."""
