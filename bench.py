@@ -34,11 +34,15 @@ from fastforwardattention_b200.workloads import CONFIGS, device_prompt_kv, devic
 METRIC = "decode_attention_steps_per_sec"
 DTYPE_NAME = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}   # storage type; sums are fp32
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the streaming kernel divided by
-# the launch's algorithmic bytes, from the ncu capture summarised under profiles/ (captured on
-# the 2048-token case and scaled by bytes streamed, which is what the kernel's traffic is
-# proportional to).
-TRAFFIC_RATIO = 1.004
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch divided by the launch's algorithmic
+# bytes, from one ncu capture per kernel (the exact kernel on the bf16 head_dim-128 2048-token
+# case, the pruning kernel on the fp16 head_dim-64 pruning configuration), scaled by the bytes a
+# launch streams, which is what both kernels' traffic is proportional to.
+TRAFFIC_RATIO = {"exact": 1.004, "pruned": 0.99}
+# workloads reported in the `configs` key next to the headline (kernel time only, N = 1)
+EXTRA_CONFIGS = ("opt13b-fp32-b1", "opt13b-fp16-b10", "gptj-fp16-b8", "prune-fp16-b10-p1e-3", "long-512", "long-2048",
+                 "long-8192")
+ROUND_LIKE_TORCH_CONFIGS = ("long-512", "long-2048")
 
 
 def algorithmic_bytes(es, B, H, Dh, t, kept_frac=None):
@@ -175,6 +179,138 @@ def run_reference(args, w):
     print(json.dumps(line))
 
 
+def replicas_for(w):
+    """Engines a workload needs so that consecutive steps stream from HBM, not from the 126 MB L2:
+    one when its KV is >= 600 MB, else enough replicas (own caches each) to reach 600 MB together."""
+    kv_bytes = 2 * w.B * w.H * w.max_len * w.Dh * w.dtype.itemsize
+    return 1 if kv_bytes >= 600e6 else min(16, -(-int(600e6) // kv_bytes))
+
+
+def kept_fraction(engine, step):
+    """Share of cached V rows that survive the threshold, counted from the kept mask of one step."""
+    engine.record_kept_mask(True)
+    t = step()
+    m = engine.get_kept_mask().view(-1)
+    bits = sum(int(((m >> i) & 1).sum()) for i in range(32))
+    engine.record_kept_mask(False)
+    return bits / (m.numel() // ((engine.max_len + 31) // 32) * (t + 1))
+
+
+def graph_replay_ms(step, steps):
+    """Records `steps` consecutive calls of step(i) in one CUDA graph and returns the device time
+    of one replay divided by `steps`: no host work between the launches."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step(0)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):   # other threads (NCCL watchdog) keep running
+        for i in range(steps):
+            step(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    graph.replay()
+    g1.record()
+    torch.cuda.synchronize()
+    return g0.elapsed_time(g1) / steps
+
+
+def measure_config(name, dev, peak, mode=None, steps=32):
+    """Kernel time of one workload at its last decode step: `steps` launches over rotating
+    replicas replayed from a CUDA graph, CUDA events around the replay."""
+    from dataclasses import replace
+
+    from fastforwardattention_b200 import FastForwardAttn
+
+    w = CONFIGS[name]
+    nrep = replicas_for(w)
+    engines = []
+    for r in range(nrep):
+        K, V = device_prompt_kv(w if w.peaked else replace(w, seed=w.seed + 17 * r), dev)
+        engines.append(FastForwardAttn(K, V, w.max_len, False))
+        kc, vc = engines[-1].get_cache()     # rows the decode steps would have filled
+        kc[:, :, w.prompt:].normal_()
+        vc[:, :, w.prompt:].normal_()
+        if mode:
+            engines[-1].set_mode(mode)
+        del K, V
+    qkv = device_step_qkv(w, 4, dev)
+    out = torch.empty(w.B, w.H, w.Dh, dtype=w.dtype, device=dev)
+    t = w.max_len - 1
+
+    def step(i):
+        engines[i % nrep].attention(qkv[i % 4, 0], qkv[i % 4, 1], qkv[i % 4, 2], w.scale, t, w.p, out=out)
+        return t
+
+    for i in range(nrep):
+        step(i)
+    ms = graph_replay_ms(step, steps)
+    kept = kept_fraction(engines[0], lambda: step(0)) if w.p > 0 else None
+    alg = algorithmic_bytes(w.dtype.itemsize, w.B, w.H, w.Dh, t, kept)
+    gbs = alg / (ms * 1e-3) / 1e9
+    res = {"workload": name, "dtype": DTYPE_NAME[w.dtype], "batch": w.B, "heads": w.H, "head_dim": w.Dh, "rows": t + 1,
+           "p": w.p, "mode": mode or "exact", "kernel_us": round(ms * 1e3, 2), "bytes_per_launch": alg,
+           "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "kept_v_rows": kept, "replicas": nrep,
+           "launch_shape": dict(engines[0].launch_shape(t)), "device_status": max(e.device_status() for e in engines)}
+    del engines
+    torch.cuda.empty_cache()
+    return res
+
+
+def result_check(w, world, rank, engine, sharded, host_step, qkv_host, t, dev):
+    """One step outside the timed regions, checked three ways: (N > 1) the gathered [B, H, Dh]
+    holds this rank's own shard bit for bit and equals an NCCL all-gather of the same shards;
+    the tensor the end-to-end step leaves in pinned host memory agrees with the per-call path;
+    four sampled (batch, head) pairs of this rank's shard agree with the checker's float64
+    evaluation of softmax(q K^T scale) V over the cache rows 0..t."""
+    import torch.distributed as dist
+
+    from oracle.ffa_oracle import attention_reference, pruned_attention   # the checker, not the product
+
+    q, k, v = (qkv_host[i].to(dev) for i in range(3))
+    local = engine.attention(q, k, v, w.scale, t, w.p)
+    full, res = local, {"ok": True}
+    if world > 1:
+        full = sharded.gather(local)
+        ref = torch.empty(world, w.B, w.H, w.Dh, dtype=w.dtype, device=dev)
+        dist.all_gather_into_tensor(ref.view(-1), local.contiguous().view(-1))
+        ref = ref.permute(1, 0, 2, 3).reshape(w.B, world * w.H, w.Dh)
+        res["own_shard_bitwise"] = bool(torch.equal(full[:, rank * w.H:(rank + 1) * w.H], local))
+        res["equals_nccl_all_gather"] = bool(torch.equal(full, ref))
+        res["ok"] = res["own_shard_bitwise"] and res["equals_nccl_all_gather"]
+    if host_step is not None:
+        # the same step again through the graphed end-to-end path (row t is rewritten with the same k, v)
+        host_step.reset_row(t)
+        out_host = host_step(qkv_host)
+        torch.cuda.current_stream().synchronize()
+        res["graphed_vs_per_call_max_diff"] = (out_host.float() - full.cpu().float()).abs().max().item()
+        res["ok"] = res["ok"] and res["graphed_vs_per_call_max_diff"] <= 2e-3
+        delivered = out_host.clone()
+    else:
+        delivered = full.cpu()
+    kc, vc = engine.get_cache()
+    g = torch.Generator().manual_seed(4242 + rank)
+    worst = 0.0
+    for _ in range(4):
+        b, h = int(torch.randint(w.B, (1,), generator=g)), int(torch.randint(w.H, (1,), generator=g))
+        Kp, Vp, qp = kc[b, h, :t + 1].cpu()[None], vc[b, h, :t + 1].cpu()[None], qkv_host[0][b, h]
+        if w.p > 0:
+            ref64 = pruned_attention(qp.view(1, w.Dh), Kp, Vp, w.scale, w.p)[0][0].double()   # the pruning rule, restated
+        else:
+            ref64 = attention_reference(qp.view(1, 1, w.Dh), Kp, Vp, w.scale, torch.float64)[0]
+        worst = max(worst, (delivered[b, rank * w.H + h].double() - ref64).abs().max().item())
+    tol = 1e-6 if w.dtype == torch.float32 else 2e-3
+    res.update({"max_err": worst, "tolerance": tol, "pairs_checked_per_rank": 4,
+                "against": "float64 evaluation of softmax(q K^T scale) V on the cache rows" if w.p == 0 else
+                "the restated pruning rule on the cache rows"})
+    res["ok"] = res["ok"] and worst <= tol
+    return res
+
+
 def workload_config(w, n):
     return {"workload": w.name, "batch": w.B, "heads": w.H, "head_dim": w.Dh, "prompt": w.prompt,
             "decode_steps": w.steps, "final_len": w.max_len, "p": w.p,
@@ -193,9 +329,9 @@ def main():
     ap.add_argument("--workload", default="long-32768", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the `configs` key (the other configurations, N = 1)")
     ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
                     help="N > 1: output all-gather by the engine's peer-memory kernel (default) or by NCCL")
-    ap.add_argument("--launch", default="", help="tile_rows,stages,consumer_warps,ctas_per_sm override (tuning)")
     args = ap.parse_args()
     full = CONFIGS[args.workload]
     if args.impl == "reference":
@@ -221,8 +357,7 @@ def main():
     # 126 MB L2 gets replicas with their own caches, used round-robin, so that every timed step
     # streams from HBM without a flush kernel in between (a zero-fill flush leaves dirty lines
     # whose write-back then competes with the step being timed).
-    kv_bytes = 2 * w.B * w.H * w.max_len * w.Dh * es
-    nrep = 1 if kv_bytes >= 600e6 else min(16, -(-int(600e6) // kv_bytes))
+    nrep = replicas_for(w)
     from dataclasses import replace
 
     sharded, engines = [], []
@@ -240,9 +375,6 @@ def main():
     if world > 1:
         peer_ok = args.gather == "peer" and all([s.enable_peer_gather() for s in sharded])
         gather_kind = "peer-memory kernel" if peer_ok else "nccl all_gather_into_tensor"
-    if args.launch:
-        for e in engines:
-            e.set_launch(*[int(x) for x in args.launch.split(",")])
     shape = engines[0].launch_shape(w.max_len - 1)
 
     total = args.warmup + args.steps
@@ -261,7 +393,7 @@ def main():
     def resident_step(s):
         engines[s % nrep].attention(qkv_d[s, 0], qkv_d[s, 1], qkv_d[s, 2], w.scale, t_of(s), w.p, out=out_d)
 
-    def e2e_step(s):
+    def eager_e2e_step(s):
         stage.copy_(qkv_h[s], non_blocking=True)
         if world > 1:
             o = sharded[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), w.p, gather=True)
@@ -269,6 +401,27 @@ def main():
             o = engines[s % nrep].attention(stage[0], stage[1], stage[2], w.scale, t_of(s), w.p)
         out_h.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the caller consumes the result every step
+
+    # The end-to-end step of the public API: GraphedHostStep / ShardedFastForwardAttn.graphed_step -- one
+    # upload of the step's q/k/v from pinned host memory, one replay of a CUDA graph holding the attention
+    # launch (row index in device memory), the peer-memory all-gather (N > 1) and the download of the
+    # result into pinned host memory, then the stream sync with which the caller takes the result.
+    host_steps = None
+    if world == 1 or gather_kind == "peer-memory kernel":
+        from fastforwardattention_b200 import GraphedHostStep
+
+        host_steps = [sharded[r].graphed_step(w.scale, w.prompt, w.p) if world > 1 else
+                      GraphedHostStep(engines[r], w.scale, w.prompt, w.p) for r in range(nrep)]
+
+    def e2e_step(s):
+        if host_steps is None:
+            return eager_e2e_step(s)
+        hs = host_steps[s % nrep]
+        if hs.next_row != t_of(s):
+            hs.reset_row(t_of(s))
+        hs(qkv_h[s])
+        torch.cuda.current_stream().synchronize()   # the caller consumes hs.out_host every step
+        return hs.out_host
 
     clocks = ClockSampler(gpu_id(dev)).start()
 
@@ -296,50 +449,31 @@ def main():
     # the kernel's own duration for the roofline: the same K launches recorded in a CUDA graph and
     # replayed, so no host work sits between them (matters when a launch is shorter than the
     # host's per-call time); CUDA events around the replay, on the replay's stream
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        resident_step(args.warmup)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, capture_error_mode="thread_local"):   # other threads (NCCL watchdog) keep running
-        for i in range(args.steps):
-            resident_step(args.warmup + i)
-    graph.replay()
-    torch.cuda.synchronize()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g0.record()
-    graph.replay()
-    g1.record()
-    torch.cuda.synchronize()
-    graph_ms = g0.elapsed_time(g1) / args.steps
+    graph_ms = graph_replay_ms(lambda i: resident_step(args.warmup + i), args.steps)
     # long launches: the timed region itself is the kernel time (host gaps are < 0.5 %); short ones: the replay
     use_region = loop_ms / args.steps >= 0.2
     kernel_ms = [loop_ms / args.steps if use_region else graph_ms] * args.steps
     kept_frac = None
     if w.p > 0:
-        # share of cached V rows that survive the threshold, counted from the kept mask of one step
         s_last = args.warmup + args.steps - 1
-        engines[s_last % nrep].record_kept_mask(True)
-        resident_step(s_last)
-        m = engines[s_last % nrep].get_kept_mask().view(-1)
-        bits = sum(int(((m >> i) & 1).sum()) for i in range(32))
-        kept_frac = bits / (w.B * w.H * (t_of(s_last) + 1))
-        engines[s_last % nrep].record_kept_mask(False)
+        kept_frac = kept_fraction(engines[s_last % nrep], lambda: (resident_step(s_last), t_of(s_last))[1])
     alg = [algorithmic_bytes(es, w.B, w.H, w.Dh, t_of(args.warmup + i), kept_frac) for i in range(args.steps)]
 
-    # ---- leg 2: end to end through the Python class with host buffers ----
-    for s in range(min(3, args.warmup)):
-        e2e_step(s)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        e2e_step(args.warmup + i)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    # ---- leg 2: end to end with host buffers (upload, attention, gather, download, sync every step) ----
+    def timed_leg(step):
+        for s in range(min(3, args.warmup)):
+            step(s)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    e2e_ms = timed_leg(e2e_step)
+    eager_ms = timed_leg(eager_e2e_step) if host_steps is not None else e2e_ms   # same step, one API call per operation
     # ---- leg 3: the same step with no staging copies: the kernels read q/k/v from pinned host memory
     # and write the (gathered) result to pinned host memory in place ----
     in_place_ms = None
@@ -353,22 +487,19 @@ def main():
                 engines[s % nrep].attention(q, k, v, w.scale, t_of(s), w.p, out=out_h)
             torch.cuda.current_stream().synchronize()
 
-        for s in range(min(3, args.warmup)):
-            in_place_step(s)
-        barrier()
-        e0.record()
-        for i in range(args.steps):
-            in_place_step(args.warmup + i)
-        e1.record()
-        barrier()
-        in_place_ms = e0.elapsed_time(e1)
+        in_place_ms = timed_leg(in_place_step)
+    # ---- outside every timed region: is what the end-to-end step delivers the right tensor? ----
+    check = result_check(w, world, rank, engines[0], sharded[0] if world > 1 else None,
+                         host_steps[0] if host_steps is not None else None, qkv_h[args.warmup], w.prompt + 5, dev)
     status = max(e.device_status() for e in engines)
 
     # ---- max over ranks ----
-    times = torch.tensor([loop_ms, e2e_ms, sum(kernel_ms), in_place_ms or 0.0], dtype=torch.float64, device=dev)
+    times = torch.tensor([loop_ms, e2e_ms, sum(kernel_ms), in_place_ms or 0.0, eager_ms, check["max_err"],
+                          0.0 if check["ok"] else 1.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    loop_ms, e2e_ms, ksum_ms, in_place_ms = times.tolist()
+    loop_ms, e2e_ms, ksum_ms, in_place_ms, eager_ms, check_err, check_bad = times.tolist()
+    check["max_err"], check["ok"] = check_err, check_bad == 0.0
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -386,23 +517,35 @@ def main():
                              "avg_launch_ms": ksum_ms / args.steps,
                              "duration_from": "CUDA events around the timed steps" if use_region else
                              "CUDA events around a CUDA-graph replay of the same launches (launch shorter than host time per call)",
-                             "traffic": TRAFFIC_RATIO * per_launch_alg if (TRAFFIC_RATIO and w.p == 0) else None},
+                             "traffic": TRAFFIC_RATIO["exact" if w.p == 0 else "pruned"] * per_launch_alg},
                 "e2e": {"value": args.steps / (e2e_ms * 1e-3), "unit": "steps/s",
                         "h2d_bytes_per_step": 3 * w.B * w.H * w.Dh * es, "d2h_bytes_per_step": out_h.numel() * es,
                         "includes": "pinned-host q/k/v upload, attention, output all-gather (N>1), output download, sync",
+                        "api": "GraphedHostStep / ShardedFastForwardAttn.graphed_step: one upload + one CUDA-graph replay "
+                               "(attention, gather, download) + stream sync per step" if host_steps is not None else
+                               "FastForwardAttn.attention + gather + copies, one call each",
                         "gather": gather_kind,
+                        "one_call_per_operation": {"value": args.steps / (eager_ms * 1e-3), "unit": "steps/s",
+                                                   "what": "same step as five separate host-issued operations (no graph)"},
                         "in_place": None if not in_place_ms else {
                             "value": args.steps / (in_place_ms * 1e-3), "unit": "steps/s",
                             "what": "same step without staging copies: kernels read q/k/v from, and write the result to, "
                                     "pinned host memory over PCIe"}},
                 "gpu_launches": int(launches), "launch_shape": dict(shape), "device_status": status,
-                "clocks": clocks.summary(wall0, wall1), "replicas": nrep}
+                "clocks": clocks.summary(wall0, wall1), "replicas": nrep,
+                ("gather_check" if world > 1 else "result_check"): check}
         if world == 1 and not args.no_cpu_baseline:
             smp = CpuReferenceSample(full)
             probe = smp.step()
             n = max(3, min(50, int(15.0 / max(probe, 1e-3))))
             line["cpu_baseline"] = {"value": smp.run(n, 1), "unit": "steps/s", "cores": smp.cores, "kind": "port",
                                     "sample": smp.describe(n)}
+        if world == 1 and not args.no_configs:
+            # the other configurations of the benchmark definition, kernel time only (a few seconds together)
+            del host_steps, engines, sharded
+            torch.cuda.empty_cache()
+            line["configs"] = [measure_config(n, dev, peak) for n in EXTRA_CONFIGS]
+            line["configs"] += [measure_config(n, dev, peak, mode="round_like_torch") for n in ROUND_LIKE_TORCH_CONFIGS]
         print(json.dumps(line))
     if world > 1:
         for sh in sharded:

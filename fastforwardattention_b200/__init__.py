@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import importlib
 
-__all__ = ["FastForwardAttn", "ShardedFastForwardAttn", "GraphedStep", "GraphedLayers", "PagePool", "PagedFastForwardAttn", "launch_count"]
+__all__ = ["FastForwardAttn", "ShardedFastForwardAttn", "GraphedStep", "GraphedHostStep", "GraphedLayers", "PagePool", "PagedFastForwardAttn", "launch_count"]
 
 
 def _extension():
@@ -37,10 +37,10 @@ def __getattr__(name):
         from .graphed import GraphedLayers
 
         return GraphedLayers
-    if name == "GraphedStep":
-        from .graphed import GraphedStep
+    if name in ("GraphedStep", "GraphedHostStep"):
+        from . import graphed
 
-        return GraphedStep
+        return getattr(graphed, name)
     if name == "ShardedFastForwardAttn":
         from .sharded import ShardedFastForwardAttn
 

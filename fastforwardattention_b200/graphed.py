@@ -80,6 +80,83 @@ class GraphedStep:
         return self.out
 
 
+class GraphedHostStep:
+    """A host-driven decode step -- q, k, v arrive in pinned host memory, the result is wanted in
+    pinned host memory -- with two host-issued operations per token instead of five:
+
+        step = GraphedHostStep(ffa, softmax_scale, first_row=prompt_len)        # or sharded.graphed_step(...)
+        for token in range(n):
+            out_host = step(qkv_host)        # qkv_host: pinned [3, B, H, 1, Dh]
+            torch.cuda.current_stream().synchronize()    # out_host is valid from here until the next call
+
+    One asynchronous upload of q/k/v into a static device buffer, then one replay of a graph that
+    holds the attention launch (row index in device memory), the increment of the row index, the
+    all-gather of the outputs over peer memory when the heads are sharded (`gather` = the
+    ShardedFastForwardAttn, after enable_peer_gather()), and the download of the result into
+    `out_host` ([B, H, Dh], or [B, world*H, Dh] when gathered).  Graphs are recorded per bucket
+    of rows, like GraphedStep.
+    """
+
+    def __init__(self, ffa, softmax_scale: float, first_row: int, prob_thresh: float = 0.0, gather=None):
+        kc, _ = ffa.get_cache()
+        B, H, Lmax, Dh = kc.shape
+        if not 0 <= first_row < Lmax:
+            raise ValueError(f"first_row {first_row} outside [0, {Lmax})")
+        self.ffa, self.max_len, self.scale, self.p = ffa, Lmax, softmax_scale, prob_thresh
+        self.gather = gather if gather is not None and getattr(gather, "world", 1) > 1 else None
+        if self.gather is not None and not self.gather.peer_gather_enabled:
+            raise ValueError("a graphed gather needs the peer-memory all-gather: call enable_peer_gather() first")
+        dev, dt = kc.device, kc.dtype
+        world = self.gather.world if self.gather is not None else 1
+        self.stage = torch.zeros(3, B, H, 1, Dh, dtype=dt, device=dev)
+        self.local = torch.zeros(B, H, Dh, dtype=dt, device=dev)
+        self.full = torch.zeros(B, world * H, Dh, dtype=dt, device=dev) if world > 1 else self.local
+        self.out_host = torch.zeros(B, world * H, Dh, dtype=dt).pin_memory()
+        self.rows = torch.full((B,), first_row, dtype=torch.int32, device=dev)
+        self.next_row = first_row
+        self.graphs = {}
+        # lazy initialisation (kernel attributes, occupancy answers) outside any capture; writes zeros
+        # to row `first_row`, which the first real step overwrites.  No gather here: it is collective.
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            ffa.attention_per_sample(self.stage[0], self.stage[1], self.stage[2], softmax_scale, self.rows, prob_thresh,
+                                     out=self.local, max_row=row_bucket(first_row, Lmax))
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self._graph_for(first_row)
+
+    def _graph_for(self, row: int) -> torch.cuda.CUDAGraph:
+        bound = row_bucket(row, self.max_len)
+        graph = self.graphs.get(bound)
+        if graph is None:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.ffa.attention_per_sample(self.stage[0], self.stage[1], self.stage[2], self.scale, self.rows, self.p,
+                                              out=self.local, max_row=bound)
+                self.rows.add_(1)
+                if self.gather is not None:
+                    self.ffa.peer_gather(self.local, out=self.full)
+                self.out_host.copy_(self.full, non_blocking=True)
+            self.graphs[bound] = graph
+        return graph
+
+    def reset_row(self, row: int) -> None:
+        """The next step appends at `row` (a new generation over the same caches)."""
+        if not 0 <= row < self.max_len:
+            raise ValueError(f"row {row} outside [0, {self.max_len})")
+        self.rows.fill_(row)
+        self.next_row = row
+
+    def __call__(self, qkv_host: torch.Tensor) -> torch.Tensor:
+        if self.next_row >= self.max_len:
+            raise RuntimeError(f"the cache is full ({self.max_len} rows)")
+        graph = self._graph_for(self.next_row)
+        self.stage.copy_(qkv_host.view_as(self.stage), non_blocking=True)
+        graph.replay()
+        self.next_row += 1
+        return self.out_host
+
+
 class GraphedLayers:
     """Every layer's attention for one token -- and whatever the caller computes between the
     layers -- recorded in ONE CUDA graph.

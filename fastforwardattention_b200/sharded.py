@@ -104,6 +104,19 @@ class ShardedFastForwardAttn:
             eng.peer_gather_free()
         return False
 
+    @property
+    def peer_gather_enabled(self) -> bool:
+        return self._peer
+
+    def graphed_step(self, softmax_scale: float, first_row: int, prob_thresh: float = 0.0):
+        """A whole host-driven step of this rank -- upload of its q/k/v slice, attention, all-gather
+        over peer memory, download of the full [B, H, Dh] result -- as one upload plus one CUDA
+        graph replay (see GraphedHostStep).  Needs enable_peer_gather(); every rank must then call
+        the step the same number of times."""
+        from .graphed import GraphedHostStep
+
+        return GraphedHostStep(self.engine, softmax_scale, first_row, prob_thresh, gather=self)
+
     def close(self) -> None:
         """Collective: releases the peer-gather buffers.  Every rank finishes its queued work and
         meets at a barrier (no store can still be aimed at anyone's buffer), unmaps the peers'
