@@ -24,7 +24,8 @@ LIB = os.path.join(PKG, "libffa_b200.so")
 EXT = os.path.join(PKG, "ff_attention" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 CUDA_SOURCES = ["ffa_decode_kernels.cu", "ffa_c_api.cu", "ffa_no_alloc.cu", "ffa_peer_gather.cu"]
-KERNEL_HEADERS = ["ffa_internal.h", "ffa_device_common.cuh", "ffa_stream_kernel.cuh", "ffa_prune_kernels.cuh"]
+KERNEL_HEADERS = ["ffa_internal.h", "ffa_device_common.cuh", "ffa_stream_kernel.cuh", "ffa_prune_kernels.cuh",
+                  "ffa_prune_stream_kernel.cuh"]
 CUDA_DEPS = CUDA_SOURCES + KERNEL_HEADERS + [os.path.join(ROOT, "include", "ffa_c_api.h")]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <new>
 
 #include "../../include/ffa_c_api.h"
@@ -38,6 +39,7 @@ int elem_size(int dtype) { return dtype == FFA_DTYPE_F32 ? 4 : 2; }
 bool dtype_ok(int dtype) { return dtype == FFA_DTYPE_F32 || dtype == FFA_DTYPE_F16 || dtype == FFA_DTYPE_BF16; }
 bool head_dim_ok(int d) { return d == 64 || d == 80 || d == 128 || d == 256; }
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+int score_stride(int max_len) { return (max_len + 7) / 8 * 8; }   // score rows start on 32-byte boundaries
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kMaxCtasPerSm = 8;
@@ -48,12 +50,14 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 // bf16 x 128, batch 32 x 32 heads: 2 K tokens 154.9 vs 159.3 us, 1 K 81.8 vs 88.3 us, 512 45.6 vs
 // 48.9 us in favour of the aligned cut; 8 K tokens 603 vs 594 us against it)
 constexpr long long kAlignedBelowUnitsPerSlot = 200;
+// pruned steps that stream at least this many bytes of K take the streaming kernel (when the score scratch is bound)
+constexpr double kStreamPruneAboveBytes = 200e6;
 
 }  // namespace
 
 struct ffa_plan {
     int dtype, B, H, Dh, Lmax, use_default, device, mode;
-    int prune_path;  // 0 = choose, 1 = fused cluster kernel only, 2 = two kernels only
+    int prune_path;  // 0 = choose, 1 = fused cluster kernel only, 2 = streaming kernel only
     int cluster_merge;  // 1 = merge split pairs inside a thread-block cluster when the cut allows it
     // answers of the occupancy query for cluster launches, keyed by (threads, shared memory, cluster size)
     struct { int threads, smem, cluster, clusters; } occ[8];
@@ -67,7 +71,6 @@ struct ffa_plan {
     size_t ws_bytes;
     int* status;
     int* tickets;
-    float* stats;
     float* partials;
     float* scores;
     int max_grid;
@@ -79,7 +82,7 @@ struct ffa_plan {
 namespace {
 
 struct Carve {
-    size_t status, tickets, stats, partials, scores, total;
+    size_t status, tickets, partials, scores, total;
 };
 Carve carve(const ffa_plan* p, bool with_scores)
 {
@@ -87,11 +90,10 @@ Carve carve(const ffa_plan* p, bool with_scores)
     Carve c;
     size_t off = 0;
     c.status = off, off += 256;
-    c.tickets = off, off += align_up(2 * BH * sizeof(int), 256);
-    c.stats = off, off += align_up(2 * BH * sizeof(float), 256);
+    c.tickets = off, off += align_up(BH * sizeof(int), 256);
     c.partials = off, off += align_up(((size_t)p->max_grid + BH) * (p->Dh + 2) * sizeof(float), 256);
     c.scores = off;
-    if (with_scores) off += align_up(BH * (size_t)p->Lmax * sizeof(float), 256);
+    if (with_scores) off += align_up(BH * (size_t)score_stride(p->Lmax) * sizeof(float), 256);
     c.total = off;
     return c;
 }
@@ -115,10 +117,15 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
     Shape s;
     s.warps = 4;
     s.cps = 2;
-    s.stages = tensors == 2 ? 2 : 3;
+    s.stages = 2;
     s.tile_rows = 16384 / row_bytes;
     // head_dim 80 (160- and 320-byte rows): a batch of the row loop is 128 / 64 rows there
     if ((row_bytes / 16) % 5 == 0) s.tile_rows = 20480 / row_bytes;
+    if (tensors == 1) {
+        // the streaming pruning kernel: K tiles only carry half the bytes per row-loop iteration: twice the
+        // compute warps keep up with the ring, and twice the stages keep as many bytes in flight
+        s.warps = 8, s.stages = 4;
+    }
     return s;
 }
 
@@ -172,6 +179,7 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
     }
     if (s.warps < 1) s.warps = 1;
     if (s.warps > 8) s.warps = 8;   // the kernels are compiled for at most 1 + 8 warps
+    if (tensors == 1 && p->Dh == 80 && s.warps > 4) s.warps = 4;   // streaming pruning kernel, five vectors per lane: register budget
     if (s.cps < 1) s.cps = 1;
     if (s.cps > kMaxCtasPerSm) s.cps = kMaxCtasPerSm;
     if (s.stages < 2) s.stages = 2;
@@ -267,7 +275,7 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
 // and the grid is not persistent, so the time is (number of waves) x (one CTA's chain): C is
 // the candidate with the smallest  ceil(B*H*C / resident CTAs) x (chunk + fixed cost), the
 // fixed cost of a CTA (start, barriers, merge) taken as 512 rows' worth.  Slices stay >= 128
-// rows.  False when 8 slices do not fit in shared memory (then the two-kernel path runs).
+// rows.  False when 8 slices do not fit in shared memory (then the streaming kernel runs).
 bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out)
 {
     const int rowb = p->Dh * elem_size(p->dtype);
@@ -460,7 +468,7 @@ int ffa_plan_get_prune_launch(const ffa_plan_t* plan, int t, int* cluster, int* 
     std::memset(&P, 0, sizeof(P));
     int smem = 0;
     if (plan->prune_path == 2 || !plan_fused(plan, t, &P, &smem)) {
-        *cluster = 0, *chunk_rows = 0, *tile_rows = 0, *grid = 0, *smem_bytes = 0;   // two-kernel path
+        *cluster = 0, *chunk_rows = 0, *tile_rows = 0, *grid = 0, *smem_bytes = 0;   // streaming kernel
         return FFA_OK;
     }
     *cluster = P.cluster, *chunk_rows = P.chunk_rows, *tile_rows = P.tile_rows, *grid = P.grid, *smem_bytes = smem;
@@ -490,7 +498,7 @@ int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch)
 int ffa_plan_set_prune_path(ffa_plan_t* plan, int path)
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
-    if (path < 0 || path > 2) return fail(FFA_ERR_ARG, "prune path must be 0 (choose), 1 (fused) or 2 (two kernels)");
+    if (path < 0 || path > 2) return fail(FFA_ERR_ARG, "prune path must be 0 (choose), 1 (cluster kernel) or 2 (streaming kernel)");
     plan->prune_path = path;
     return FFA_OK;
 }
@@ -524,12 +532,11 @@ int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* st
     if (bytes < small.total) return fail(FFA_ERR_WORKSPACE, "workspace of %zu bytes, need at least %zu", bytes, small.total);
     char* base = static_cast<char*>(workspace);
     // status word + arrival counters start at zero; everything else is written before it is read
-    cudaError_t e = cudaMemsetAsync(base, 0, small.stats, static_cast<cudaStream_t>(stream));
+    cudaError_t e = cudaMemsetAsync(base, 0, small.partials, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "workspace clear");
     plan->ws = workspace, plan->ws_bytes = bytes;
     plan->status = reinterpret_cast<int*>(base + small.status);
     plan->tickets = reinterpret_cast<int*>(base + small.tickets);
-    plan->stats = reinterpret_cast<float*>(base + small.stats);
     plan->partials = reinterpret_cast<float*>(base + small.partials);
     plan->scores = bytes >= big.total ? reinterpret_cast<float*>(base + big.scores) : nullptr;
     return FFA_OK;
@@ -569,12 +576,18 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     P.scale = softmax_scale, P.p = p;
     P.round_like_torch = plan->mode == FFA_MODE_ROUND_LIKE_TORCH && !(p > 0.f);
     P.partials = plan->partials, P.tickets = plan->tickets, P.status = plan->status;
-    P.stats = plan->stats, P.scores = plan->scores;
+    P.scores = plan->scores, P.score_stride = score_stride(plan->Lmax);
     P.kept_mask = kept_mask, P.mask_words = (plan->Lmax + 31) / 32;
     P.page_table = pages.table, P.max_pages = pages.max_pages, P.page_rows = pages.page_rows;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-    if (twopass && plan->prune_path != 2) {
+    // p > 0 / torch rounding.  Small steps: the cluster kernel (scores stay in shared memory, nothing but the
+    // launch is fixed cost).  Large steps: the streaming kernel (a persistent grid keeps HBM busy; the cluster
+    // kernel pays its start, two cluster barriers and the merge once per CTA).  The streaming kernel needs
+    // the score scratch; without it the cluster kernel runs whenever it fits.
+    const double k_bytes = (double)BH * cap * plan->Dh * elem_size(plan->dtype);
+    const bool stream_first = plan->prune_path == 2 || (plan->prune_path == 0 && plan->scores != nullptr && k_bytes >= kStreamPruneAboveBytes);
+    if (twopass && !stream_first) {
         FfaStepParams F = P;
         int smem_f = 0;
         if (plan_fused(plan, cap, &F, &smem_f)) {
@@ -586,7 +599,7 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
         if (plan->prune_path == 1) return fail(FFA_ERR_ARG, "the fused pruning kernel does not fit this shape in shared memory");
     }
     if (twopass && plan->scores == nullptr)
-        return fail(FFA_ERR_WORKSPACE, "this shape needs the two-kernel pruning path: bind a workspace sized with with_scores = 1");
+        return fail(FFA_ERR_WORKSPACE, "this shape needs the streaming pruning kernel: bind a workspace sized with with_scores = 1");
 
     ffa_launch_t L;
     // the streaming kernel never lets a tile straddle a page: tiles are powers of two that divide it
@@ -596,7 +609,6 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
     P.units_per_bh = cap / L.tile_rows + 1;
     P.parts_per_bh = L.parts_per_bh;
-    int threads = 32 * (L.consumer_warps + 1);
     if (!twopass) {
         // the C CTAs of a pair merge inside a thread-block cluster when every CTA owns exactly one part
         // (pairs with more than 8 parts: whole clusters of 8, the cluster leaders merge through global memory)
@@ -605,28 +617,16 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
         P.tile_rows = L.tile_rows, P.stages = L.stages, P.grid = L.grid;
         P.units_per_bh = cap / L.tile_rows + 1;
         P.parts_per_bh = L.parts_per_bh;
-        threads = 32 * (L.consumer_warps + 1);
+        const int threads = 32 * (L.consumer_warps + 1);
         r = ffa_k_decode_onepass(plan->dtype, plan->Dh, P, threads, L.smem_bytes, st);
         if (r != 0) return cuda_fail(r, "attention launch");
         g_launches.fetch_add(1);
         return FFA_OK;
     }
-    // value pass: units of 512 rows (only 4-byte scores are read densely), no copy ring
-    FfaStepParams V = P;
-    V.tile_rows = 512;
-    V.stages = 0;
-    V.units_per_bh = cap / V.tile_rows + 1;
-    V.parts_per_bh = V.units_per_bh;
-    const long long v_units = BH * V.units_per_bh;
-    long long vgrid = (long long)plan->sms * 4;
-    if (vgrid > v_units) vgrid = v_units;
-    if (vgrid > plan->max_grid) vgrid = plan->max_grid;
-    V.grid = (int)vgrid;
-    V.tickets = plan->tickets + BH;
-    const int smem_v = ffa_k_gather_smem_bytes(plan->dtype, plan->Dh, V.tile_rows);
-    r = ffa_k_decode_twopass(plan->dtype, plan->Dh, P, V, threads, L.smem_bytes, smem_v, st);
-    if (r != 0) return cuda_fail(r, "two-pass attention launch");
-    g_launches.fetch_add(2);
+    { const char* dbg = getenv("FFA_DEBUG"); P.chunk_rows = dbg ? atoi(dbg) : 0; }
+    r = ffa_k_decode_prune_stream(plan->dtype, plan->Dh, P, L.consumer_warps, L.smem_bytes, st);
+    if (r != 0) return cuda_fail(r, "streaming pruning launch");
+    g_launches.fetch_add(1);
     return FFA_OK;
 }
 

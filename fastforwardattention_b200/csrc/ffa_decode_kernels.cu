@@ -8,15 +8,16 @@
 // runs, one per CTA of a persistent grid, so all SMs stream from HBM whatever the batch*head
 // count and the sequence length is bounded by memory only.
 //
-//   ffa_stream_kernel<T, DH, PASS_ONE>    p == 0: K and V tiles through a bulk-copy ring,
+//   ffa_stream_kernel<T, DH>              p == 0: K and V tiles through a bulk-copy ring,
 //                                         online softmax, cross-CTA merge by the CTA that
 //                                         arrives last (no waiting), k/v append fused
-//   ffa_stream_kernel<T, DH, PASS_SCORE>  first half of the two-pass modes: K tiles only,
-//                                         fp32 scores to scratch, global max and sum
-//   ffa_value_gather_kernel<T, DH>        second half: tests every cached row with the
+//   ffa_prune_stream_kernel<T, DH>        p > 0 at any size, one persistent launch: K tiles
+//                                         through the ring, fp32 scores to scratch, global max
+//                                         and sum; gather warps test every cached row with the
 //                                         reference's pruning rule (attention.cu:1184-1191,
-//                                         461-469) and loads only the V rows that survive
-//   ffa_prune_cluster_kernel<T, DH>       both halves in one launch: a thread-block cluster per
+//                                         461-469) and load only the V rows that survive, while
+//                                         the next pairs' K rows keep streaming
+//   ffa_prune_cluster_kernel<T, DH>       p > 0 at small sizes: a thread-block cluster per
 //                                         (batch, head), scores in shared memory, statistics
 //                                         and partial outputs over distributed shared memory
 //   ffa_cache_init_kernel                 prompt K/V -> rows [0, prompt) of the caches
@@ -34,6 +35,7 @@
 #include "ffa_internal.h"
 #include "ffa_device_common.cuh"
 #include "ffa_prune_kernels.cuh"
+#include "ffa_prune_stream_kernel.cuh"
 #include "ffa_stream_kernel.cuh"
 
 using namespace ffa_dev;
@@ -123,16 +125,17 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
     const int rowb = head_dim * elem_size(dtype);
     const int lpr = lanes_per_row(rowb);
     const int ng = consumer_warps * 32 / lpr;
+    if (tensors_per_stage == 1) {
+        // the streaming pruning kernel: K ring, scorer groups' (max, sum), survivor lists, gather partials,
+        // job slots, barriers, flags
+        return stages * tile_rows * rowb + kPsGatherWarps * kPsStageBytes + ng * 4 * 8 + kPsGatherWarps * kPsListCap * 8 + kPsJobs * kPsGatherWarps * head_dim * 4 +
+               (int)sizeof(PsJob) * (kPsJobs + (kPsJobs & 1)) + (2 * stages + 3 * kPsJobs) * 8 + 16;
+    }
     // ring, group reduction area, barriers, flags, the CTA's partial for the cluster merge
     return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16 + (head_dim + 4) * 4;
 }
 
-int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows)
-{
-    const int rowb = head_dim * elem_size(dtype);
-    const int lpr = lanes_per_row(rowb);
-    return tile_rows * 8 + (kGatherThreads / lpr) * head_dim * 4;
-}
+int ffa_k_prune_stream_threads(int scorer_warps) { return 32 * (1 + scorer_warps + kPsGatherWarps); }
 
 int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows)
 {
@@ -155,11 +158,9 @@ int ffa_k_prepare(int dtype, int head_dim, int max_smem_bytes)
             if (err != cudaSuccess) return err;
             return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_bytes - (int)a.sharedSizeBytes);
         };
-        cudaError_t e = raise_limit(reinterpret_cast<const void*>(ffa_stream_kernel<T, DH, kPassOne>));
+        cudaError_t e = raise_limit(reinterpret_cast<const void*>(ffa_stream_kernel<T, DH>));
         if (e != cudaSuccess) return (int)e;
-        e = raise_limit(reinterpret_cast<const void*>(ffa_stream_kernel<T, DH, kPassScore>));
-        if (e != cudaSuccess) return (int)e;
-        e = raise_limit(reinterpret_cast<const void*>(ffa_value_gather_kernel<T, DH>));
+        e = raise_limit(reinterpret_cast<const void*>(ffa_prune_stream_kernel<T, DH>));
         if (e != cudaSuccess) return (int)e;
         e = raise_limit(reinterpret_cast<const void*>(ffa_prune_cluster_kernel<T, DH>));
         return (int)e;
@@ -203,14 +204,14 @@ int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int th
             attr.id = cudaLaunchAttributeClusterDimension;
             attr.val.clusterDim.x = (unsigned)P.cluster, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
             cfg.attrs = &attr, cfg.numAttrs = 1;
-            if (cudaLaunchKernelEx(&cfg, ffa_stream_kernel<T, DH, kPassOne>, P) == cudaSuccess) return 0;
+            if (cudaLaunchKernelEx(&cfg, ffa_stream_kernel<T, DH>, P) == cudaSuccess) return 0;
             // a cluster shape this device cannot co-schedule: the same cut runs without clusters,
             // the parts merging through global memory
             (void)cudaGetLastError();
         }
         FfaStepParams Q = P;
         Q.cluster = 0;
-        ffa_stream_kernel<T, DH, kPassOne><<<Q.grid, threads, smem, stream>>>(Q);
+        ffa_stream_kernel<T, DH><<<Q.grid, threads, smem, stream>>>(Q);
         return (int)cudaGetLastError();
     });
 }
@@ -229,7 +230,7 @@ int ffa_k_max_active_clusters(int dtype, int head_dim, int threads, int smem, in
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = (unsigned)cluster, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
         cfg.attrs = &attr, cfg.numAttrs = 1;
-        return (int)cudaOccupancyMaxActiveClusters(clusters, ffa_stream_kernel<T, DH, kPassOne>, &cfg);
+        return (int)cudaOccupancyMaxActiveClusters(clusters, ffa_stream_kernel<T, DH>, &cfg);
     });
 }
 
@@ -255,16 +256,13 @@ int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, in
     });
 }
 
-int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const FfaStepParams& Pv, int threads,
-                         int smem_k, int smem_v, cudaStream_t stream)
+int ffa_k_decode_prune_stream(int dtype, int head_dim, const FfaStepParams& P, int scorer_warps, int smem, cudaStream_t stream)
 {
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
-        ffa_stream_kernel<T, DH, kPassScore><<<Pk.grid, threads, smem_k, stream>>>(Pk);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return (int)e;
-        ffa_value_gather_kernel<T, DH><<<Pv.grid, kGatherThreads, smem_v, stream>>>(Pv);
+        if (scorer_warps < 1 || scorer_warps > ps_max_scorer_warps(DH)) return (int)cudaErrorInvalidConfiguration;
+        ffa_prune_stream_kernel<T, DH><<<P.grid, ffa_k_prune_stream_threads(scorer_warps), smem, stream>>>(P);
         return (int)cudaGetLastError();
     });
 }

@@ -15,14 +15,11 @@
 namespace ffa_dev {
 
 
-constexpr int kPassOne = 0;
-constexpr int kPassScore = 1;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bounded barrier wait: 2 s, then give up
 constexpr uint32_t kDrainPolls = 1u << 20;
 constexpr int kMaxClusterCtas = 8;   // portable thread-block cluster size
 constexpr int kStatusWaitTimeout = 1;
 constexpr int kStatusBadLength = 2;
-constexpr int kGatherThreads = 256;
 
 // ------------------------------------------------------------------------------------------
 // PTX wrappers: mbarrier + 1-D bulk copy global -> this CTA's shared memory
@@ -95,6 +92,16 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// 16 bytes global -> this thread's slot in shared memory, asynchronously (bypassing L1); the issuing thread
+// may read the slot after cp_async_wait_all()
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all()
+{
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -145,6 +152,7 @@ struct Elem<float> {
         f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
     }
     static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ float to_float(float x) { return x; }
     static __device__ __forceinline__ void store(float* p, float x) { *p = x; }
     // attention.cu:461-464
     static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
@@ -168,6 +176,7 @@ struct Elem<__half> {
         for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
     }
     static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
     static __device__ __forceinline__ void store(__half* p, float x) { *p = __float2half_rn(x); }
     // attention.cu:466-469 hands two raw bit patterns to __hle; the unsigned short -> __half
     // conversion there is the NUMERIC one, so the patterns themselves are rounded to 11
@@ -198,6 +207,7 @@ struct Elem<__nv_bfloat16> {
         for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
     }
     static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
     static __device__ __forceinline__ void store(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
     // the reference has no bf16; plain value comparison
     static __device__ __forceinline__ bool leq(float a, float b) { return a <= b; }
@@ -300,6 +310,39 @@ __device__ __forceinline__ void load_row_f32(const unsigned char* row, int li, f
             for (int e = 0; e < G::EPV; ++e) f[x][e] = 0.f;
         }
     }
+}
+
+// Sums RB per-lane partials over the LPR lanes of a group and leaves ONE of the RB totals in every lane:
+// the first log2(RB) butterfly levels exchange halves of the value set instead of adding everything
+// everywhere (5 shuffles for 4 values over 16 lanes, where four full butterflies take 16).  Lane `li`
+// of the group ends up with the total of value transposed_row<LPR, RB>(li), replicated over LPR / RB lanes.
+template <int LPR, int RB>
+__device__ __forceinline__ int transposed_row(int li)
+{
+    static_assert((RB == 4 && LPR >= 4) || (RB == 2 && LPR >= 2), "RB values over at least RB lanes");
+    if constexpr (RB == 4) return ((li / (LPR / 2)) & 1) * 2 + ((li / (LPR / 4)) & 1);
+    else return (li / (LPR / 2)) & 1;
+}
+template <int LPR, int RB>
+__device__ __forceinline__ float transposed_group_sum(const float (&v)[RB], int li)
+{
+    float c;
+    if constexpr (RB == 4) {
+        const bool hi = (li / (LPR / 2)) & 1;            // keeps values {2, 3}, hands {0, 1} to its partner
+        float a = hi ? v[2] : v[0], b = hi ? v[3] : v[1];
+        a += __shfl_xor_sync(0xffffffffu, hi ? v[0] : v[2], LPR / 2);
+        b += __shfl_xor_sync(0xffffffffu, hi ? v[1] : v[3], LPR / 2);
+        const bool odd = (li / (LPR / 4)) & 1;           // keeps the odd one of its pair
+        c = (odd ? b : a) + __shfl_xor_sync(0xffffffffu, odd ? a : b, LPR / 4);
+#pragma unroll
+        for (int off = LPR / 8; off >= 1; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
+    } else {
+        const bool hi = (li / (LPR / 2)) & 1;
+        c = (hi ? v[1] : v[0]) + __shfl_xor_sync(0xffffffffu, hi ? v[0] : v[1], LPR / 2);
+#pragma unroll
+        for (int off = LPR / 4; off >= 1; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
+    }
+    return c;
 }
 
 template <int LPR>

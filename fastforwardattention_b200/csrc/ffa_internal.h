@@ -22,10 +22,10 @@ struct FfaStepParams {
     int round_like_torch;
     // scratch
     float* partials;   // [(grid + B*H)] x (Dh + 2): weighted sum, running max, running sum
-    int* tickets;      // [2 * B*H] arrival counters, zero between launches
+    int* tickets;      // [B*H] arrival counters, zero between launches
     int* status;       // device status word
-    float* stats;      // [B*H] x 2: global max, 1/sum (two-pass modes)
-    float* scores;     // [B*H, Lmax] fp32 scores (two-pass modes)
+    float* scores;     // [B*H, score_stride] fp32 scores (streaming pruning kernel); rows start 32-byte aligned
+    int score_stride;  // Lmax rounded up to a multiple of 8
     uint32_t* kept_mask;  // [B*H, mask_words] or null
     int mask_words;
     // thread-block cluster size: CTAs per (batch, head) (fused pruning kernel; streaming kernel when
@@ -59,13 +59,13 @@ int ffa_k_cache_init(int dtype, int BH, int prompt_len, int src_len, int max_len
 int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int threads, int smem, cudaStream_t stream);
 // how many clusters of `cluster` CTAs of the one-pass kernel the device keeps resident at once
 int ffa_k_max_active_clusters(int dtype, int head_dim, int threads, int smem, int cluster, int* clusters);
-// p > 0 or round-like-torch: score pass then value pass, two launches.
-int ffa_k_decode_twopass(int dtype, int head_dim, const FfaStepParams& Pk, const FfaStepParams& Pv, int threads,
-                         int smem_k, int smem_v, cudaStream_t stream);
-// shared-memory bytes a launch shape needs
+// p > 0 or round-like-torch at any size: the streaming pruning kernel (scores through the scratch), one launch.
+int ffa_k_decode_prune_stream(int dtype, int head_dim, const FfaStepParams& P, int scorer_warps, int smem, cudaStream_t stream);
+int ffa_k_prune_stream_threads(int scorer_warps);
+// shared-memory bytes a launch shape needs (tensors_per_stage 2: the exact kernel, K and V tiles; 1: the
+// streaming pruning kernel, K tiles only)
 int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage);
-int ffa_k_gather_smem_bytes(int dtype, int head_dim, int tile_rows);
-// p > 0 or round-like-torch when a slice's scores fit in shared memory: one cluster launch.
+// p > 0 or round-like-torch, small steps whose slices' scores fit in shared memory: one cluster launch.
 int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, int smem, cudaStream_t stream);
 int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows);
 // diagnostic: a bounded wait that must time out (see ffa_selftest_wait_timeout)

@@ -1,195 +1,8 @@
-// Pruning (and torch-rounding) kernels: the value pass of the two-launch path and the fused cluster kernel.
+// Pruning (and torch-rounding) at small sizes: the fused cluster kernel.
 #pragma once
 #include "ffa_device_common.cuh"
 
 namespace ffa_dev {
-
-// ------------------------------------------------------------------------------------------
-// Value pass of the two-pass modes: prune test on every cached row, gather the survivors
-// ------------------------------------------------------------------------------------------
-// Shared memory: kept-row list (index + probability) for one unit of tile_rows rows, then the
-// group reduction area [NG][DH].  All 8 warps compute; rows that survive are fetched with
-// 16-byte global loads, four rows in flight per lane group.
-template <typename T, int DH>
-__global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const FfaStepParams P)
-{
-    using G = RowGeom<T, DH>;
-    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
-    constexpr int NT = kGatherThreads, NG = NT / LPR;
-
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int R = P.tile_rows;  // multiple of 32
-    int* list_idx = reinterpret_cast<int*>(smem);
-    float* list_p = reinterpret_cast<float*>(list_idx + R);
-    float* red = list_p + R;  // [NG][DH]
-    __shared__ int s_n, s_last;
-    __shared__ unsigned s_words[16];   // one ballot per 32 rows of a 512-row unit
-
-    const int upb = P.units_per_bh;
-    const Partition cut = make_partition(P);
-    const long long u0 = cut.first_unit(blockIdx.x), u1 = cut.first_unit(blockIdx.x + 1);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = tid / LPR, li = tid % LPR;
-    const bool prune = P.p > 0.f;
-    const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
-
-    long long u = u0;
-    while (u < u1) {
-        const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
-        const int j1 = (int)min((long long)upb, j0 + (u1 - u));
-        const SampleRange sr = sample_range(P, bh / P.H);
-        const int jt = sr.row / R;
-        const float M = P.stats[2 * bh], Lsum = P.stats[2 * bh + 1];
-        // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125,
-        // 1185); the torch-rounding mode divides exactly like torch's softmax does
-        const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
-        const float theta = Elem<T>::round(P.p * inv);
-        const float* sc = P.scores + (size_t)bh * P.Lmax;
-        auto prob_of = [&](float s) -> float {
-            if (prune) return Elem<T>::round(__expf(s - M) * inv);
-            return Elem<T>::round(expf(s - M) / Lsum);
-        };
-
-        float acc[VPL][EPV];
-#pragma unroll
-        for (int x = 0; x < VPL; ++x)
-#pragma unroll
-            for (int e = 0; e < EPV; ++e) acc[x][e] = 0.f;
-
-        for (int j = j0; j < j1 && sr.ok; ++j) {
-            const int lo = j * R, hi = min((j + 1) * R, sr.row + 1);  // includes the new token's bit
-            if (hi <= lo) break;
-            // survivors are listed in row order: ballots first, then a prefix over the words
-            __syncthreads();
-            float my_p[2];
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const int base = lo + (warp + 8 * k) * 32;
-                my_p[k] = -1.f;
-                if (base >= hi) continue;   // warp-uniform
-                const int i = base + lane;
-                const bool cached = i < sr.row && i >= sr.first;
-                float pr = 0.f;
-                bool keep = false;
-                if (cached) {
-                    pr = prob_of(sc[i]);
-                    keep = prune ? !Elem<T>::leq(pr, theta) : true;
-                }
-                const unsigned bal = __ballot_sync(0xffffffffu, keep);
-                if (P.kept_mask != nullptr && lane == 0)
-                    P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
-                        bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
-                if (lane == 0) s_words[warp + 8 * k] = bal;
-                if (keep) my_p[k] = pr;
-            }
-            __syncthreads();
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                if (my_p[k] >= 0.f) {
-                    const int w = warp + 8 * k;
-                    int pos = __popc(s_words[w] & ((1u << lane) - 1u));
-                    for (int ww = 0; ww < w; ++ww) pos += __popc(s_words[ww]);
-                    list_idx[pos] = lo + w * 32 + lane, list_p[pos] = my_p[k];
-                }
-            }
-            if (tid == 0) {
-                int tot = 0;
-                for (int w = 0; w < ((hi - lo + 31) >> 5); ++w) tot += __popc(s_words[w]);
-                s_n = tot;
-            }
-            __syncthreads();
-            const int n = s_n;
-            for (int base = 0; base < n; base += RB * NG) {
-                uint4 raw[RB][VPL];
-                float pr[RB];
-#pragma unroll
-                for (int uu = 0; uu < RB; ++uu) {
-                    const int idx = base + uu * NG + g;
-                    const bool okr = idx < n;
-                    pr[uu] = okr ? list_p[idx] : 0.f;
-                    const size_t roff = okr ? cache_row_offset(P, bh, list_idx[idx], ROWB) : 0;
-#pragma unroll
-                    for (int x = 0; x < VPL; ++x) {
-                        const int vec = li + x * LPR;
-                        raw[uu][x] = make_uint4(0, 0, 0, 0);
-                        if (okr && vec < VPR)
-                            raw[uu][x] = __ldg(reinterpret_cast<const uint4*>(vc + roff + vec * 16));
-                    }
-                }
-#pragma unroll
-                for (int uu = 0; uu < RB; ++uu)
-#pragma unroll
-                    for (int x = 0; x < VPL; ++x) {
-                        float vf[EPV];
-                        Elem<T>::unpack(raw[uu][x], vf);
-#pragma unroll
-                        for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pr[uu], vf[e], acc[x][e]);
-                    }
-            }
-        }
-
-        // the new token is never pruned (attention.cu:1227-1256): append v, add P_t * v
-        if (sr.ok && j0 <= jt && jt < j1 && g == 0) {
-            const float pt = prob_of(sc[sr.row]);
-            const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
-#pragma unroll
-            for (int x = 0; x < VPL; ++x) {
-                const int vec = li + x * LPR;
-                if (vec < VPR) {
-                    const uint4 vraw = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + (size_t)bh * ROWB + vec * 16);
-                    *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vraw;
-                    float vf[EPV];
-                    Elem<T>::unpack(vraw, vf);
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) acc[x][e] = fmaf(pt, vf[e], acc[x][e]);
-                }
-            }
-        }
-
-        // ---- sum the groups, then the CTAs ----
-        __syncthreads();
-#pragma unroll
-        for (int x = 0; x < VPL; ++x) {
-            const int vec = li + x * LPR;
-            if (vec < VPR) {
-#pragma unroll
-                for (int e = 0; e < EPV; e += 4)
-                    *reinterpret_cast<float4*>(red + g * DH + vec * EPV + e) =
-                        make_float4(acc[x][e], acc[x][e + 1], acc[x][e + 2], acc[x][e + 3]);
-            }
-        }
-        __syncthreads();
-        const bool whole = (j0 == 0 && j1 == upb);
-        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
-        float* part = P.partials + (size_t)(blockIdx.x + bh) * (DH + 2);
-        for (int d = tid; d < DH; d += NT) {
-            float A = 0.f;
-            for (int gg = 0; gg < NG; ++gg) A += red[gg * DH + d];
-            if (whole) Elem<T>::store(outp + d, A);
-            else part[d] = A;
-        }
-        if (!whole) {
-            __threadfence();
-            __syncthreads();
-            const int c_first = cut.first_cta_of(bh), c_last = cut.last_cta_of(bh);
-            const int count = c_last - c_first + 1;
-            if (tid == 0) s_last = (atomicAdd(P.tickets + bh, 1) == count - 1);
-            __syncthreads();
-            if (s_last) {
-                __threadfence();
-                const float* pbase = P.partials + (size_t)(c_first + bh) * (DH + 2);
-                for (int d = tid; d < DH; d += NT) {
-                    float A = 0.f;
-                    for (int k = 0; k < count; ++k) A += __ldcg(pbase + (size_t)k * (DH + 2) + d);
-                    Elem<T>::store(outp + d, A);
-                }
-                if (tid == 0) P.tickets[bh] = 0;
-            }
-        }
-        if (!sr.ok && tid == 0) atomicOr(P.status, kStatusBadLength);
-        u += j1 - j0;
-    }
-}
 
 // ------------------------------------------------------------------------------------------
 // Fused pruning step: one thread-block cluster per (batch, head), scores never leave the SMs
@@ -201,8 +14,8 @@ __global__ void __launch_bounds__(kGatherThreads) ffa_value_gather_kernel(const 
 // the C pairs (max, sum) are exchanged through distributed shared memory behind a cluster
 // barrier, every CTA prunes and gathers the V rows of its slice, and CTA 0 adds the C partial
 // outputs (again through distributed shared memory).  No score scratch in HBM, no second
-// launch, no arrival counters.  Used when a slice's scores fit in shared memory; the two
-// kernels above remain for everything else.
+// launch, no arrival counters.  Used for small steps whose slices' scores fit in shared memory; the
+// streaming pruning kernel takes everything else.
 //
 // Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (index, probability)
 // | ballot words | group reduction area [NG][DH + 4] | partial output [DH] | (max, sum) | barriers | flags.

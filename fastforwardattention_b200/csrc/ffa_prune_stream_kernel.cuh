@@ -1,0 +1,488 @@
+// The streaming pruning kernel: one persistent launch for p > 0 (and the torch-rounding mode) at any size.
+#pragma once
+#include "ffa_device_common.cuh"
+
+namespace ffa_dev {
+
+// The pruning rule needs the global max and sum of a (batch, head) before any V row may be
+// touched (attention.cu:1184-1191): every K row is read, then only the surviving V rows.  The
+// reference does both in one CTA per (batch, head) with all scores in shared memory, which caps
+// its sequence length; here the K rows of ALL pairs stream through one persistent grid exactly
+// like the exact kernel's K and V rows do, and the V rows of a pair are gathered while the K
+// rows of the next pairs keep streaming.  A CTA has three roles:
+//
+//   warp 0              issues the K tiles (1-D bulk copies into a ring of `stages` buffers,
+//                       full / empty mbarriers) for this CTA's run of the flat unit list;
+//   scorer warps        (4 or 8) consume the tiles: fp32 score of every row to the score scratch
+//                       in global memory (4 bytes per row; read back from L2), running (max, sum)
+//                       per lane group, the new token's score and its K append.  A pair cut over
+//                       several CTAs is combined by whoever arrives last (partials + ticket, no
+//                       waiting).  The CTA that completes a pair's (max, sum) posts a JOB;
+//   gather warps        (4) take jobs: re-read the pair's scores, apply the reference rule
+//                       (P = cvt_T(e * inv), Theta = cvt_T(p * inv), skip iff leq(P, Theta)),
+//                       write the optional kept mask, list the survivors per warp in row order,
+//                       fetch only those V rows (16-byte cp.async into a staging area, 8 KB in flight per warp),
+//                       append the new token's v, and store the output row.
+//
+// Scoring never waits for gathering unless two jobs are already queued, so HBM sees one
+// continuous K stream with the V reads of earlier pairs mixed in.  The floating-point sums
+// follow a fixed order (row -> gather warp and lane group by position, groups and warps added
+// in index order), so results do not depend on timing.  Every wait is time-bounded.
+//
+// Shared memory: [stages][K tile] ring | per gather warp: V-row staging [kPsStageBytes] | scorer groups'
+// (max, sum) [NG * RB][2] | per gather warp: survivor list (row, probability) [kPsListCap] | gather partial
+// outputs [jobs][warps][DH] | job slots | barriers: full[S], empty[S], job_full[J], job_empty[J],
+// gather_done[J] | flags.
+constexpr int kPsGatherWarps = 4;
+constexpr int kPsListCap = 256;   // rows a gather warp tests per round: 8 words of 32 rows
+constexpr int kPsWordsPerRound = kPsListCap / 32;
+constexpr int kPsStageBytes = 8192;   // per gather warp: surviving V rows land here (cp.async), up to 32 rows in flight
+constexpr int kPsJobs = 2;        // queued (batch, head) pairs between scorers and gatherers
+
+struct PsJob {
+    int bh;       // pair to gather; -1: no more jobs
+    float M, L;   // max and sum(exp) over the pair's rows, new token included
+};
+
+// head_dim 80 keeps five vectors per lane in flight: at most 4 scorer warps there, for the register budget of
+// two resident CTAs
+constexpr int ps_max_scorer_warps(int dh) { return dh == 80 ? 4 : 8; }
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherWarps), 2) ffa_prune_stream_kernel(const FfaStepParams P)
+{
+    using G = RowGeom<T, DH>;
+    constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
+    constexpr int E2 = EPV / 2;
+    constexpr bool kAllLanes = (VPR == LPR * VPL);
+    constexpr int NGW = kPsGatherWarps, GPW = 32 / LPR;     // gather warps; lane groups (rows in flight per step) per warp
+    constexpr int STEPS = VPL >= 4 ? 2 : 16 / VPL;          // V rows a lane group keeps in flight per batch
+    constexpr int SROWS = STEPS * GPW;                      // rows per batch and gather warp
+    static_assert(SROWS * ROWB <= kPsStageBytes, "a batch of V rows fits the warp's staging area");
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int R = P.tile_rows, S = P.stages;
+    const int nsw = (blockDim.x >> 5) - 1 - NGW;   // scorer warps
+    const int nct = nsw * 32, NG = nct / LPR;      // scorer threads, scorer lane groups
+    const uint32_t tile_bytes = (uint32_t)R * ROWB;
+    unsigned char* gstage = smem + (size_t)S * tile_bytes;                           // [NGW][kPsStageBytes]
+    float* red = reinterpret_cast<float*>(gstage + NGW * kPsStageBytes);             // [NG * RB][2]
+    int* list_idx = reinterpret_cast<int*>(red + 2 * NG * RB);                            // [NGW][kPsListCap]
+    float* list_p = reinterpret_cast<float*>(list_idx + NGW * kPsListCap);           // [NGW][kPsListCap]
+    float* gred = list_p + NGW * kPsListCap;                                         // [kPsJobs][NGW][DH]
+    PsJob* jobs = reinterpret_cast<PsJob*>(gred + kPsJobs * NGW * DH);               // [kPsJobs]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(jobs + kPsJobs + (kPsJobs & 1));    // 8-byte aligned: sizeof(PsJob) = 12
+    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S + 3 * kPsJobs);  // [0] dead, [1] last-arriver
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
+    const uint32_t bar_jfull = smem_u32(bars + 2 * S), bar_jempty = bar_jfull + 8 * kPsJobs, bar_gdone = bar_jempty + 8 * kPsJobs;
+    const uint32_t ring = smem_u32(smem);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, nsw);
+        }
+        for (int j = 0; j < kPsJobs; ++j) {
+            mbar_init(bar_jfull + 8 * j, 1);
+            mbar_init(bar_jempty + 8 * j, 1);
+            mbar_init(bar_gdone + 8 * j, NGW);
+        }
+        flags[0] = 0, flags[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int upb = P.units_per_bh;
+    const Partition cut = make_partition(P);
+    const long long u0 = cut.first_unit(blockIdx.x), u1 = cut.first_unit(blockIdx.x + 1);
+    const bool prune = P.p > 0.f;
+
+    if (warp == 0) {
+        // ---------------- producer: K tiles of this CTA's run ----------------
+        if (tid == 0) {
+            const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache);
+            uint32_t issued = 0, stage = 0, use = 0;
+            int cur_b = -1;
+            SampleRange sr{0, 0, false};
+            int bh = (int)(u0 / upb), j = (int)(u0 - (long long)bh * upb);
+            for (long long u = u0; u < u1; ++u, ++j) {
+                if (j == upb) j = 0, ++bh;
+                const int b = bh / P.H;
+                if (b != cur_b) sr = sample_range(P, b), cur_b = b;
+                if (!sr.ok) continue;
+                const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
+                if (hi <= lo) continue;
+                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
+                const uint32_t bytes = (uint32_t)(hi - lo) * ROWB;
+                mbar_expect_tx(bar_full + 8 * stage, bytes);
+                bulk_copy_g2s(ring + stage * tile_bytes, kc + cache_row_offset(P, bh, lo, ROWB), bytes, bar_full + 8 * stage);
+                ++issued;
+                if (++stage == (uint32_t)S) stage = 0, ++use;
+            }
+            if (flags[0]) {   // gave up: let the copies already issued land before the CTA releases its shared memory
+                const uint32_t pending = issued < (uint32_t)S ? issued : (uint32_t)S;
+                for (uint32_t k = 0; k < pending; ++k) {
+                    const uint32_t id = issued - 1 - k, st = id % S, us = id / S;
+                    for (uint32_t n = 0; n < kDrainPolls && !mbar_try_wait(bar_full + 8 * st, us & 1); ++n) __nanosleep(256);
+                }
+            }
+        }
+    } else if (warp <= nsw) {
+        // ---------------- scorers ----------------
+        const int ctid = tid - 32;
+        const int g = ctid / LPR, li = ctid % LPR;
+        const int myrow = transposed_row<LPR, RB>(li);                  // which of a batch's RB rows this lane ends up holding
+        const bool store_lane = (li % (LPR / RB)) == 0;                 // one lane per (group, row) writes the score
+        uint32_t stage = 0, phase = 0, jslot = 0, juse = 0;
+        const unsigned char* qbase = static_cast<const unsigned char*>(P.q);
+        uint4 qraw[VPL];
+#pragma unroll
+        for (int x = 0; x < VPL; ++x) {
+            qraw[x] = make_uint4(0, 0, 0, 0);
+            if (u0 < u1 && li + x * LPR < VPR)
+                qraw[x] = *reinterpret_cast<const uint4*>(qbase + (size_t)(u0 / upb) * ROWB + (li + x * LPR) * 16);
+        }
+        auto score_of = [&](float dot) -> float {
+            if (P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
+            return dot * P.scale;
+        };
+        // one job to the gather warps (scorer thread 0): wait for a free slot, fill it, publish it
+        auto post_job = [&](int bh, float M, float L) {
+            if (juse > 0 && !mbar_wait_bounded(bar_jempty + 8 * jslot, (juse - 1) & 1, flags)) return;
+            jobs[jslot].bh = bh, jobs[jslot].M = M, jobs[jslot].L = L;
+            mbar_arrive(bar_jfull + 8 * jslot);
+            if (++jslot == kPsJobs) jslot = 0, ++juse;
+        };
+        long long u = u0;
+        while (u < u1) {
+            const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
+            const int j1 = (int)min((long long)upb, j0 + (u1 - u));
+            const SampleRange sr = sample_range(P, bh / P.H);
+            const int jt = sr.row / R;   // the unit that also owns the new token
+            float qf[VPL][EPV];
+            float2 q2[VPL][E2];
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                Elem<T>::unpack(qraw[x], qf[x]);
+#pragma unroll
+                for (int e = 1; e < EPV; e += 2) q2[x][e >> 1] = make_float2(qf[x][e - 1], qf[x][e]);
+            }
+            if (u + (j1 - j0) < u1) {   // this CTA goes on with the next (batch, head): fetch its q now
+#pragma unroll
+                for (int x = 0; x < VPL; ++x)
+                    if (li + x * LPR < VPR)
+                        qraw[x] = *reinterpret_cast<const uint4*>(qbase + (size_t)(bh + 1) * ROWB + (li + x * LPR) * 16);
+            }
+            const bool owns_new = sr.ok && j0 <= jt && jt < j1;
+            uint4 knew[VPL];
+#pragma unroll
+            for (int x = 0; x < VPL; ++x) {
+                knew[x] = make_uint4(0, 0, 0, 0);
+                if (owns_new && li + x * LPR < VPR)
+                    knew[x] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB + (li + x * LPR) * 16);
+            }
+            float m = -CUDART_INF_F, l = 0.f;   // of the rows this lane was handed (see transposed_group_sum)
+            float* sc_row = P.scores + (size_t)bh * P.score_stride;
+
+            // RB rows per lane group at a time: shared-memory loads first, packed fp32 FMAs,
+            // interleaved butterfly sums; FULL: every row of the batch exists
+            auto batch = [&](auto full_tag, const unsigned char* ks, int base, int nrows, int row0) {
+                constexpr bool FULL = decltype(full_tag)::value;
+                uint4 kraw[RB][VPL];
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) {
+                    const int r = base + g * RB + uu;   // a lane group owns RB consecutive rows: its scores are one vector store
+                    const int rc = FULL ? r : min(r, nrows - 1);
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x)
+                        if (kAllLanes || li + x * LPR < VPR)
+                            kraw[uu][x] = *reinterpret_cast<const uint4*>(ks + (size_t)rc * ROWB + (li + x * LPR) * 16);
+                }
+                float sc[RB];
+#pragma unroll
+                for (int uu = 0; uu < RB; ++uu) {
+                    float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x)
+                        if (kAllLanes || li + x * LPR < VPR) {
+                            float2 k2[E2];
+                            Elem<T>::unpack2(kraw[uu][x], k2);
+#pragma unroll
+                            for (int e = 0; e < E2; ++e) a = __ffma2_rn(q2[x][e], k2[e], a);
+                        }
+                    sc[uu] = a.x + a.y;
+                }
+                // every lane ends up with ONE row's total (row `myrow` of the group's RB rows) and keeps the
+                // running (max, sum) of the rows it is handed: no cross-lane softmax step in the loop
+                const float dot = transposed_group_sum<LPR, RB>(sc, li);
+                const bool okr = FULL || base + g * RB + myrow < nrows;
+                const float st = okr ? score_of(dot) : -CUDART_INF_F;
+                if (okr && store_lane && !(P.chunk_rows & 1)) sc_row[row0 + base + g * RB + myrow] = st;   // RB lanes, RB * 4 contiguous bytes
+                const float m_new = fmaxf(m, st);
+                if (FULL || m_new != -CUDART_INF_F) {
+                    l = l * __expf(m - m_new) + __expf(st - m_new);   // as attention.cu:1113
+                    m = m_new;
+                }
+            };
+
+            if (sr.ok) {
+                for (int j = j0; j < j1; ++j) {
+                    const int lo = max(j * R, sr.first), hi = min((j + 1) * R, sr.row);
+                    if (hi <= lo) continue;
+                    const int nrows = hi - lo;
+                    const bool ready = mbar_wait_bounded(bar_full + 8 * stage, phase, flags);
+                    const unsigned char* ks = smem + (size_t)stage * tile_bytes;
+                    if (ready) {
+                        int base = 0;
+                        for (; base + RB * NG <= nrows; base += RB * NG) batch(std::true_type{}, ks, base, nrows, lo);
+                        if (base < nrows) batch(std::false_type{}, ks, base, nrows, lo);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+                    if (++stage == (uint32_t)S) stage = 0, phase ^= 1;
+                }
+            }
+            // the new token: score against k, append k at row sr.row (attention.cu:900-958)
+            if (owns_new) {
+                float dot = 0.f;
+#pragma unroll
+                for (int x = 0; x < VPL; ++x) {
+                    float kf[EPV];
+                    Elem<T>::unpack(knew[x], kf);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) dot = fmaf(qf[x][e], kf[e], dot);
+                }
+                dot = group_sum<LPR>(dot);
+                if (g == 0) {
+                    const float st = score_of(dot);
+                    if (li == 0) {   // one lane's state takes the new token (lane 0 is a store lane, so it is counted below)
+                        const float m_new = fmaxf(m, st);
+                        l = l * __expf(m - m_new) + __expf(st - m_new);
+                        m = m_new;
+                        sc_row[sr.row] = st;
+                    }
+                    const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
+#pragma unroll
+                    for (int x = 0; x < VPL; ++x)
+                        if (li + x * LPR < VPR)
+                            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + (li + x * LPR) * 16) = knew[x];
+                }
+            }
+            // ---- (max, sum) of this CTA's piece: the first scorer warp combines the lane groups ----
+            if (store_lane) red[2 * (g * RB + myrow)] = m, red[2 * (g * RB + myrow) + 1] = l;   // one entry per (group, row class)
+            __threadfence();   // this thread's scores are visible device-wide before anybody is told about them
+            named_bar_sync(1, nct);
+            const bool whole = (j0 == 0 && j1 == upb);
+            if (warp == 1) {
+                float Mg = -CUDART_INF_F, Lg = 0.f;
+                for (int gg = lane; gg < NG * RB; gg += 32) Mg = fmaxf(Mg, red[2 * gg]);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) Mg = fmaxf(Mg, __shfl_xor_sync(0xffffffffu, Mg, off));
+                for (int gg = lane; gg < NG * RB; gg += 32)
+                    if (red[2 * gg] != -CUDART_INF_F) Lg += red[2 * gg + 1] * __expf(red[2 * gg] - Mg);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) Lg += __shfl_xor_sync(0xffffffffu, Lg, off);
+                if (!sr.ok) {
+                    // the CTA that owns the pair's first unit reports the bad length and clears the output row
+                    if (lane == 0 && j0 == 0) atomicOr(P.status, kStatusBadLength);
+                    if (j0 == 0)
+                        for (int d = lane; d < DH; d += 32) Elem<T>::store(static_cast<T*>(P.out) + (size_t)bh * DH + d, 0.f);
+                } else if (whole) {
+                    if (lane == 0) post_job(bh, Mg, Lg);
+                } else {
+                    // a pair cut over several CTAs: partial (max, sum) to global memory; whoever arrives last combines
+                    float* part = P.partials + (size_t)(blockIdx.x + bh) * (DH + 2);
+                    const int c_first = cut.first_cta_of(bh), c_last = cut.last_cta_of(bh);
+                    const int count = c_last - c_first + 1;
+                    int last = 0;
+                    if (lane == 0) {
+                        part[DH] = Mg, part[DH + 1] = Lg;
+                        __threadfence();
+                        last = atomicAdd(P.tickets + bh, 1) == count - 1;
+                    }
+                    last = __shfl_sync(0xffffffffu, last, 0);
+                    if (last) {
+                        __threadfence();
+                        const float* pbase = P.partials + (size_t)(c_first + bh) * (DH + 2);
+                        float MM = -CUDART_INF_F, LL = 0.f;
+                        for (int k = lane; k < count; k += 32) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) MM = fmaxf(MM, __shfl_xor_sync(0xffffffffu, MM, off));
+                        for (int k = lane; k < count; k += 32) {
+                            const float mk = __ldcg(pbase + (size_t)k * (DH + 2) + DH);
+                            if (mk != -CUDART_INF_F) LL += __ldcg(pbase + (size_t)k * (DH + 2) + DH + 1) * __expf(mk - MM);
+                        }
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) LL += __shfl_xor_sync(0xffffffffu, LL, off);
+                        if (lane == 0) {
+                            P.tickets[bh] = 0;   // ready for the next launch on this stream
+                            post_job(bh, MM, LL);
+                        }
+                    }
+                }
+            }
+            named_bar_sync(1, nct);   // `red` is reused by the next segment
+            u += j1 - j0;
+        }
+        if (tid == 32) post_job(-1, 0.f, 0.f);   // no more jobs from this CTA
+    } else {
+        // ---------------- gatherers ----------------
+        const int gw = warp - 1 - nsw;
+        const int gl = lane / LPR, li = lane % LPR;
+        int* my_idx = list_idx + gw * kPsListCap;
+        float* my_p = list_p + gw * kPsListCap;
+        const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
+        const unsigned char* my_stage_p = gstage + gw * kPsStageBytes;
+        const uint32_t my_stage = smem_u32(my_stage_p);
+        uint32_t jslot = 0, jphase = 0;
+        for (;;) {
+            if (!mbar_wait_bounded(bar_jfull + 8 * jslot, jphase, flags)) break;
+            const int bh = jobs[jslot].bh;
+            const float M = jobs[jslot].M, Lsum = jobs[jslot].L;
+            if (bh < 0) break;
+            const SampleRange sr = sample_range(P, bh / P.H);
+            // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
+            // the torch-rounding mode divides exactly like torch's softmax does
+            const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
+            const float theta = Elem<T>::round(P.p * inv);
+            auto prob_of = [&](float s) -> float {
+                if (prune) return Elem<T>::round(__expf(s - M) * inv);
+                return Elem<T>::round(expf(s - M) / Lsum);
+            };
+            const float* sc_row = P.scores + (size_t)bh * P.score_stride;
+            float2 acc2[VPL][E2];
+#pragma unroll
+            for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
+
+            const int nwords = (sr.row >> 5) + 1;   // 32-row words that hold rows 0..sr.row
+            // scores of up to 16 words, all loads before the first use (written by other threads: read at L2)
+            auto load_scores = [&](int w0, float (&s)[kPsWordsPerRound]) {
+#pragma unroll
+                for (int k = 0; k < kPsWordsPerRound; ++k) {
+                    const int i = (w0 + k) * 32 + lane;
+                    s[k] = (w0 + k < nwords && i >= sr.first && i < sr.row) ? __ldcg(sc_row + i) : 0.f;
+                }
+            };
+            float s[kPsWordsPerRound];
+            int w0 = gw * kPsWordsPerRound;
+            if (w0 < nwords) load_scores(w0, s);
+            for (; w0 < nwords && !(P.chunk_rows & 2); w0 += NGW * kPsWordsPerRound) {
+                int n = 0;
+                __syncwarp();   // the previous round's list has been consumed by every lane
+#pragma unroll
+                for (int k = 0; k < kPsWordsPerRound; ++k) {
+                    if (w0 + k >= nwords) break;   // warp-uniform
+                    const int base = (w0 + k) * 32, i = base + lane;
+                    const bool cached = i >= sr.first && i < sr.row;
+                    float pr = 0.f;
+                    bool keep = false;
+                    if (cached) {
+                        pr = prob_of(s[k]);
+                        keep = prune ? !Elem<T>::leq(pr, theta) : true;
+                    }
+                    const unsigned bal = __ballot_sync(0xffffffffu, keep);
+                    if (P.kept_mask != nullptr && lane == 0)
+                        P.kept_mask[(size_t)bh * P.mask_words + (w0 + k)] =
+                            bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+                    if (keep) {
+                        const int pos = n + __popc(bal & ((1u << lane) - 1u));
+                        my_idx[pos] = i, my_p[pos] = pr;
+                    }
+                    n += __popc(bal);
+                }
+                // the next round's scores travel while this round's V rows are fetched
+                if (w0 + NGW * kPsWordsPerRound < nwords) load_scores(w0 + NGW * kPsWordsPerRound, s);
+                __syncwarp();
+                // survivors in row order; lane group gl takes entries gl, gl + GPW, ...; a batch of SROWS rows is
+                // copied into the warp's staging area (every lane its own 16-byte pieces), then accumulated
+                for (int base = 0; base < n; base += SROWS) {
+#pragma unroll
+                    for (int st = 0; st < STEPS; ++st) {
+                        const int e = base + st * GPW + gl;
+                        if (e < n) {
+                            const unsigned char* src = vc + cache_row_offset(P, bh, my_idx[e], ROWB);
+#pragma unroll
+                            for (int x = 0; x < VPL; ++x)
+                                if (kAllLanes || li + x * LPR < VPR)
+                                    cp_async_16(my_stage + (uint32_t)((st * GPW + gl) * ROWB + (li + x * LPR) * 16), src + (li + x * LPR) * 16);
+                        }
+                    }
+                    cp_async_wait_all();
+#pragma unroll
+                    for (int st = 0; st < STEPS; ++st) {
+                        const int e = base + st * GPW + gl;
+                        if (e < n) {
+                            const float pe = my_p[e];
+                            const float2 p2 = make_float2(pe, pe);
+#pragma unroll
+                            for (int x = 0; x < VPL; ++x)
+                                if (kAllLanes || li + x * LPR < VPR) {
+                                    float2 v2[E2];
+                                    Elem<T>::unpack2(*reinterpret_cast<const uint4*>(my_stage_p + (st * GPW + gl) * ROWB + (li + x * LPR) * 16), v2);
+#pragma unroll
+                                    for (int e2 = 0; e2 < E2; ++e2) acc2[x][e2] = __ffma2_rn(p2, v2[e2], acc2[x][e2]);
+                                }
+                        }
+                    }
+                }
+            }
+            // lane groups of the warp added in index order (butterfly over the group bits), then one
+            // vector per warp in shared memory
+#pragma unroll
+            for (int off = LPR; off < 32; off <<= 1)
+#pragma unroll
+                for (int x = 0; x < VPL; ++x)
+#pragma unroll
+                    for (int e = 0; e < E2; ++e) {
+                        acc2[x][e].x += __shfl_xor_sync(0xffffffffu, acc2[x][e].x, off);
+                        acc2[x][e].y += __shfl_xor_sync(0xffffffffu, acc2[x][e].y, off);
+                    }
+            float* mine = gred + ((size_t)jslot * NGW + gw) * DH;
+            if (gl == 0) {
+#pragma unroll
+                for (int x = 0; x < VPL; ++x) {
+                    const int vec = li + x * LPR;
+                    if (vec < VPR) {
+#pragma unroll
+                        for (int e = 0; e < E2; ++e) {
+                            mine[vec * EPV + 2 * e] = acc2[x][e].x;
+                            mine[vec * EPV + 2 * e + 1] = acc2[x][e].y;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_gdone + 8 * jslot);
+            if (gw == 0) {
+                // the first gather warp adds the warps' vectors in order, then the new token, which is
+                // never pruned (attention.cu:1227-1256): append v, add P_t * v
+                const bool ready = mbar_wait_bounded(bar_gdone + 8 * jslot, jphase, flags);
+                const float pt = prob_of(__ldcg(sc_row + sr.row));
+                const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
+                const T* vnew = static_cast<const T*>(P.v) + (size_t)bh * DH;
+                T* vdst = reinterpret_cast<T*>(static_cast<unsigned char*>(P.v_cache) + row_off);
+                T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+                if (ready) {
+                    for (int d = lane; d < DH; d += 32) {
+                        float A = 0.f;
+#pragma unroll
+                        for (int w = 0; w < NGW; ++w) A += gred[((size_t)jslot * NGW + w) * DH + d];
+                        const T vd = vnew[d];
+                        vdst[d] = vd;
+                        Elem<T>::store(outp + d, fmaf(pt, Elem<T>::to_float(vd), A));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_jempty + 8 * jslot);   // the slot and its vectors are free again
+            }
+            if (++jslot == kPsJobs) jslot = 0, jphase ^= 1;
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && flags[0]) atomicOr(P.status, kStatusWaitTimeout);
+}
+
+}  // namespace ffa_dev

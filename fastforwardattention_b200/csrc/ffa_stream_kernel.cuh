@@ -1,53 +1,50 @@
-// The streaming split-KV kernel: exact one-pass attention, or the score pass of the two-launch pruning path.
+// The streaming split-KV kernel: exact one-pass attention.
 #pragma once
 #include "ffa_device_common.cuh"
 
 namespace ffa_dev {
 
 // Combines `count` partials (weighted sum [DH], running max, running sum; stride DH + 2 floats)
-// that other CTAs left in global memory, in slot order, and writes the normalised output
-// (one-pass) or the pair's (max, sum) (score pass).  Called by all `nthreads` threads of the
-// CTA that arrived last.
-template <typename T, int DH, int PASS, bool kPrecise>
-__device__ __forceinline__ void merge_partials(const float* pbase, int count, T* outp, float* stats2, int tid, int nthreads)
+// that other CTAs left in global memory, in slot order, and writes the normalised output.
+// Called by all `nthreads` threads of the CTA that arrived last.
+template <typename T, int DH, bool kPrecise>
+__device__ __forceinline__ void merge_partials(const float* pbase, int count, T* outp, int tid, int nthreads)
 {
-    auto expo = [&](float x) -> float { return PASS == kPassScore ? __expf(x) : (kPrecise ? expf(x) : fast_exp2(x)); };
-    const int nd = PASS == kPassOne ? DH : 1;
+    auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
     float MM = -CUDART_INF_F;
     for (int k = 0; k < count; ++k) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
-    for (int d = tid; d < nd; d += nthreads) {
+    for (int d = tid; d < DH; d += nthreads) {
         float A = 0.f, L = 0.f;
         for (int k = 0; k < count; ++k) {
             const float* pk = pbase + (size_t)k * (DH + 2);
             const float mk = __ldcg(pk + DH);
             const float w = mk == -CUDART_INF_F ? 0.f : expo(mk - MM);
-            if (PASS == kPassOne) A = fmaf(w, __ldcg(pk + d), A);
+            A = fmaf(w, __ldcg(pk + d), A);
             L = fmaf(w, __ldcg(pk + DH + 1), L);
         }
-        if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
-        else stats2[0] = MM, stats2[1] = L;
+        Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
     }
 }
 
 // ------------------------------------------------------------------------------------------
-// Streaming kernel (one-pass attention, or the score pass of the two-pass modes)
+// Streaming kernel (one-pass attention)
 // ------------------------------------------------------------------------------------------
-// Shared memory: [stages][K tile | V tile] ring (score pass: K tile only), then the group
+// Shared memory: [stages][K tile | V tile] ring, then the group
 // reduction area [NG][DH + 4] (rows 16-byte aligned; max and sum in the tail), then
 // full/empty barriers, then two flags, then the CTA's partial result [DH + 2] for the merge
 // inside a thread-block cluster.
 // Warp 0 issues the copies (one elected lane); warps 1.. compute.  A lane group of LPR lanes
 // owns a row: 16-byte shared-memory reads, fp32 FMAs, butterfly sum.  Each group keeps its
 // own online-softmax state, so the row loop has no CTA-level synchronisation at all.
-template <typename T, int DH, int PASS>
+template <typename T, int DH>
 // Register budget: 4 resident CTAs of 160 threads (or 2 of 288) need <= 96 registers per thread;
 // head_dim 80 keeps five vectors per lane in flight and is compiled for 2 CTAs of 160 threads.
 __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_stream_kernel(const FfaStepParams P)
 {
     using G = RowGeom<T, DH>;
     constexpr int EPV = G::EPV, ROWB = G::ROWB, VPR = G::VPR, LPR = G::LPR, VPL = G::VPL, RB = G::RB;
-    constexpr bool kPrecise = sizeof(T) == 4 || PASS == kPassScore;  // natural-log domain, full-precision exp
-    constexpr int TENSORS = PASS == kPassOne ? 2 : 1;
+    constexpr bool kPrecise = sizeof(T) == 4;  // natural-log domain, full-precision exp
+    constexpr int TENSORS = 2;
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr int RS = DH + 4;  // row stride of the group reduction area, in floats
 
@@ -67,7 +64,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
     // memory, no fence, no arrival counter.  The launcher guarantees grid = B*H*C, so a CTA owns
     // exactly one part of exactly one pair.
     float* clp = reinterpret_cast<float*>(const_cast<int*>(flags) + 4);
-    const bool cl = PASS == kPassOne && P.cluster > 1;
+    const bool cl = P.cluster > 1;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
     const uint32_t ring = smem_u32(smem);
 
@@ -109,7 +106,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 const size_t off = cache_row_offset(P, bh, lo, ROWB);
                 mbar_expect_tx(bar_full + 8 * stage, bytes * TENSORS);
                 bulk_copy_g2s(ring + stage * stage_bytes, kc + off, bytes, bar_full + 8 * stage);
-                if (TENSORS == 2) bulk_copy_g2s(ring + stage * stage_bytes + tile_bytes, vc + off, bytes, bar_full + 8 * stage);
+                bulk_copy_g2s(ring + stage * stage_bytes + tile_bytes, vc + off, bytes, bar_full + 8 * stage);
                 ++issued;
                 if (++stage == (uint32_t)S) stage = 0, ++use;
             }
@@ -169,7 +166,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 if (owns_new && li + x * LPR < VPR) {
                     const size_t src = (size_t)bh * ROWB + (li + x * LPR) * 16;
                     knew[x] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.k) + src);
-                    if (PASS == kPassOne) vnew[x] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + src);
+                    vnew[x] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(P.v) + src);
                 }
             }
             const float qmul = kPrecise ? 1.f : P.scale * kLog2e;
@@ -189,18 +186,13 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
 #pragma unroll
                 for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
 
-            auto score_of = [&](float dot) -> float {
-                if (!kPrecise) return dot;
-                if (PASS == kPassScore && P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
-                return dot * P.scale;
-            };
-            // the score pass only feeds the softmax denominator: __expf, like the reference (attention.cu:1113)
-            auto expo = [&](float x) -> float { return PASS == kPassScore ? __expf(x) : (kPrecise ? expf(x) : fast_exp2(x)); };
+            auto score_of = [&](float dot) -> float { return kPrecise ? dot * P.scale : dot; };
+            auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
 
             // RB (four; two for head_dim 80) rows per lane group at a time: all shared-memory loads first, then the
             // packed fp32 FMAs (fma.rn.f32x2), four interleaved butterfly sums, one softmax
             // update.  FULL: every row of the batch exists (no predicates, no clamping).
-            auto batch = [&](auto full_tag, const unsigned char* ks, const unsigned char* vs, int base, int nrows, int row0) {
+            auto batch = [&](auto full_tag, const unsigned char* ks, const unsigned char* vs, int base, int nrows) {
                 constexpr bool FULL = decltype(full_tag)::value;
                 int rc[RB];
                 uint4 kraw[RB][VPL];
@@ -246,7 +238,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
 #pragma unroll
                 for (int uu = 0; uu < RB; ++uu) psum += pr[uu];
                 l = fmaf(l, corr, psum);
-                if (PASS == kPassOne) {
+                {
                     uint4 vraw[RB][VPL];
 #pragma unroll
                     for (int uu = 0; uu < RB; ++uu)
@@ -271,10 +263,6 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                                 for (int e = 0; e < E2; ++e) acc2[x][e] = __ffma2_rn(p2, v2[e], acc2[x][e]);
                             }
                     }
-                } else if (li == 0) {
-#pragma unroll
-                    for (int uu = 0; uu < RB; ++uu)
-                        if (FULL || base + uu * NG + g < nrows) P.scores[(size_t)bh * P.Lmax + row0 + base + uu * NG + g] = sc[uu];
                 }
             };
 
@@ -288,8 +276,8 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                     const unsigned char* vs = ks + tile_bytes;
                     if (ready) {
                         int base = 0;
-                        for (; base + RB * NG <= nrows; base += RB * NG) batch(std::true_type{}, ks, vs, base, nrows, lo);
-                        if (base < nrows) batch(std::false_type{}, ks, vs, base, nrows, lo);
+                        for (; base + RB * NG <= nrows; base += RB * NG) batch(std::true_type{}, ks, vs, base, nrows);
+                        if (base < nrows) batch(std::false_type{}, ks, vs, base, nrows);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
@@ -320,7 +308,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                         const int vec = li + x * LPR;
                         if (vec < VPR) {
                             *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.k_cache) + row_off + vec * 16) = knew[x];
-                            if (PASS == kPassOne) {
+                            {
                                 *reinterpret_cast<uint4*>(static_cast<unsigned char*>(P.v_cache) + row_off + vec * 16) = vnew[x];
                                 float2 v2[E2];
                                 Elem<T>::unpack2(vnew[x], v2);
@@ -332,22 +320,19 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                             }
                         }
                     }
-                    if (PASS == kPassScore && li == 0) P.scores[(size_t)bh * P.Lmax + sr.row] = st;
                 }
             }
 
             // ---- merge the groups of this CTA ----
             float* mine = red + g * RS;
-            if (PASS == kPassOne) {
 #pragma unroll
-                for (int x = 0; x < VPL; ++x) {
-                    const int vec = li + x * LPR;
-                    if (vec < VPR) {
+            for (int x = 0; x < VPL; ++x) {
+                const int vec = li + x * LPR;
+                if (vec < VPR) {
 #pragma unroll
-                        for (int e = 0; e < E2; e += 2)
-                            *reinterpret_cast<float4*>(mine + vec * EPV + 2 * e) =
-                                make_float4(acc2[x][e].x, acc2[x][e].y, acc2[x][e + 1].x, acc2[x][e + 1].y);
-                    }
+                    for (int e = 0; e < E2; e += 2)
+                        *reinterpret_cast<float4*>(mine + vec * EPV + 2 * e) =
+                            make_float4(acc2[x][e].x, acc2[x][e].y, acc2[x][e + 1].x, acc2[x][e + 1].y);
                 }
             }
             if (li == 0) mine[DH] = m, mine[DH + 1] = l;
@@ -358,23 +343,21 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             const int slot = blockIdx.x + bh;
             float* part = P.partials + (size_t)slot * (DH + 2);
             T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
-            const int nd = PASS == kPassOne ? DH : 1;
-            for (int d = ctid; d < nd; d += nct) {
+            for (int d = ctid; d < DH; d += nct) {
                 float A = 0.f, L = 0.f;
                 for (int gg = 0; gg < NG; ++gg) {
                     const float mg = red[gg * RS + DH];
                     const float w = mg == -CUDART_INF_F ? 0.f : expo(mg - M);
-                    if (PASS == kPassOne) A = fmaf(w, red[gg * RS + d], A);
+                    A = fmaf(w, red[gg * RS + d], A);
                     L = fmaf(w, red[gg * RS + DH + 1], L);
                 }
                 if (whole) {
-                    if (PASS == kPassOne) Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
-                    else P.stats[2 * bh] = M, P.stats[2 * bh + 1] = L;
+                    Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
                 } else if (cl) {
                     clp[d] = A;
                     if (d == 0) clp[DH] = M, clp[DH + 1] = L;
                 } else {
-                    if (PASS == kPassOne) part[d] = A;
+                    part[d] = A;
                     if (d == 0) part[DH] = M, part[DH + 1] = L;
                 }
             }
@@ -391,7 +374,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 named_bar_sync(1, nct);
                 if (flags[1]) {
                     __threadfence();
-                    merge_partials<T, DH, PASS, kPrecise>(P.partials + (size_t)(c_first + bh) * (DH + 2), count, outp, P.stats + 2 * bh, ctid, nct);
+                    merge_partials<T, DH, kPrecise>(P.partials + (size_t)(c_first + bh) * (DH + 2), count, outp, ctid, nct);
                     if (ctid == 0) P.tickets[bh] = 0;  // ready for the next launch on this stream
                 }
             }
@@ -450,7 +433,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             __syncthreads();
             if (flags[1]) {
                 __threadfence();
-                merge_partials<T, DH, PASS, kPrecise>(P.partials + (size_t)bh * K * (DH + 2), K, outp, nullptr, threadIdx.x, blockDim.x);
+                merge_partials<T, DH, kPrecise>(P.partials + (size_t)bh * K * (DH + 2), K, outp, threadIdx.x, blockDim.x);
                 if (threadIdx.x == 0) P.tickets[bh] = 0;
             }
         }

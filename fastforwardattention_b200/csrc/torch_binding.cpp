@@ -183,6 +183,9 @@ struct FastForwardAttn {
             if (!kept_mask.defined()) kept_mask = torch::zeros({B, H, (Lmax + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
             mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
         }
+        // pruned and torch-rounding steps of any size go through an fp32 score scratch (4 bytes per cache row,
+        // under 1 % of the caches): bound the first time such a step is asked for
+        if ((p > 0.0 || mode == FFA_MODE_ROUND_LIKE_TORCH) && !has_scores) bind_workspace(true);
         auto call = [&]() {
             return ffa_attention(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
                                  (float)softmax_scale, (int)t, seq_lengths ? sl.data_ptr<int>() : nullptr, right_or_no_padding,
@@ -439,6 +442,7 @@ struct PagedEngine {
                 kept_mask = torch::zeros({B, H, (max_pages * page_rows + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
             mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
         }
+        if ((p > 0.0 || mode == FFA_MODE_ROUND_LIKE_TORCH) && !has_scores) bind_workspace(true);
         auto call = [&]() {
             return ffa_attention_paged(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kp.data_ptr(), vp.data_ptr(),
                                        table.data_ptr<int>(), (int)max_pages, (int)page_rows, out.data_ptr(), (float)softmax_scale,
@@ -470,7 +474,8 @@ struct PagedEngine {
     void set_mode(const std::string& m)
     {
         TORCH_CHECK(m == "exact" || m == "round_like_torch", "PagedEngine: mode must be 'exact' or 'round_like_torch'");
-        check(ffa_plan_set_mode(plan, m == "exact" ? FFA_MODE_EXACT : FFA_MODE_ROUND_LIKE_TORCH), "mode");
+        mode = m == "exact" ? FFA_MODE_EXACT : FFA_MODE_ROUND_LIKE_TORCH;
+        check(ffa_plan_set_mode(plan, mode), "mode");
     }
     void set_prune_path(int path) { check(ffa_plan_set_prune_path(plan, path), "prune path"); }
     void record_kept_mask(bool on) { want_mask = on; }
@@ -492,7 +497,7 @@ struct PagedEngine {
     torch::Tensor kp, vp, workspace, kept_mask;
     c10::Device device{c10::kCUDA, 0};
     int64_t B = 0, H = 0, Dh = 0, page_rows = 0, max_pages = 0;
-    int dtype = 0;
+    int dtype = 0, mode = FFA_MODE_EXACT;
     bool has_scores = false, want_mask = false;
 };
 
@@ -526,7 +531,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
              py::arg("k"), py::arg("v"), py::arg("softmax_scale"), py::arg("seq_lengths"), py::arg("prob_thresh") = 0.0,
              py::arg("out") = py::none(), py::arg("max_row") = -1)
         .def("set_mode", &FastForwardAttn::set_mode, "'exact' (default) or 'round_like_torch'")
-        .def("set_prune_path", &FastForwardAttn::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
+        .def("set_prune_path", &FastForwardAttn::set_prune_path, "0 choose, 1 cluster kernel, 2 streaming kernel")
         .def("set_cluster_merge", &FastForwardAttn::set_cluster_merge, "merge split pairs inside a thread-block cluster (default on)")
         .def("set_launch", &FastForwardAttn::set_launch, py::arg("tile_rows") = 0, py::arg("stages") = 0,
              py::arg("consumer_warps") = 0, py::arg("ctas_per_sm") = 0, py::arg("grid") = 0)
@@ -554,7 +559,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
              py::arg("k"), py::arg("v"), py::arg("page_table"), py::arg("softmax_scale"), py::arg("rows"),
              py::arg("prob_thresh") = 0.0, py::arg("out") = py::none(), py::arg("max_row") = -1)
         .def("set_mode", &PagedEngine::set_mode, "'exact' (default) or 'round_like_torch'")
-        .def("set_prune_path", &PagedEngine::set_prune_path, "0 choose, 1 fused cluster kernel, 2 two kernels")
+        .def("set_prune_path", &PagedEngine::set_prune_path, "0 choose, 1 cluster kernel, 2 streaming kernel")
         .def("record_kept_mask", &PagedEngine::record_kept_mask)
         .def("get_kept_mask", &PagedEngine::get_kept_mask)
         .def("device_status", &PagedEngine::device_status);

@@ -106,9 +106,12 @@ int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch);
 int ffa_plan_set_launch(ffa_plan_t* plan, const ffa_launch_t* launch);
 int ffa_plan_set_mode(ffa_plan_t* plan, int mode);
 /* p > 0 and the torch-rounding mode need the global softmax statistics before any V row is
- * read.  Two implementations: 1 = one launch, a thread-block cluster per (batch, head) with the
- * scores in shared memory (needs no score scratch); 2 = two launches through an fp32 score
- * scratch in the workspace (any size).  0 (default) picks 1 whenever a slice fits in shared
+ * read.  Two implementations, one launch each: 1 = a thread-block cluster per (batch, head)
+ * with the scores in shared memory (needs no score scratch; small steps); 2 = the streaming
+ * kernel: a persistent grid streams the K rows of all pairs, leaves fp32 scores in the
+ * workspace's score scratch, and its gather warps fetch the surviving V rows of finished
+ * pairs while the K stream goes on (any size).  0 (default) picks 2 for steps that stream
+ * at least 200 MB of K when the score scratch is bound, else 1 whenever a slice fits in shared
  * memory.  The reference does both phases in one CTA per (batch, head) (attention.cu:1077-1257),
  * which is what caps its sequence length. */
 int ffa_plan_set_prune_path(ffa_plan_t* plan, int path);
@@ -117,14 +120,14 @@ int ffa_plan_set_prune_path(ffa_plan_t* plan, int path);
  * partial results in global memory and an arrival counter (on = 0; kept for comparison). */
 int ffa_plan_set_cluster_merge(ffa_plan_t* plan, int on);
 /* The fused pruning launch the planner picks for step t: CTAs per (batch, head) cluster, cache
- * rows per CTA, tile rows, grid and dynamic shared memory; all zero when the two-launch path
- * would run instead. */
+ * rows per CTA, tile rows, grid and dynamic shared memory; all zero when the streaming kernel
+ * would run instead (path 2, or no cluster shape fits). */
 int ffa_plan_get_prune_launch(const ffa_plan_t* plan, int t, int* cluster, int* chunk_rows, int* tile_rows, int* grid,
                               int* smem_bytes);
 
 /* Scratch the engine needs in device memory: split partials, arrival counters, the status
  * word and, when with_scores != 0 (needed for p > 0 and FFA_MODE_ROUND_LIKE_TORCH), one fp32
- * score per cache row (only the two-launch pruning path reads it; ffa_attention returns
+ * score per cache row (the streaming pruning kernel's scratch; ffa_attention returns
  * FFA_ERR_WORKSPACE if a call needs it and it is missing).  The caller allocates it (256-byte aligned) and binds it once;
  * binding clears the counters on the stream.  One workspace serves one stream at a time. */
 size_t ffa_workspace_bytes(const ffa_plan_t* plan, int with_scores);

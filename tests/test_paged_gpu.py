@@ -90,7 +90,7 @@ def _unpack_mask(mask: torch.Tensor, rows: int) -> torch.Tensor:
     return bits.reshape(m.shape[0], -1)[:, :rows].bool()
 
 
-@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+@pytest.mark.parametrize("path", [1, 2], ids=["cluster-kernel", "streaming-kernel"])
 @pytest.mark.parametrize("dt,Dh,pr,max_len", [(torch.float16, 64, 128, 1024), (torch.bfloat16, 128, 256, 1024),
                                               (torch.float32, 80, 128, 1024), (torch.float16, 64, 128, 1152)])
 def test_pruned_step_over_pages(dt, Dh, pr, max_len, path):

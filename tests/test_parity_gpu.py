@@ -124,7 +124,7 @@ def test_config_long_bf16(x):
     run_config(w, lambda i: i in (0, 1, 64, 127))
 
 
-@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+@pytest.mark.parametrize("path", [1, 2], ids=["cluster-kernel", "streaming-kernel"])
 @pytest.mark.parametrize("x", [512, 2048])
 def test_config_long_bf16_torch_rounding_mode(x, path):
     w = CONFIGS[f"long-{x}"]
@@ -251,7 +251,7 @@ def test_canary_rows_are_untouched():
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("p", [0.0, 1e-3])
-@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+@pytest.mark.parametrize("path", [1, 2], ids=["cluster-kernel", "streaming-kernel"])
 def test_left_padding_mask(dt, p, path):
     """The 9-argument overload of the reference: keys below seq_lengths[b] are masked
     (attention.cu:814-817, 1054, 1112-1113)."""
@@ -327,7 +327,7 @@ def test_per_sample_lengths_right_padding(dt):
 # ------------------------------------------------------------------------------------------
 # pruning: the kept set must equal the reference rule's
 # ------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+@pytest.mark.parametrize("path", [1, 2], ids=["cluster-kernel", "streaming-kernel"])
 @pytest.mark.parametrize("name", ["prune-fp16-b10-p1e-4", "prune-fp16-b10-p1e-3"])
 def test_pruning_workload_kept_set(name, path):
     w = CONFIGS[name]
@@ -352,7 +352,7 @@ def test_pruning_workload_kept_set(name, path):
     assert checked >= 6 and eng.status() == 0
 
 
-@pytest.mark.parametrize("path", [1, 2], ids=["fused-cluster", "two-kernels"])
+@pytest.mark.parametrize("path", [1, 2], ids=["cluster-kernel", "streaming-kernel"])
 @pytest.mark.parametrize("dt,Dh,B,H,Lp", [(torch.float32, 80, 1, 3, 333), (torch.float16, 80, 2, 2, 1500),
                                           (torch.bfloat16, 256, 1, 2, 2100), (torch.float32, 256, 1, 1, 40),
                                           (torch.float16, 128, 40, 8, 95), (torch.bfloat16, 64, 1, 1, 9000)])
@@ -428,7 +428,7 @@ def test_bounded_wait_times_out_and_reports():
     assert eng.status() == 0
 
 
-@pytest.mark.parametrize("p,path", [(0.0, 0), (1e-2, 1), (1e-2, 2)], ids=["exact", "prune-fused", "prune-two-kernels"])
+@pytest.mark.parametrize("p,path", [(0.0, 0), (1e-2, 1), (1e-2, 2)], ids=["exact", "prune-cluster", "prune-streaming"])
 def test_results_are_bitwise_reproducible(p, path):
     """Split partials are merged in slot order and pruning survivors are listed in row order, so
     two runs on the same inputs give the same bits whatever the CTA timing."""
@@ -486,7 +486,7 @@ def test_very_long_sequences_exact_and_pruned(dt, B, H, Dh, L):
     """Far beyond the reference's ~8 K-token limit (its scores live in 48 KB of shared memory,
     attention.cu:660-688): 128 K to 500 K tokens, few pairs, so a pair is spread over many
     clusters.  Exact step against an fp64 evaluation; pruned step (fused kernel where a slice's
-    scores fit in shared memory, two kernels where they do not) against the restated rule."""
+    scores fit in shared memory, the streaming kernel where they do not) against the restated rule."""
     from fastforwardattention_b200 import FastForwardAttn
 
     dev = torch.device("cuda:0")

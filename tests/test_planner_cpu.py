@@ -130,7 +130,7 @@ def test_fused_pruning_launch_rules():
     c, chunk, r, grid, smem = prune_launch(L, p, 32767)
     assert c >= 2 and chunk * c >= 32768 and chunk % 32 == 0 and smem <= SMEM_CTA
     assert SMEM_SM // (smem + 1024) >= 2
-    # a sequence no 8 slices can hold in shared memory falls back to the two-kernel path
+    # a sequence no 8 slices can hold in shared memory falls back to the streaming kernel
     L, p = offline(capi.F32, 1, 1, 64, 2000000)
     assert prune_launch(L, p, 1999999) == (0, 0, 0, 0, 0)
     for t in (0, 1, 31, 32, 33, 500):
