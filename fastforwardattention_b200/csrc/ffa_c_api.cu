@@ -11,7 +11,6 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
-#include <cstdlib>
 #include <new>
 
 #include "../../include/ffa_c_api.h"
@@ -50,8 +49,10 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 // bf16 x 128, batch 32 x 32 heads: 2 K tokens 154.9 vs 159.3 us, 1 K 81.8 vs 88.3 us, 512 45.6 vs
 // 48.9 us in favour of the aligned cut; 8 K tokens 603 vs 594 us against it)
 constexpr long long kAlignedBelowUnitsPerSlot = 200;
-// pruned steps that stream at least this many bytes of K take the streaming kernel (when the score scratch is bound)
-constexpr double kStreamPruneAboveBytes = 200e6;
+// pruned steps that stream at least this many bytes of K take the streaming kernel when the score scratch is bound
+// (bf16 x 128, 1024 pairs, 5 % of the V rows kept: 2 K tokens 119 vs 112 us for the cluster kernel, 3 K 162 vs 167 us,
+// 4 K 202 vs 223 us, 8 K 378 vs 428 us, 32 K 1492 vs 1830 us)
+constexpr double kStreamPruneAboveBytes = 700e6;
 
 }  // namespace
 
@@ -623,7 +624,6 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
         g_launches.fetch_add(1);
         return FFA_OK;
     }
-    { const char* dbg = getenv("FFA_DEBUG"); P.chunk_rows = dbg ? atoi(dbg) : 0; }
     r = ffa_k_decode_prune_stream(plan->dtype, plan->Dh, P, L.consumer_warps, L.smem_bytes, st);
     if (r != 0) return cuda_fail(r, "streaming pruning launch");
     g_launches.fetch_add(1);

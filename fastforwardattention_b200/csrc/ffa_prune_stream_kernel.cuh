@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         // ---------------- producer: K tiles of this CTA's run ----------------
         if (tid == 0) {
             const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache);
+            const uint64_t once = l2_policy_evict_first();   // K rows are read once: keep them from displacing the scores in L2
             uint32_t issued = 0, stage = 0, use = 0;
             int cur_b = -1;
             SampleRange sr{0, 0, false};
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
                 const uint32_t bytes = (uint32_t)(hi - lo) * ROWB;
                 mbar_expect_tx(bar_full + 8 * stage, bytes);
-                bulk_copy_g2s(ring + stage * tile_bytes, kc + cache_row_offset(P, bh, lo, ROWB), bytes, bar_full + 8 * stage);
+                bulk_copy_g2s_hint(ring + stage * tile_bytes, kc + cache_row_offset(P, bh, lo, ROWB), bytes, bar_full + 8 * stage, once);
                 ++issued;
                 if (++stage == (uint32_t)S) stage = 0, ++use;
             }
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 const float dot = transposed_group_sum<LPR, RB>(sc, li);
                 const bool okr = FULL || base + g * RB + myrow < nrows;
                 const float st = okr ? score_of(dot) : -CUDART_INF_F;
-                if (okr && store_lane && !(P.chunk_rows & 1)) sc_row[row0 + base + g * RB + myrow] = st;   // RB lanes, RB * 4 contiguous bytes
+                if (okr && store_lane) sc_row[row0 + base + g * RB + myrow] = st;   // RB lanes, RB * 4 contiguous bytes
                 const float m_new = fmaxf(m, st);
                 if (FULL || m_new != -CUDART_INF_F) {
                     l = l * __expf(m - m_new) + __expf(st - m_new);   // as attention.cu:1113
@@ -335,6 +336,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
         const unsigned char* my_stage_p = gstage + gw * kPsStageBytes;
         const uint32_t my_stage = smem_u32(my_stage_p);
+        const uint64_t once = l2_policy_evict_first();   // surviving V rows are read once too
         uint32_t jslot = 0, jphase = 0;
         for (;;) {
             if (!mbar_wait_bounded(bar_jfull + 8 * jslot, jphase, flags)) break;
@@ -369,7 +371,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
             float s[kPsWordsPerRound];
             int w0 = gw * kPsWordsPerRound;
             if (w0 < nwords) load_scores(w0, s);
-            for (; w0 < nwords && !(P.chunk_rows & 2); w0 += NGW * kPsWordsPerRound) {
+            for (; w0 < nwords; w0 += NGW * kPsWordsPerRound) {
                 int n = 0;
                 __syncwarp();   // the previous round's list has been consumed by every lane
 #pragma unroll
@@ -407,7 +409,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
 #pragma unroll
                             for (int x = 0; x < VPL; ++x)
                                 if (kAllLanes || li + x * LPR < VPR)
-                                    cp_async_16(my_stage + (uint32_t)((st * GPW + gl) * ROWB + (li + x * LPR) * 16), src + (li + x * LPR) * 16);
+                                    cp_async_16_hint(my_stage + (uint32_t)((st * GPW + gl) * ROWB + (li + x * LPR) * 16), src + (li + x * LPR) * 16, once);
                         }
                     }
                     cp_async_wait_all();
