@@ -21,3 +21,13 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Measured numbers the tests recorded (parity errors per configuration, timing tables)."""
+    from tests.helpers import REPORT
+
+    if REPORT:
+        terminalreporter.write_sep("-", "measured")
+        for line in REPORT:
+            terminalreporter.write_line(line)

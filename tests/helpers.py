@@ -5,6 +5,14 @@ import os
 import numpy as np
 import torch
 
+# lines the tests want shown after the run (measured errors, timing tables): printed by conftest's terminal summary
+REPORT = []
+
+
+def report(line: str) -> None:
+    REPORT.append(line)
+
+
 GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
 # max-abs gates stated by the benchmark definition: fp32 1e-6, fp16 / bf16 2e-3

@@ -17,7 +17,7 @@ from fastforwardattention_b200 import capi
 from fastforwardattention_b200.workloads import CONFIGS, Workload, device_prompt_kv, prompt_kv, step_qkv
 from oracle import ffa_oracle as O
 from tests.cabi_engine import CAbiEngine
-from tests.helpers import TOL, ULP, assert_close_ulp, golden_names, load_golden, max_err, same_dtype_gate
+from tests.helpers import TOL, ULP, assert_close_ulp, golden_names, load_golden, max_err, report, same_dtype_gate
 
 pytestmark = pytest.mark.gpu
 
@@ -101,8 +101,9 @@ def run_config(w: Workload, step_filter, mode=capi.MODE_EXACT, use_default=False
     last = w.max_len - 1
     assert torch.equal(eng.k_cache.view(N, w.max_len, w.Dh)[:, : last + 1].cpu(), orc.K[:, : last + 1])
     assert torch.equal(eng.v_cache.view(N, w.max_len, w.Dh)[:, : last + 1].cpu(), orc.V[:, : last + 1])
-    print(f"\n[parity] {w.name} mode={mode}: max|engine-torch|={worst['same']:.3e} "
-          f"oracle noise={worst['noise']:.3e} max|engine-fp64|={worst['f64']:.3e}")
+    report(f"[parity] {w.name} mode={'exact' if mode == capi.MODE_EXACT else 'round_like_torch'} path={prune_path}: "
+           f"max|engine - same-dtype torch| = {worst['same']:.3e} (gate {TOL[w.dtype]:.0e}), same-dtype torch vs fp64 = "
+           f"{worst['noise']:.3e}, max|engine - fp64| = {worst['f64']:.3e}")
     return worst
 
 
@@ -156,6 +157,7 @@ def test_long_sequence_full_size_sampled_heads(x):
     del K, V
     orc = O.DecodeOracle(Ks[:, None], Vs[:, None], w.max_len)
     outs = {}
+    worst = {"same": 0.0, "noise": 0.0, "f64": 0.0}
     for shape in ({}, {"tile_rows": 32, "stages": 2, "ctas_per_sm": 3}):
         eng.set_launch(**shape)
         for i, t in enumerate((w.prompt, w.prompt + 1, w.max_len - 1)):
@@ -175,8 +177,15 @@ def test_long_sequence_full_size_sampled_heads(x):
             ref64 = O.attention_reference(q[pick][:, None], orc.K[:, : t + 1], orc.V[:, : t + 1], w.scale, torch.float64)
             gs = got.view(N, w.Dh)[pick.to(dev)]
             assert_close_ulp(gs, ref64, w.dtype, f"{w.name} t={t} sampled heads vs fp64")
-            same_dtype_gate(gs, same, ref64, w.dtype, f"{w.name} t={t}")
+            err, noise = same_dtype_gate(gs, same, ref64, w.dtype, f"{w.name} t={t}")
+            # at the benchmarked lengths the stated gate holds as it stands, without the allowance for the oracle's own noise
+            assert err <= TOL[w.dtype], (w.name, t, err, noise)
+            worst["same"], worst["noise"] = max(worst["same"], err), max(worst["noise"], noise)
+            worst["f64"] = max(worst["f64"], max_err(gs, ref64))
             outs.setdefault(i, []).append(got.float().cpu())
+    report(f"[parity] {w.name} mode=exact, 6 sampled pairs x 3 steps x 2 launch shapes: max|engine - same-dtype torch| = "
+           f"{worst['same']:.3e} (gate {TOL[w.dtype]:.0e}, un-widened), same-dtype torch vs fp64 = {worst['noise']:.3e}, "
+           f"max|engine - fp64| = {worst['f64']:.3e}")
     # the result must not depend on how the work was cut (different tiles, ring, grid)
     for i, (a, b) in outs.items():
         assert (a - b).abs().max().item() <= 2 * ULP[w.dtype] * max(1.0, a.abs().max().item())

@@ -17,6 +17,7 @@ import torch
 
 from fastforwardattention_b200.workloads import CONFIGS, device_prompt_kv, device_step_qkv
 from tests import ref_kernel
+from tests.helpers import report
 from tests.ref_kernel import _p
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_kernel.available(), reason="oracle/_ref/libffa_ref.so not built")]
@@ -96,7 +97,7 @@ def measure(name):
     return row
 
 
-def test_engine_is_faster_than_the_reference_kernel_on_its_own_configurations(capsys):
+def test_engine_is_faster_than_the_reference_kernel_on_its_own_configurations():
     rows = [measure(n) for n in NAMES]
     lines = ["", "reference kernel (attention.cu, sm_100a) vs this engine, us per decode step at the last step:",
              f"{'workload':24s} {'MB':>7s} {'ref optimized':>14s} {'ref FT default':>15s} {'engine':>9s} {'engine, graph':>14s} {'speed-up':>9s}"]
@@ -104,7 +105,7 @@ def test_engine_is_faster_than_the_reference_kernel_on_its_own_configurations(ca
         best = min(r["optimized"], r["ft_default"])
         lines.append(f"{r['workload']:24s} {r['MB']:7.1f} {r['optimized']:14.1f} {r['ft_default']:15.1f} {r['engine']:9.1f} "
                      f"{r['engine_graph']:14.1f} {best / r['engine_graph']:8.1f}x")
-    with capsys.disabled():
-        print("\n".join(lines))
+    for line in lines[1:]:
+        report(line)
     for r in rows:
         assert r["engine"] < min(r["optimized"], r["ft_default"]), r
