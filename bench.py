@@ -41,7 +41,7 @@ FALLBACK_HBM_GBS = 6650.0
 TRAFFIC_RATIO = {"exact": 1.004, "pruned": 0.99}
 # workloads reported in the `configs` key next to the headline (kernel time only, N = 1)
 EXTRA_CONFIGS = ("opt13b-fp32-b1", "opt13b-fp16-b10", "gptj-fp16-b8", "prune-fp16-b10-p1e-3", "long-512", "long-2048",
-                 "long-8192")
+                 "long-8192", "prune-long-8192")
 ROUND_LIKE_TORCH_CONFIGS = ("long-512", "long-2048")
 
 
@@ -512,7 +512,8 @@ def main():
                 "hbm_gbs_all_gpus": world * sum(alg) / (loop_ms * 1e-3) / 1e9,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
-                             "kernel": "ffa_stream_kernel (one-pass)" if w.p == 0 else "ffa_prune_cluster_kernel",
+                             "kernel": "ffa_stream_kernel (one-pass)" if w.p == 0 else
+                             "ffa_prune_stream_kernel" if w.B * w.H * w.max_len * w.Dh * es >= 700e6 else "ffa_prune_cluster_kernel",
                              "kept_v_rows": kept_frac, "bytes_per_launch": per_launch_alg,
                              "avg_launch_ms": ksum_ms / args.steps,
                              "duration_from": "CUDA events around the timed steps" if use_region else

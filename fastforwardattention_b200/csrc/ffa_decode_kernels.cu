@@ -188,31 +188,46 @@ int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long 
     return (int)cudaGetLastError();
 }
 
+// Launch with the programmatic-serialisation attribute (the kernel may start while the previous kernel of the
+// stream drains; it waits at pdl_wait() before touching global memory) and, when cluster > 1, as thread-block
+// clusters of that many CTAs.
+template <typename K>
+cudaError_t launch_pdl(K kernel, int grid, int threads, int smem, int cluster, cudaStream_t stream, const FfaStepParams& P)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster, attr[n].val.clusterDim.y = 1, attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr, cfg.numAttrs = (unsigned)n;
+    return cudaLaunchKernelEx(&cfg, kernel, P);
+}
+
 int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int threads, int smem, cudaStream_t stream)
 {
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
         if (P.cluster > 1) {   // the CTAs that share a (batch, head) as one thread-block cluster
-            cudaLaunchConfig_t cfg;
-            memset(&cfg, 0, sizeof(cfg));
-            cfg.gridDim = dim3((unsigned)P.grid, 1, 1);
-            cfg.blockDim = dim3((unsigned)threads, 1, 1);
-            cfg.dynamicSmemBytes = (size_t)smem;
-            cfg.stream = stream;
-            cudaLaunchAttribute attr;
-            attr.id = cudaLaunchAttributeClusterDimension;
-            attr.val.clusterDim.x = (unsigned)P.cluster, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
-            cfg.attrs = &attr, cfg.numAttrs = 1;
-            if (cudaLaunchKernelEx(&cfg, ffa_stream_kernel<T, DH>, P) == cudaSuccess) return 0;
+            if (launch_pdl(ffa_stream_kernel<T, DH>, P.grid, threads, smem, P.cluster, stream, P) == cudaSuccess) return 0;
             // a cluster shape this device cannot co-schedule: the same cut runs without clusters,
             // the parts merging through global memory
             (void)cudaGetLastError();
         }
         FfaStepParams Q = P;
         Q.cluster = 0;
-        ffa_stream_kernel<T, DH><<<Q.grid, threads, smem, stream>>>(Q);
-        return (int)cudaGetLastError();
+        return (int)launch_pdl(ffa_stream_kernel<T, DH>, Q.grid, threads, smem, 0, stream, Q);
     });
 }
 
@@ -239,20 +254,8 @@ int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, in
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
-        cfg.gridDim = dim3((unsigned)P.grid, 1, 1);
-        cfg.blockDim = dim3(kFusedThreads, 1, 1);
-        cfg.dynamicSmemBytes = (size_t)smem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)P.cluster;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        return (int)cudaLaunchKernelEx(&cfg, ffa_prune_cluster_kernel<T, DH>, P);
+        // cluster = 1 is a plain launch: the kernel's cluster barriers and shared-memory mappings degenerate to the CTA's own
+        return (int)launch_pdl(ffa_prune_cluster_kernel<T, DH>, P.grid, kFusedThreads, smem, P.cluster, stream, P);
     });
 }
 
@@ -262,7 +265,6 @@ int ffa_k_decode_prune_stream(int dtype, int head_dim, const FfaStepParams& P, i
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
         if (scorer_warps < 1 || scorer_warps > ps_max_scorer_warps(DH)) return (int)cudaErrorInvalidConfiguration;
-        ffa_prune_stream_kernel<T, DH><<<P.grid, ffa_k_prune_stream_threads(scorer_warps), smem, stream>>>(P);
-        return (int)cudaGetLastError();
+        return (int)launch_pdl(ffa_prune_stream_kernel<T, DH>, P.grid, ffa_k_prune_stream_threads(scorer_warps), smem, 0, stream, P);
     });
 }

@@ -120,6 +120,13 @@ __device__ __forceinline__ void cp_async_16_hint(uint32_t dst, const void* src, 
 {
     asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(pol) : "memory");
 }
+// Programmatic dependent launch.  pdl_release(): the next kernel in the stream (if it was launched with the
+// programmatic-serialisation attribute) may start its CTAs as soon as every CTA of this grid has got this far;
+// pdl_wait(): blocks until every grid this one depends on has completed and its memory is visible.  A kernel
+// does only what needs no global memory (barrier and shared-memory set-up) before pdl_wait(), so its launch
+// latency and prologue overlap the previous kernel's last tiles.  Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

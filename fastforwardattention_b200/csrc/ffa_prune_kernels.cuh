@@ -45,6 +45,17 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S), ring = smem_u32(smem);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_release();
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, NCW);
+        }
+        flags[0] = 0, flags[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();   // nothing above touches global memory (the per-sample lengths below are)
     const uint32_t rank = cluster_rank();
     const int bh = blockIdx.x / C;
     const SampleRange sr = sample_range(P, bh / P.H);
@@ -55,15 +66,6 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     const int nrows = max(hi - lo, 0), ntiles = (nrows + R - 1) / R;
     const bool prune = P.p > 0.f;
 
-    if (tid == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, NCW);
-        }
-        flags[0] = 0, flags[1] = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
 
     const int ctid = tid - 32, g = ctid / LPR, li = ctid % LPR;   // meaningful for compute warps only
     float2 q2[VPL][E2];

@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
     const uint32_t ring = smem_u32(smem);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_release();
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(bar_full + 8 * s, 1);
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();   // nothing above touches global memory
 
     const int upb = P.units_per_bh;
     const Partition cut = make_partition(P);

@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
     const uint32_t ring = smem_u32(smem);
 
+    pdl_release();
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(bar_full + 8 * s, 1);
@@ -79,6 +80,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
     if (cl)
         for (int i = threadIdx.x; i < DH + 2; i += blockDim.x) clp[i] = i == DH ? -CUDART_INF_F : 0.f;   // "nothing seen"
     __syncthreads();
+    pdl_wait();   // nothing above touches global memory; everything below may read what the previous kernel wrote
 
     const int upb = P.units_per_bh;
     const Partition cut = make_partition(P);

@@ -56,6 +56,9 @@ CONFIGS = {
     "prune-fp16-b10-p1e-3": Workload("prune-fp16-b10-p1e-3", torch.float16, 10, 32, 64, 1000, 256, p=1e-3,
                                      seed=1238, peaked=True),
     **{f"long-{x}": long_sweep(x) for x in (512, 2048, 8192, 32768)},
+    # the long-sequence shapes with peaked keys and a threshold: what pruning is for at lengths the reference cannot reach
+    **{f"prune-long-{x}": replace(long_sweep(x), name=f"prune-long-bf16-b32-h32-d128-L{x}", p=1e-3, seed=1240, peaked=True)
+       for x in (8192, 32768)},
 }
 
 
