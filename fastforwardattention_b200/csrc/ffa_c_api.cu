@@ -38,7 +38,7 @@ int elem_size(int dtype) { return dtype == FFA_DTYPE_F32 ? 4 : 2; }
 bool dtype_ok(int dtype) { return dtype == FFA_DTYPE_F32 || dtype == FFA_DTYPE_F16 || dtype == FFA_DTYPE_BF16; }
 bool head_dim_ok(int d) { return d == 64 || d == 80 || d == 128 || d == 256; }
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
-int score_stride(int max_len) { return (max_len + 7) / 8 * 8; }   // score rows start on 32-byte boundaries
+int score_stride(int max_len) { return (max_len + 31) / 32 * 32; }   // a pair's scores are whole 128-byte lines (32 rows each)
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kMaxCtasPerSm = 8;
@@ -49,7 +49,6 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 // bf16 x 128, batch 32 x 32 heads: 2 K tokens 154.9 vs 159.3 us, 1 K 81.8 vs 88.3 us, 512 45.6 vs
 // 48.9 us in favour of the aligned cut; 8 K tokens 603 vs 594 us against it)
 constexpr long long kAlignedBelowUnitsPerSlot = 200;
-constexpr long long kMinBytesPerCta = 256 * 1024;   // whole-pair CTAs stream at least this much (several pairs each if need be)
 // pruned steps that stream at least this many bytes of K take the streaming kernel when the score scratch is bound
 // (bf16 x 128, 1024 pairs, 5 % of the V rows kept: 2 K tokens 119 vs 112 us for the cluster kernel, 3 K 162 vs 167 us,
 // 4 K 202 vs 223 us, 8 K 378 vs 428 us, 32 K 1492 vs 1830 us)
@@ -233,7 +232,6 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
     const long long units = BH * upb;
     long long grid = (long long)p->sms * s.cps;
     int parts = upb;
-    bool whole_pairs_grid = false;
     if (!grid_forced && units < kAlignedBelowUnitsPerSlot * grid) {
         if (BH <= grid) {
             long long c = grid / BH;
@@ -254,23 +252,18 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
             if (need <= 4 && (long long)need * (smem + kSmemReservePerCta) <= p->smem_per_sm && !(p->forced && p->force.ctas_per_sm > 0)) {
                 s.cps = need, parts = 1, grid = BH;
             } else {
-                // more pairs than slots: k whole pairs per CTA, nothing straddles -- and MORE CTAs than slots: the
-                // hardware hands the next CTA to whichever SM frees a slot first, which evens out what a static
-                // cut of whole pairs cannot (1024 pairs over 592 slots leave some SMs 8 pairs and others 6;
-                // over 296 slots a cut of 4 pairs per CTA uses 256 of them).  k keeps a CTA's stream at
-                // kMinBytesPerCta or more, so that its start-up is a small part of its life.
-                const long long pair_bytes = (long long)cap_rows * rowb * tensors;
-                long long k = pair_bytes > 0 ? (kMinBytesPerCta + pair_bytes - 1) / pair_bytes : BH;
-                if (k < 1) k = 1;
+                // more pairs than slots: k whole pairs per persistent CTA, nothing straddles; its copy warp streams across
+                // pair boundaries without a bubble.  (One CTA per pair with more CTAs than slots, handed out by the
+                // hardware as slots free up, balances better but pays a CTA's start-up per pair: 1024 pairs of 256 KB
+                // 48.0 vs 43.5 us, of 1 MB 161.7 vs 161.0 us.)
+                const long long k = (BH + grid - 1) / grid;
                 parts = 1, grid = (BH + k - 1) / k;
-                whole_pairs_grid = true;
             }
         }
     }
     if (grid > units) grid = units;
     if (grid_forced && p->force.grid < grid) grid = p->force.grid;
-    // split pairs leave one partial per CTA in the workspace, which is sized for max_grid CTAs; CTAs of whole pairs leave none
-    if (grid > p->max_grid && !whole_pairs_grid) grid = p->max_grid;
+    if (grid > p->max_grid) grid = p->max_grid;
     out->parts_per_bh = parts;
     out->tile_rows = s.tile_rows;
     out->stages = s.stages;

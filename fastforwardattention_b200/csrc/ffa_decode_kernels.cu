@@ -188,11 +188,17 @@ int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long 
     return (int)cudaGetLastError();
 }
 
-// Launch with the programmatic-serialisation attribute (the kernel may start while the previous kernel of the
-// stream drains; it waits at pdl_wait() before touching global memory) and, when cluster > 1, as thread-block
-// clusters of that many CTAs.
+// Steps that stream less than this get the programmatic-serialisation attribute: their launch latency and prologue
+// are a visible share of the step (bf16 x 128, 1024 pairs: 512 tokens 44.0 vs 44.9 us, fp32 x 64 batch 1: 8.8 vs
+// 9.2 us with it); above, an early start of the next grid's CTAs costs more than it hides (2 K tokens 161.8 vs 156.0 us,
+// 8 K 605.8 vs 593.6 us)
+constexpr double kPdlBelowBytes = 512e6;
+
+// Launch -- when `overlap`, with the programmatic-serialisation attribute: the kernel may start while the previous
+// kernel of the stream drains and waits at pdl_wait() before touching global memory -- and, when cluster > 1, as
+// thread-block clusters of that many CTAs.
 template <typename K>
-cudaError_t launch_pdl(K kernel, int grid, int threads, int smem, int cluster, cudaStream_t stream, const FfaStepParams& P)
+cudaError_t launch_pdl(K kernel, int grid, int threads, int smem, int cluster, bool overlap, cudaStream_t stream, const FfaStepParams& P)
 {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -202,9 +208,11 @@ cudaError_t launch_pdl(K kernel, int grid, int threads, int smem, int cluster, c
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[n].val.programmaticStreamSerializationAllowed = 1;
-    ++n;
+    if (overlap) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     if (cluster > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
         attr[n].val.clusterDim.x = (unsigned)cluster, attr[n].val.clusterDim.y = 1, attr[n].val.clusterDim.z = 1;
@@ -219,15 +227,17 @@ int ffa_k_decode_onepass(int dtype, int head_dim, const FfaStepParams& P, int th
     return dispatch(dtype, head_dim, [&](auto t, auto dh) -> int {
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
+        // rows the step streams: at most t of every pair (per-sample lengths: t is their bound)
+        const bool overlap = 2.0 * P.B * P.H * P.t * DH * sizeof(T) < kPdlBelowBytes;
         if (P.cluster > 1) {   // the CTAs that share a (batch, head) as one thread-block cluster
-            if (launch_pdl(ffa_stream_kernel<T, DH>, P.grid, threads, smem, P.cluster, stream, P) == cudaSuccess) return 0;
+            if (launch_pdl(ffa_stream_kernel<T, DH>, P.grid, threads, smem, P.cluster, overlap, stream, P) == cudaSuccess) return 0;
             // a cluster shape this device cannot co-schedule: the same cut runs without clusters,
             // the parts merging through global memory
             (void)cudaGetLastError();
         }
         FfaStepParams Q = P;
         Q.cluster = 0;
-        return (int)launch_pdl(ffa_stream_kernel<T, DH>, Q.grid, threads, smem, 0, stream, Q);
+        return (int)launch_pdl(ffa_stream_kernel<T, DH>, Q.grid, threads, smem, 0, overlap, stream, Q);
     });
 }
 
@@ -255,7 +265,8 @@ int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, in
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
         // cluster = 1 is a plain launch: the kernel's cluster barriers and shared-memory mappings degenerate to the CTA's own
-        return (int)launch_pdl(ffa_prune_cluster_kernel<T, DH>, P.grid, kFusedThreads, smem, P.cluster, stream, P);
+        const bool overlap = 1.0 * P.B * P.H * P.t * DH * sizeof(T) < kPdlBelowBytes;
+        return (int)launch_pdl(ffa_prune_cluster_kernel<T, DH>, P.grid, kFusedThreads, smem, P.cluster, overlap, stream, P);
     });
 }
 
@@ -265,6 +276,7 @@ int ffa_k_decode_prune_stream(int dtype, int head_dim, const FfaStepParams& P, i
         using T = decltype(t);
         constexpr int DH = decltype(dh)::value;
         if (scorer_warps < 1 || scorer_warps > ps_max_scorer_warps(DH)) return (int)cudaErrorInvalidConfiguration;
-        return (int)launch_pdl(ffa_prune_stream_kernel<T, DH>, P.grid, ffa_k_prune_stream_threads(scorer_warps), smem, 0, stream, P);
+        const bool overlap = 1.0 * P.B * P.H * P.t * DH * sizeof(T) < kPdlBelowBytes;
+        return (int)launch_pdl(ffa_prune_stream_kernel<T, DH>, P.grid, ffa_k_prune_stream_threads(scorer_warps), smem, 0, overlap, stream, P);
     });
 }

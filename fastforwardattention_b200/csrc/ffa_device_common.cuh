@@ -127,6 +127,9 @@ __device__ __forceinline__ void cp_async_16_hint(uint32_t dst, const void* src, 
 // latency and prologue overlap the previous kernel's last tiles.  Both are no-ops in a plain launch.
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The 128-byte line at `p` (128-byte aligned) will not be read again before it is rewritten: L2 may drop it
+// without writing it back to HBM
+__device__ __forceinline__ void l2_discard_line(const void* p) { asm volatile("discard.global.L2 [%0], 128;" ::"l"(p) : "memory"); }
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

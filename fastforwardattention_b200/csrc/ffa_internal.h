@@ -24,8 +24,8 @@ struct FfaStepParams {
     float* partials;   // [(grid + B*H)] x (Dh + 2): weighted sum, running max, running sum
     int* tickets;      // [B*H] arrival counters, zero between launches
     int* status;       // device status word
-    float* scores;     // [B*H, score_stride] fp32 scores (streaming pruning kernel); rows start 32-byte aligned
-    int score_stride;  // Lmax rounded up to a multiple of 8
+    float* scores;     // [B*H, score_stride] fp32 scores (streaming pruning kernel); a pair's scores are whole 128-byte lines
+    int score_stride;  // Lmax rounded up to a multiple of 32
     uint32_t* kept_mask;  // [B*H, mask_words] or null
     int mask_words;
     // thread-block cluster size: CTAs per (batch, head) (fused pruning kernel; streaming kernel when

@@ -397,6 +397,9 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                     }
                     n += __popc(bal);
                 }
+                // This round's score lines (one per 32-row word; every lane has used its values by now) are not needed
+                // again: spare HBM their write-back.  The word of the new token's row is read once more and left alone.
+                if (lane < kPsWordsPerRound && w0 + lane < nwords - 1) l2_discard_line(sc_row + (size_t)(w0 + lane) * 32);
                 // the next round's scores travel while this round's V rows are fetched
                 if (w0 + NGW * kPsWordsPerRound < nwords) load_scores(w0 + NGW * kPsWordsPerRound, s);
                 __syncwarp();

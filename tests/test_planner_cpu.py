@@ -36,12 +36,8 @@ def test_every_shape_fits_and_covers_the_work(dtype, Dh):
             assert 2 <= l.stages <= 16 and 1 <= l.consumer_warps <= 8
             assert l.smem_bytes <= SMEM_CTA and l.ctas_per_sm * (l.smem_bytes + 1024) <= SMEM_SM
             units = B * H * (t // l.tile_rows + 1)
-            assert 1 <= l.grid <= units                          # no CTA without a unit
-            # a grid is one wave of resident CTAs, unless every CTA owns whole (batch, head) pairs: then there may be
-            # more CTAs than slots, and the hardware hands them out as slots free up
-            whole_pairs = l.parts_per_bh == 1 and l.grid <= B * H
-            assert l.grid <= SMS * l.ctas_per_sm or whole_pairs
-            assert l.grid <= SMS * 8 or whole_pairs              # split pairs: one partial per CTA in the workspace
+            assert 1 <= l.grid <= min(units, SMS * 8)            # no CTA without a unit
+            assert l.grid <= SMS * l.ctas_per_sm
             upb = t // l.tile_rows + 1
             assert 1 <= l.parts_per_bh <= upb and l.grid <= B * H * l.parts_per_bh   # every CTA owns whole parts
             # the ring really holds stages x (K tile + V tile)

@@ -207,6 +207,34 @@ def test_graphed_step_in_a_mostly_empty_cache_crosses_row_buckets():
     assert torch.equal(kc[:, :, Lp + n - 1].cpu(), k[:, :, 0])
 
 
+def test_graphed_host_step_upload_graph_download():
+    """The host-driven step as one upload plus one graph replay: q/k/v come from pinned host memory, the
+    result lands in pinned host memory; a new generation over the same caches starts with reset_row()."""
+    from fastforwardattention_b200 import FastForwardAttn, GraphedHostStep
+
+    dt = torch.float16
+    g = torch.Generator().manual_seed(14)
+    B, H, Dh, Lp, n = 2, 4, 64, 200, 4
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    ffa = FastForwardAttn(K.cuda(), V.cuda(), Lp + n, False)
+    step = GraphedHostStep(ffa, Dh ** -0.5, first_row=Lp)
+    for generation in range(2):
+        orc = O.DecodeOracle(K, V, Lp + n, compute_dtype=torch.float64)
+        if generation:
+            step.reset_row(Lp)
+        for i in range(n):
+            qkv_host = torch.randn(3, B, H, 1, Dh, generator=g).to(dt).pin_memory()
+            out = step(qkv_host)
+            torch.cuda.current_stream().synchronize()
+            assert out.is_pinned() and out.shape == (B, H, Dh)
+            ref = orc.step(qkv_host[0], qkv_host[1], qkv_host[2], Dh ** -0.5, Lp + i)
+            assert (out.double() - ref).abs().max().item() <= 1e-3, (generation, i)
+    with pytest.raises(RuntimeError, match="full"):
+        step(qkv_host)
+    assert ffa.device_status() == 0
+
+
 def test_graphed_layers_whole_token_in_one_graph():
     """A toy decoder (three layers, fp32 projections between the attention calls) replayed from
     one CUDA graph gives what the same layers give when called one by one."""

@@ -152,3 +152,56 @@ def test_two_ranks_step_and_gather_replayed_from_one_graph_per_rank():
         assert p.exitcode == 0
     assert sorted(r for r, _ in res) == [0, 1]
     assert all(w <= 1.0 for _, w in res), res
+
+
+def _host_step_worker(rank, world, port, q_out):
+    """ShardedFastForwardAttn.graphed_step(): upload of the rank's q/k/v slice from pinned host memory, then one graph
+    with the attention launch, the peer-memory gather and the download of the full [B, H, Dh] result."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from fastforwardattention_b200.sharded import ShardedFastForwardAttn, shard_heads
+        from oracle.ffa_oracle import DecodeOracle
+
+        dt, tol = torch.float16, 2e-3
+        g = torch.Generator().manual_seed(8)
+        B, H, Dh, Lp, steps = 2, 8, 64, 260, 5
+        K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+        V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+        full = DecodeOracle(K, V, Lp + steps, compute_dtype=torch.float64)
+        sh = ShardedFastForwardAttn(shard_heads(K, rank, world, H).to(dev), shard_heads(V, rank, world, H).to(dev),
+                                    Lp + steps, False)
+        assert sh.enable_peer_gather()
+        step = sh.graphed_step(Dh ** -0.5, first_row=Lp)
+        worst = 0.0
+        for i in range(steps):
+            qkv = torch.randn(3, B, H, 1, Dh, generator=g).to(dt)
+            mine = torch.stack([shard_heads(qkv[j], rank, world, H) for j in range(3)]).pin_memory()
+            out = step(mine)
+            torch.cuda.current_stream(dev).synchronize()
+            assert out.shape == (B, H, Dh)
+            want = full.step(qkv[0], qkv[1], qkv[2], Dh ** -0.5, Lp + i)
+            worst = max(worst, (out.double() - want).abs().max().item() / tol)
+        assert sh.engine.device_status() == 0
+        sh.close()
+        q_out.put((rank, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_graphed_host_step():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_host_step_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert sorted(r for r, _ in res) == [0, 1]
+    assert all(w <= 1.0 for _, w in res), res
