@@ -18,7 +18,7 @@ SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_des
            "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_static_scratch_status", "ffa_static_scratch_selftest_wait_timeout", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
            "ffa_plan_get_prune_launch", "ffa_cache_copy", "ffa_attention_paged", "ffa_peer_gather_bytes",
            "ffa_peer_mem_alloc", "ffa_peer_mem_open", "ffa_peer_mem_close", "ffa_peer_mem_free", "ffa_peer_gather_attach",
-           "ffa_peer_gather", "ffa_plan_set_cluster_merge"]
+           "ffa_peer_gather", "ffa_plan_set_cluster_merge", "ffa_peer_push_target"]
 
 
 class Launch(C.Structure):
@@ -73,6 +73,7 @@ def lib() -> C.CDLL:
         L.ffa_peer_mem_free.argtypes = [vp]
         L.ffa_peer_gather_attach.argtypes = [vp, i, i, C.POINTER(vp), sz]
         L.ffa_peer_gather.argtypes = [vp, vp, vp, i, C.c_uint, vp]
+        L.ffa_peer_push_target.argtypes = [vp, vp]
         L.ffa_launch_count.restype = C.c_ulonglong
         L.ffa_last_error.restype = C.c_char_p
         _lib = L

@@ -78,6 +78,7 @@ struct ffa_plan {
     // output gather over peer memory
     int peer_world, peer_rank;
     void* peer_buf[FFA_MAX_PEERS];
+    void* push_gathered;   // non-null: exact steps push their output rows to the peers (ffa_peer_push_target)
 };
 
 namespace {
@@ -548,6 +549,12 @@ int ffa_workspace_bind(ffa_plan_t* plan, void* workspace, size_t bytes, void* st
 
 namespace {
 
+// a half of a rank's staging buffer for the output gather: [B][world][H * Dh] elements
+size_t peer_half_bytes(const ffa_plan* p, int world)
+{
+    return align_up((size_t)p->B * world * p->H * p->Dh * elem_size(p->dtype), 256);
+}
+
 struct PageArgs {
     const int* table = nullptr;
     int max_pages = 0, page_rows = 0;
@@ -614,6 +621,12 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     P.units_per_bh = cap / L.tile_rows + 1;
     P.parts_per_bh = L.parts_per_bh;
     if (!twopass) {
+        if (plan->push_gathered != nullptr && plan->peer_world > 1 && !paged) {
+            // the kernel's epilogue is the push phase of the output all-gather
+            for (int r = 0; r < plan->peer_world; ++r) P.push_peer[r] = plan->peer_buf[r];
+            P.push_gathered = plan->push_gathered, P.push_half_bytes = peer_half_bytes(plan, plan->peer_world);
+            P.push_world = plan->peer_world, P.push_rank = plan->peer_rank;
+        }
         // the C CTAs of a pair merge inside a thread-block cluster when every CTA owns exactly one part
         // (pairs with more than 8 parts: whole clusters of 8, the cluster leaders merge through global memory)
         r = fit_clusters(plan, cap, paged, &L, &P.cluster);
@@ -686,10 +699,6 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status)
 // Staging buffer of every rank: half 0 | half 1 | flags[FFA_MAX_PEERS], step counter, ticket (256 bytes);
 // a half is [B][world][H * Dh] elements.
 
-static size_t peer_half_bytes(const ffa_plan* p, int world)
-{
-    return align_up((size_t)p->B * world * p->H * p->Dh * elem_size(p->dtype), 256);
-}
 
 size_t ffa_peer_gather_bytes(const ffa_plan_t* plan, int world)
 {
@@ -744,7 +753,7 @@ int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* b
 {
     if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
     if (world == 0) {   // detach
-        plan->peer_world = 0;
+        plan->peer_world = 0, plan->push_gathered = nullptr;
         return FFA_OK;
     }
     if (buffers == nullptr) return fail(FFA_ERR_ARG, "null buffer list");
@@ -758,6 +767,15 @@ int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* b
     }
     for (int r = 0; r < world; ++r) plan->peer_buf[r] = buffers[r];
     plan->peer_world = world, plan->peer_rank = rank;
+    return FFA_OK;
+}
+
+int ffa_peer_push_target(ffa_plan_t* plan, void* gathered)
+{
+    if (plan == nullptr) return fail(FFA_ERR_ARG, "null plan");
+    if (gathered != nullptr && plan->peer_world < 1) return fail(FFA_ERR_ARG, "no peer buffers attached (ffa_peer_gather_attach)");
+    if (gathered != nullptr && !aligned16(gathered)) return fail(FFA_ERR_ARG, "gathered must be a 16-byte aligned pointer");
+    plan->push_gathered = gathered;
     return FFA_OK;
 }
 

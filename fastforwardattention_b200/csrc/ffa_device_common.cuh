@@ -373,6 +373,48 @@ __device__ __forceinline__ float transposed_group_sum(const float (&v)[RB], int 
     return c;
 }
 
+// ------------------------------------------------------------------------------------------
+// Output push over peer memory (see FfaStepParams::push_*)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t* push_tail(const FfaStepParams& P, int rank)
+{
+    return reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(P.push_peer[rank]) + 2 * P.push_half_bytes);
+}
+// the step this launch pushes: one past the counter in this rank's own buffer (nobody advances it before every pair is out)
+__device__ __forceinline__ uint32_t push_step(const FfaStepParams& P)
+{
+    return *reinterpret_cast<volatile uint32_t*>(push_tail(P, P.push_rank) + kPeerTailCounter) + 1u;
+}
+// element d of out[bh, :] -> this rank's slot in the own result and in every peer's staging half of step `seq`.
+// Consecutive threads hold consecutive d, so a warp's stores to one peer are one contiguous run.
+template <typename T, int DH>
+__device__ __forceinline__ void push_store(const FfaStepParams& P, uint32_t seq, int bh, int d, T v)
+{
+    const int b = bh / P.H, h = bh - b * P.H;
+    const size_t at = ((size_t)(b * P.push_world + P.push_rank) * P.H + h) * DH + d;
+    static_cast<T*>(P.push_gathered)[at] = v;
+    const size_t half = (size_t)(seq & 1u) * P.push_half_bytes;
+    for (int r = 0; r < P.push_world; ++r)
+        if (r != P.push_rank) reinterpret_cast<T*>(static_cast<unsigned char*>(P.push_peer[r]) + half)[at] = v;
+}
+// One thread per finished pair, after every thread that pushed the pair has fenced (system scope) and met at a barrier:
+// counts the pair; the one that counts the step's last pair raises this rank's flag at every peer and advances the step.
+__device__ __forceinline__ void push_pair_done(const FfaStepParams& P, uint32_t seq)
+{
+    uint32_t* own = push_tail(P, P.push_rank);
+    if (atomicAdd(own + kPeerTailPairsDone, 1u) == (uint32_t)(P.B * P.H) - 1u) {
+        own[kPeerTailPairsDone] = 0;
+        __threadfence_system();   // every CTA's rows (fenced before its count) are at the peers before the flags
+        for (int r = 0; r < P.push_world; ++r)
+            if (r != P.push_rank) st_release_sys(push_tail(P, r) + kPeerTailFlags + P.push_rank, seq);
+        *reinterpret_cast<volatile uint32_t*>(own + kPeerTailCounter) = seq;
+    }
+}
+
 template <int LPR>
 __device__ __forceinline__ float group_sum(float x)
 {

@@ -35,7 +35,19 @@ struct FfaStepParams {
     // page_table [B, max_pages] names the page of every page_rows rows of a sequence; null = contiguous
     const int* page_table;
     int max_pages, page_rows;
+    // Output push over peer memory (heads sharded over the GPUs of a node; exact kernel only): the CTA that writes
+    // out[b, h, :] also stores the row into this rank's slot of every peer's staging half and of the own gathered
+    // result, and the CTA that finishes the step's last pair raises the arrival flags.  push_world <= 1: off.
+    void* push_peer[8];     // every rank's staging buffer (layout: see FfaPeerGatherParams)
+    void* push_gathered;    // [B][push_world * H][Dh]: this rank's own result tensor
+    size_t push_half_bytes;
+    int push_world, push_rank;
 };
+
+// 32-bit words of the 256-byte tail of a staging buffer: arrival flags (one per peer), the step counter, the ticket that
+// advances it, one ticket per peer that elects the CTA raising that peer's flag, and the count of (batch, head)
+// pairs whose output the attention kernel has pushed in the current step
+enum { kPeerTailFlags = 0, kPeerTailCounter = 16, kPeerTailTicket = 17, kPeerTailPushTickets = 24, kPeerTailPairsDone = 32 };
 
 // One all-gather of the step outputs over peer memory.  Every rank owns a staging buffer: two
 // halves [B][world * row_bytes] (used alternately), then flags[8], the step counter, a ticket.

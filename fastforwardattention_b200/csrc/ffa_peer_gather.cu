@@ -27,10 +27,6 @@ using namespace ffa_dev;
 
 namespace {
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
 {
     uint32_t v;
@@ -42,9 +38,8 @@ constexpr int kGatherPushThreads = 256;
 constexpr int kVecPerThread = 4;      // 16-byte vectors a thread moves per phase, all loads before the first store
 constexpr int kMaxSlices = 16;        // CTAs per peer
 
-// tail of a staging buffer, in 32-bit words: arrival flags, step counter, the ticket that advances it,
-// one ticket per peer that elects the CTA raising that peer's flag
-constexpr int kTailFlags = 0, kTailCounter = 16, kTailTicket = 17, kTailPushTickets = 24;
+constexpr int kTailFlags = kPeerTailFlags, kTailCounter = kPeerTailCounter, kTailTicket = kPeerTailTicket,
+              kTailPushTickets = kPeerTailPushTickets;
 
 // Moves vectors [lo, hi) of a [B][row_bytes] slice: `from` and `to` map a vector index to its address.
 template <typename From, typename To>

@@ -5,10 +5,12 @@
 namespace ffa_dev {
 
 // Combines `count` partials (weighted sum [DH], running max, running sum; stride DH + 2 floats)
-// that other CTAs left in global memory, in slot order, and writes the normalised output.
-// Called by all `nthreads` threads of the CTA that arrived last.
+// that other CTAs left in global memory, in slot order, and writes the normalised output (and pushes it to the
+// peers when the heads are sharded, see FfaStepParams::push_*).  Called by all `nthreads` threads of the CTA that
+// arrived last.
 template <typename T, int DH, bool kPrecise>
-__device__ __forceinline__ void merge_partials(const float* pbase, int count, T* outp, int tid, int nthreads)
+__device__ __forceinline__ void merge_partials(const FfaStepParams& P, uint32_t push_seq, int bh, const float* pbase, int count,
+                                               T* outp, int tid, int nthreads)
 {
     auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
     float MM = -CUDART_INF_F;
@@ -22,7 +24,10 @@ __device__ __forceinline__ void merge_partials(const float* pbase, int count, T*
             A = fmaf(w, __ldcg(pk + d), A);
             L = fmaf(w, __ldcg(pk + DH + 1), L);
         }
-        Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+        T o;
+        Elem<T>::store(&o, L > 0.f ? A / L : 0.f);
+        outp[d] = o;
+        if (P.push_world > 1) push_store<T, DH>(P, push_seq, bh, d, o);
     }
 }
 
@@ -81,6 +86,8 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         for (int i = threadIdx.x; i < DH + 2; i += blockDim.x) clp[i] = i == DH ? -CUDART_INF_F : 0.f;   // "nothing seen"
     __syncthreads();
     pdl_wait();   // nothing above touches global memory; everything below may read what the previous kernel wrote
+    const bool push = P.push_world > 1;
+    const uint32_t push_seq = push ? push_step(P) : 0u;
 
     const int upb = P.units_per_bh;
     const Partition cut = make_partition(P);
@@ -342,6 +349,7 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             float M = -CUDART_INF_F;
             for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, red[gg * RS + DH]);
             const bool whole = (j0 == 0 && j1 == upb);
+            bool wrote_out = whole;   // this CTA wrote out[bh, :]: a whole pair, or the last arriver's merge
             const int slot = blockIdx.x + bh;
             float* part = P.partials + (size_t)slot * (DH + 2);
             T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
@@ -354,7 +362,10 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                     L = fmaf(w, red[gg * RS + DH + 1], L);
                 }
                 if (whole) {
-                    Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+                    T o;
+                    Elem<T>::store(&o, L > 0.f ? A / L : 0.f);
+                    outp[d] = o;
+                    if (push) push_store<T, DH>(P, push_seq, bh, d, o);
                 } else if (cl) {
                     clp[d] = A;
                     if (d == 0) clp[DH] = M, clp[DH + 1] = L;
@@ -376,11 +387,14 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 named_bar_sync(1, nct);
                 if (flags[1]) {
                     __threadfence();
-                    merge_partials<T, DH, kPrecise>(P.partials + (size_t)(c_first + bh) * (DH + 2), count, outp, ctid, nct);
+                    merge_partials<T, DH, kPrecise>(P, push_seq, bh, P.partials + (size_t)(c_first + bh) * (DH + 2), count, outp, ctid, nct);
                     if (ctid == 0) P.tickets[bh] = 0;  // ready for the next launch on this stream
+                    wrote_out = true;
                 }
             }
+            if (push && wrote_out) __threadfence_system();   // this thread's rows are at the peers before the pair is counted
             named_bar_sync(1, nct);  // `red` and the flag are reused by the next segment
+            if (push && wrote_out && ctid == 0) push_pair_done(P, push_seq);
             if (!sr.ok && ctid == 0) atomicOr(P.status, kStatusBadLength);
             u += j1 - j0;
         }
@@ -420,14 +434,19 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                     L = fmaf(w, lc[c], L);
                 }
                 if (K == 1) {
-                    Elem<T>::store(outp + d, L > 0.f ? A / L : 0.f);
+                    T o;
+                    Elem<T>::store(&o, L > 0.f ? A / L : 0.f);
+                    outp[d] = o;
+                    if (push) push_store<T, DH>(P, push_seq, bh, d, o);
                 } else {
                     part[d] = A;
                     if (d == 0) part[DH] = MM, part[DH + 1] = L;
                 }
             }
         }
+        if (push && leader && K == 1) __threadfence_system();   // rows at the peers before the pair is counted
         cluster_sync_all();   // peers kept their shared memory alive until the leader had read it
+        if (push && leader && K == 1 && threadIdx.x == 0) push_pair_done(P, push_seq);
         if (leader && K > 1) {
             __threadfence();
             __syncthreads();
@@ -435,8 +454,13 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             __syncthreads();
             if (flags[1]) {
                 __threadfence();
-                merge_partials<T, DH, kPrecise>(P.partials + (size_t)bh * K * (DH + 2), K, outp, threadIdx.x, blockDim.x);
+                merge_partials<T, DH, kPrecise>(P, push_seq, bh, P.partials + (size_t)bh * K * (DH + 2), K, outp, threadIdx.x, blockDim.x);
                 if (threadIdx.x == 0) P.tickets[bh] = 0;
+                if (push) {
+                    __threadfence_system();
+                    __syncthreads();
+                    if (threadIdx.x == 0) push_pair_done(P, push_seq);
+                }
             }
         }
     }

@@ -115,6 +115,7 @@ struct FastForwardAttn {
         ffa_plan_destroy(plan);
         plan = np, k_cache = nk, v_cache = nv, Lmax = new_max_len;
         kept_mask = torch::Tensor();   // one bit per row of the old length; re-created on the next recorded call
+        push_tensor = torch::Tensor();
         bind_workspace(has_scores);
         stream.synchronize();
     }
@@ -139,9 +140,14 @@ struct FastForwardAttn {
     // memory the engine's kernels can address: its own device, or pinned (page-locked) host memory
     bool reachable(const torch::Tensor& x) const { return (x.is_cuda() && x.device() == device) || (x.is_cpu() && x.is_pinned()); }
 
+    // gather_into: when given (heads sharded, peer_gather_attach done), the step also completes the all-gather of the
+    // outputs and returns gather_into = [B, world*H, Dh].  Exact steps push their rows from the attention kernel's
+    // epilogue (ffa_peer_push_target) and only the wait-and-collect kernel follows; pruned and torch-rounding steps are
+    // followed by the whole gather kernel.
     torch::Tensor run(const torch::Tensor& q_, const torch::Tensor& k_, const torch::Tensor& v_, torch::Tensor& kc,
                       torch::Tensor& vc, double softmax_scale, int64_t t, const torch::Tensor* seq_lengths,
-                      bool right_or_no_padding, double p, c10::optional<torch::Tensor> out_opt)
+                      bool right_or_no_padding, double p, c10::optional<torch::Tensor> out_opt,
+                      c10::optional<torch::Tensor> gather_into = c10::nullopt)
     {
         const int64_t n = B * H * Dh;
         // q, k, v (and out) may also live in pinned host memory: the kernel then reads (writes) them
@@ -191,21 +197,57 @@ struct FastForwardAttn {
                                  (float)softmax_scale, (int)t, seq_lengths ? sl.data_ptr<int>() : nullptr, right_or_no_padding,
                                  (float)p, mask_ptr, at::cuda::getCurrentCUDAStream().stream());
         };
+        bool pushed = false;
+        if (gather_into.has_value()) {
+            TORCH_CHECK(peer_world > 0, "FastForwardAttn: gather_into needs peer_gather_attach first");
+            TORCH_CHECK(reachable(*gather_into) && dtype_code(*gather_into) == dtype && gather_into->is_contiguous() &&
+                            gather_into->numel() == (int64_t)peer_world * n,
+                        "FastForwardAttn: gather_into must be a contiguous [batch, world*heads, head_dim] tensor of the cache's dtype on the "
+                        "engine's device (or in pinned host memory)");
+            if (peer_world > 1 && !(p > 0.0) && mode == FFA_MODE_EXACT && !push_tensor.defined()) {
+                check(ffa_peer_push_target(plan, gather_into->data_ptr()), "push target");
+                pushed = true;
+            }
+        }
         int rc = call();
         if (rc == FFA_ERR_WORKSPACE && !has_scores) {
             // a shape the fused pruning kernel cannot hold: grow the workspace by the score scratch, once
             bind_workspace(true);
             rc = call();
         }
+        if (pushed) ffa_peer_push_target(plan, nullptr);
         check(rc, "attention");
+        if (gather_into.has_value()) {
+            check(ffa_peer_gather(plan, out.data_ptr(), gather_into->data_ptr(), pushed ? 2 : 3, 2000,
+                                  at::cuda::getCurrentCUDAStream().stream()),
+                  "peer gather");
+            return *gather_into;
+        }
         return out;
+    }
+
+    // Low-level switch of the fused push (the gather_into keyword does this per call): while set, every exact step pushes
+    // its rows into `gathered` and the peers' staging buffers; the caller then issues peer_gather(..., phases=2).
+    void set_push_target(c10::optional<torch::Tensor> gathered)
+    {
+        if (!gathered.has_value()) {
+            check(ffa_peer_push_target(plan, nullptr), "push target");
+            push_tensor = torch::Tensor();
+            return;
+        }
+        TORCH_CHECK(peer_world > 0, "FastForwardAttn: peer_gather_attach first");
+        TORCH_CHECK(reachable(*gathered) && dtype_code(*gathered) == dtype && gathered->is_contiguous() &&
+                        gathered->numel() == (int64_t)peer_world * B * H * Dh,
+                    "FastForwardAttn: the push target must be a contiguous [batch, world*heads, head_dim] tensor of the cache's dtype");
+        check(ffa_peer_push_target(plan, gathered->data_ptr()), "push target");
+        push_tensor = *gathered;
     }
 
     // torch_ffa_api.cpp:189-192
     torch::Tensor attention(torch::Tensor q, torch::Tensor k, torch::Tensor v, double softmax_scale, int64_t curr_timestep,
-                            double prob_thresh, c10::optional<torch::Tensor> out)
+                            double prob_thresh, c10::optional<torch::Tensor> out, c10::optional<torch::Tensor> gather_into)
     {
-        return run(q, k, v, k_cache, v_cache, softmax_scale, curr_timestep, nullptr, true, prob_thresh, out);
+        return run(q, k, v, k_cache, v_cache, softmax_scale, curr_timestep, nullptr, true, prob_thresh, out, gather_into);
     }
     // torch_ffa_api.cpp:179-182
     torch::Tensor attention_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor kc, torch::Tensor vc,
@@ -226,10 +268,11 @@ struct FastForwardAttn {
     // laid out for rows 0..max_row.  -1 = nothing known = max_len - 1.
     torch::Tensor attention_per_sample(torch::Tensor q, torch::Tensor k, torch::Tensor v, double softmax_scale,
                                        torch::Tensor seq_lengths, double prob_thresh, c10::optional<torch::Tensor> out,
-                                       int64_t max_row)
+                                       int64_t max_row, c10::optional<torch::Tensor> gather_into)
     {
         TORCH_CHECK(max_row >= -1 && max_row < Lmax, "FastForwardAttn: max_row ", max_row, " outside [-1, ", Lmax, ")");
-        return run(q, k, v, k_cache, v_cache, softmax_scale, max_row < 0 ? Lmax - 1 : max_row, &seq_lengths, true, prob_thresh, out);
+        return run(q, k, v, k_cache, v_cache, softmax_scale, max_row < 0 ? Lmax - 1 : max_row, &seq_lengths, true, prob_thresh, out,
+                   gather_into);
     }
 
     std::pair<torch::Tensor, torch::Tensor> get_cache() { return std::make_pair(k_cache, v_cache); }
@@ -364,7 +407,7 @@ struct FastForwardAttn {
     }
 
     ffa_plan_t* plan = nullptr;
-    torch::Tensor k_cache, v_cache, workspace, kept_mask;
+    torch::Tensor k_cache, v_cache, workspace, kept_mask, push_tensor;
     c10::Device device{c10::kCUDA, 0};
     int64_t B = 0, H = 0, Dh = 0, Lmax = 0;
     int dtype = 0, mode = FFA_MODE_EXACT, prune_path = 0;
@@ -519,7 +562,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("get_cache", &FastForwardAttn::get_cache, "the live (k_cache, v_cache) tensors, [batch, heads, max_len, head_dim]")
         .def("attention", &FastForwardAttn::attention, "decode step on the engine's own caches", py::arg("q"), py::arg("k"),
              py::arg("v"), py::arg("softmax_scale"), py::arg("curr_timestep"), py::arg("prob_thresh") = 0.0,
-             py::arg("out") = py::none())
+             py::arg("out") = py::none(), py::arg("gather_into") = py::none())
         .def("attention", &FastForwardAttn::attention_cache, "decode step on caches passed back by the caller", py::arg("q"),
              py::arg("k"), py::arg("v"), py::arg("k_cache"), py::arg("v_cache"), py::arg("softmax_scale"),
              py::arg("curr_timestep"), py::arg("prob_thresh") = 0.0, py::arg("out") = py::none())
@@ -529,7 +572,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         .def("attention_per_sample", &FastForwardAttn::attention_per_sample,
              "decode step with per-sample cache lengths (right padding): sample b appends at row seq_lengths[b]", py::arg("q"),
              py::arg("k"), py::arg("v"), py::arg("softmax_scale"), py::arg("seq_lengths"), py::arg("prob_thresh") = 0.0,
-             py::arg("out") = py::none(), py::arg("max_row") = -1)
+             py::arg("out") = py::none(), py::arg("max_row") = -1, py::arg("gather_into") = py::none())
+        .def("set_push_target", &FastForwardAttn::set_push_target, py::arg("gathered") = py::none(),
+             "while set, exact steps push their output rows to the peers from the attention kernel (follow with peer_gather(phases=2))")
         .def("set_mode", &FastForwardAttn::set_mode, "'exact' (default) or 'round_like_torch'")
         .def("set_prune_path", &FastForwardAttn::set_prune_path, "0 choose, 1 cluster kernel, 2 streaming kernel")
         .def("set_cluster_merge", &FastForwardAttn::set_cluster_merge, "merge split pairs inside a thread-block cluster (default on)")

@@ -90,9 +90,9 @@ class GraphedHostStep:
             torch.cuda.current_stream().synchronize()    # out_host is valid from here until the next call
 
     One asynchronous upload of q/k/v into a static device buffer, then one replay of a graph that
-    holds the attention launch (row index in device memory), the increment of the row index, the
-    all-gather of the outputs over peer memory when the heads are sharded (`gather` = the
-    ShardedFastForwardAttn, after enable_peer_gather()), and the download of the result into
+    holds the attention launch (row index in device memory; when the heads are sharded -- `gather` =
+    the ShardedFastForwardAttn, after enable_peer_gather() -- its epilogue pushes the output rows to
+    the peers and a wait-and-collect kernel follows), the increment of the row index, and the download of the result into
     `out_host` ([B, H, Dh], or [B, world*H, Dh] when gathered).  Graphs are recorded per bucket
     of rows, like GraphedStep.
     """
@@ -132,10 +132,9 @@ class GraphedHostStep:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 self.ffa.attention_per_sample(self.stage[0], self.stage[1], self.stage[2], self.scale, self.rows, self.p,
-                                              out=self.local, max_row=bound)
+                                              out=self.local, max_row=bound,
+                                              gather_into=self.full if self.gather is not None else None)
                 self.rows.add_(1)
-                if self.gather is not None:
-                    self.ffa.peer_gather(self.local, out=self.full)
                 self.out_host.copy_(self.full, non_blocking=True)
             self.graphs[bound] = graph
         return graph

@@ -5,8 +5,9 @@ pair, attention.cu:1303), so rank r of N owns heads [r*H/N, (r+1)*H/N) for the w
 generation: its slice of the prompt K/V, its KV-cache shard, its slice of every q/k/v.  No
 cache row ever crosses NVLink.  The only collective is one all-gather of the [B, H/N, Dh]
 outputs, issued when the caller asks for the full [B, H, Dh] tensor: through the process
-group (NCCL), or -- after enable_peer_gather() -- by the engine's own kernel, which stores
-every rank's slice straight into the peers' memory and needs no permutation afterwards.
+group (NCCL), or -- after enable_peer_gather() -- by the engine's own kernels: the attention
+kernel stores every output row, as it produces it, straight into the peers' memory, and a
+short second kernel waits for the peers' rows and puts them in place (no permutation).
 
 One process per GPU (torchrun); the process group decides the backend (NCCL on GPUs).
 """
@@ -65,8 +66,16 @@ class ShardedFastForwardAttn:
                   prob_thresh: float = 0.0, gather: bool = False) -> torch.Tensor:
         """One decode step on this rank's heads; q/k/v hold B*(H/N)*Dh elements.  Returns the
         local [B, H/N, Dh] output, or the full [B, H, Dh] tensor when gather=True."""
+        if gather and self._peer:
+            # the attention kernel pushes its rows to the peers as it produces them; a short wait-and-collect kernel follows
+            return self.engine.attention(q_local, k_local, v_local, softmax_scale, curr_timestep, prob_thresh,
+                                         gather_into=self._full(q_local))
         out = self.engine.attention(q_local, k_local, v_local, softmax_scale, curr_timestep, prob_thresh)
         return self.gather(out) if gather else out
+
+    def _full(self, like: torch.Tensor) -> torch.Tensor:
+        kc = self.engine.get_cache()[0]   # q may live in pinned host memory; the result goes where the caches are
+        return torch.empty(self.B, self.H, self.Dh, dtype=kc.dtype, device=kc.device)
 
     def enable_peer_gather(self) -> bool:
         """Switch gather() to the engine's peer-memory all-gather.  Collective: every rank of the

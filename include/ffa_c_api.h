@@ -220,7 +220,7 @@ int ffa_device_status(ffa_plan_t* plan, void* stream, int* status);
  * waits -- for at most wait_limit_ms (1..2000), after which FFA_STATUS_WAIT_TIMEOUT is set in
  * the status word and the kernel returns -- until every peer's slice of the same step has
  * arrived, and writes gathered [batch, world*heads, head_dim] (this rank's own memory; rank r's
- * heads at [r*heads, (r+1)*heads)).  Every rank must make the same sequence of calls.  The
+ * heads at [r*heads, (r+1)*heads)).  out_local may be NULL when phases == 2.  Every rank must make the same sequence of calls.  The
  * step number lives in device memory and is advanced by the kernel, so all launch arguments
  * are the same for every step and the call may be recorded in a CUDA graph.
  * phases: 3 = both; 1 = store and signal only, 2 = wait and collect only (refers to the latest
@@ -241,6 +241,15 @@ int ffa_peer_mem_free(void* ptr);
 int ffa_peer_gather_attach(ffa_plan_t* plan, int world, int rank, void* const* buffers, size_t bytes_each);
 int ffa_peer_gather(ffa_plan_t* plan, const void* out_local, void* gathered, int phases, unsigned int wait_limit_ms,
                     void* stream);
+/* Folds the push phase into the attention kernel itself: while `gathered` (this rank's [batch, world*heads, head_dim]
+ * result, device memory or pinned host memory) is set, every EXACT step of ffa_attention (p == 0, exact mode, contiguous
+ * caches) stores each output row, from the CTA that computes it, into this rank's slot of every peer's staging buffer and
+ * of `gathered`, and the CTA that finishes the step's last (batch, head) pair raises the arrival flags -- one kernel does the
+ * attention and the sending half of the collective, and rows leave as they are produced.  Complete the step with
+ * ffa_peer_gather(plan, NULL, gathered, 2, ...) (wait and collect only).  Pruned and torch-rounding steps do not push: follow
+ * those with phases = 3 as before.  A push must always be followed by its wait before the next step (the two staging
+ * halves alternate on that assumption).  NULL switches the push off.  Plain 2..16-byte peer stores; no multicast. */
+int ffa_peer_push_target(ffa_plan_t* plan, void* gathered);
 
 /* Diagnostic, no counterpart in the reference: launches one warp that waits, for at most
  * limit_ms (1..2000), on a copy barrier nothing completes.  The wait must give up, the kernel

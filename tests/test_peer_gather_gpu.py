@@ -58,6 +58,48 @@ def test_every_rank_receives_every_slice(world, dt, Dh, H):
         e.peer_gather_free()
 
 
+@pytest.mark.parametrize("world,dt,B,H,Dh,Lp,cluster_merge",
+                         [(4, torch.float16, 40, 32, 64, 100, True),      # 320 pairs per rank: CTAs of whole pairs
+                          (2, torch.bfloat16, 3, 4, 128, 150, True),      # few pairs: a thread-block cluster per pair, its leader writes
+                          (2, torch.bfloat16, 3, 4, 128, 150, False),     # the same cut, merged through global memory by the last arriver
+                          (2, torch.float32, 1, 2, 64, 20000, True),      # one pair per rank over several clusters: the leaders' last arriver
+                          (8, torch.float16, 2, 8, 80, 300, True)])
+def test_attention_kernel_pushes_its_rows_and_a_short_kernel_collects(world, dt, B, H, Dh, Lp, cluster_merge):
+    """The fused form of the gather: the exact kernel's epilogue stores every output row into the peers' staging buffers
+    (and the own result) as it produces it and raises the flags after the step's last pair; only the wait-and-collect
+    kernel follows.  Pruned steps in between do not push and take the whole gather kernel."""
+    g = torch.Generator().manual_seed(50 + world)
+    steps, per = 4, H // world
+    K, V, engines = _ranks(world, dt, B, H, Dh, Lp, Lp + steps, g)
+    orc = O.DecodeOracle(K, V, Lp + steps, compute_dtype=torch.float64)
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dt]
+    full = [torch.zeros(B, H, Dh, dtype=dt, device="cuda") for _ in engines]
+    for e, f in zip(engines, full):
+        e.set_cluster_merge(cluster_merge)
+        e.set_push_target(f)
+    sl = lambda x, r: x[:, r * per:(r + 1) * per].contiguous().cuda()
+    for i in range(steps):
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        p = 1e-3 if i == 2 else 0.0
+        outs = [e.attention(sl(q, r), sl(k, r), sl(v, r), Dh ** -0.5, Lp + i, p) for r, e in enumerate(engines)]   # exact steps push here
+        if p > 0:
+            for e, o, f in zip(engines, outs, full):
+                e.peer_gather(o, phases=1, out=f)
+        got = [e.peer_gather(o, phases=2, out=f) for e, o, f in zip(engines, outs, full)]
+        want = torch.cat(outs, dim=1)
+        for r in range(world):
+            assert torch.equal(got[r], want), (i, r)
+        if p == 0:
+            ref = orc.step(q, k, v, Dh ** -0.5, Lp + i)
+            assert (got[0].cpu().double() - ref).abs().max().item() <= tol
+        else:
+            orc.append(k, v, Lp + i)
+    assert all(e.device_status() == 0 for e in engines)
+    for e in engines:
+        e.set_push_target(None)
+        e.peer_gather_free()
+
+
 def test_wait_for_a_silent_peer_runs_out_and_reports():
     """Rank 1 never pushes: rank 0's wait gives up after its limit, the time-out bit appears in
     the status word, the context stays usable, and the pair recovers on the next step."""

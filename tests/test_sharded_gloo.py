@@ -172,6 +172,13 @@ class PeerStandIn(OracleEngine):
         dist.all_gather(parts, out_local)
         return torch.cat(parts, dim=1)
 
+    def attention(self, q, k, v, scale, t, p=0.0, gather_into=None):
+        out = super().attention(q, k, v, scale, t, p)
+        if gather_into is None:
+            return out
+        gather_into.copy_(self.peer_gather(out))     # the extension pushes from the attention kernel, then collects
+        return gather_into
+
     def peer_gather_detach(self):
         self.log.append(("detach",))
 
