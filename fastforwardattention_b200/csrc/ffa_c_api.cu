@@ -152,6 +152,9 @@ Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int
         // pairs and short sequences let resident CTAs overlap those chains: <= 2 pairs per CTA
         const long long want = (BH + 2LL * p->sms - 1) / (2LL * p->sms);
         s.cps = (int)(want < 1 ? 1 : want > 4 ? 4 : want);
+        // a second CTA per SM where that is what lets a pair spread over one whole cluster of 8 (OPT-1.3B fp32 batch 1,
+        // 32 pairs on 148 SMs: 8 CTAs per pair 8.85 us, 4 per pair 9.2 us)
+        if (s.cps < 2 && 2LL * p->sms / BH >= 8 && 2LL * p->sms / BH < 16 && p->sms / BH < 8) s.cps = 2;
         if (tensors == 2) s.stages = 3;   // OPT-1.3B fp32 batch 1: 10.7 us vs 11.3 us
     } else if (bytes < 600e6) {
         if (row_bytes >= 512 && BH <= p->sms) {

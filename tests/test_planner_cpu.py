@@ -51,10 +51,10 @@ def test_benchmark_configurations_get_the_measured_shapes():
     l = launch(L, p, 32767)
     assert (l.tile_rows, l.stages, l.consumer_warps, l.ctas_per_sm, l.grid) == (64, 2, 4, 2, 296)
     assert l.parts_per_bh == 32767 // 64 + 1           # large problem: even cut of the unit list
-    # config 1 (16 MB per step): one CTA per SM, 4 CTAs per (batch, head), boundaries aligned
+    # config 1 (16 MB per step, 32 pairs): two CTAs per SM, 8 CTAs per (batch, head) = one thread-block cluster, boundaries aligned
     L, p = offline(capi.F32, 1, 32, 64, 1000)
     l = launch(L, p, 999)
-    assert (l.ctas_per_sm, l.grid, l.parts_per_bh) == (1, 128, 4)
+    assert (l.ctas_per_sm, l.grid, l.parts_per_bh) == (2, 256, 8)
     # config 2: a third resident CTA per SM makes room for one CTA per (batch, head)
     L, p = offline(capi.F16, 10, 32, 64, 1256)
     l = launch(L, p, 1255)
