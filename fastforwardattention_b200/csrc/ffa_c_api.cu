@@ -355,14 +355,6 @@ int fit_clusters(ffa_plan* plan, int cap, bool paged, ffa_launch_t* L, int* clus
     return FFA_OK;
 }
 
-// rows the unit list must cover for this call: every sample is at row t, or -- with per-sample
-// lengths, which the host cannot see -- at a row no greater than the bound t the caller states
-int cap_rows_for(const ffa_plan* p, int t, const int* seq_lengths, int right_or_no_padding)
-{
-    (void)p, (void)seq_lengths, (void)right_or_no_padding;
-    return t;
-}
-
 }  // namespace
 
 extern "C" {
@@ -580,7 +572,7 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     if (plan->ws == nullptr) return fail(FFA_ERR_WORKSPACE, "no workspace bound (ffa_workspace_bind)");
     const bool paged = pages.table != nullptr;
     const bool twopass = p > 0.f || plan->mode == FFA_MODE_ROUND_LIKE_TORCH;
-    const int cap = cap_rows_for(plan, t, seq_lengths, right_or_no_padding);
+    const int cap = t;   // rows the unit list covers: every sample is at row t, or (per-sample lengths) at a row no greater than the bound t
     const long long BH = (long long)plan->B * plan->H;
     FfaStepParams P;
     std::memset(&P, 0, sizeof(P));

@@ -13,16 +13,23 @@ namespace ffa_dev {
 //
 //   warp 0              issues the K tiles (1-D bulk copies into a ring of `stages` buffers,
 //                       full / empty mbarriers) for this CTA's run of the flat unit list;
-//   scorer warps        (4 or 8) consume the tiles: fp32 score of every row to the score scratch
-//                       in global memory (4 bytes per row; read back from L2), running (max, sum)
-//                       per lane group, the new token's score and its K append.  A pair cut over
-//                       several CTAs is combined by whoever arrives last (partials + ticket, no
-//                       waiting).  The CTA that completes a pair's (max, sum) posts a JOB;
+//   scorer warps        (4 or 8) consume the tiles, RB rows per lane group at a time: the RB partial
+//                       dot products of a group are reduced with a transposed butterfly (5 shuffles
+//                       for 4 rows over 16 lanes instead of 16), which leaves every lane with ONE row's
+//                       score; that lane stores it to the score scratch in global memory (4 bytes per
+//                       row, a 32-byte sector per warp; read back from L2) and folds it into its own
+//                       running (max, sum) -- no cross-lane softmax step in the loop.  With K tiles
+//                       only, a row-loop iteration carries half the bytes of the exact kernel's, so
+//                       the instruction count per row, not HBM, is what this loop has to watch.  The
+//                       new token's score and its K append ride along.  A pair cut over several CTAs
+//                       is combined by whoever arrives last (partials + ticket, no waiting).  The CTA
+//                       that completes a pair's (max, sum) posts a JOB;
 //   gather warps        (4) take jobs: re-read the pair's scores, apply the reference rule
 //                       (P = cvt_T(e * inv), Theta = cvt_T(p * inv), skip iff leq(P, Theta)),
 //                       write the optional kept mask, list the survivors per warp in row order,
-//                       fetch only those V rows (16-byte cp.async into a staging area, 8 KB in flight per warp),
-//                       append the new token's v, and store the output row.
+//                       fetch only those V rows (16-byte cp.async into a staging area, 8 KB in flight per
+//                       warp), drop the consumed score lines from L2, append the new token's v, and store
+//                       the output row.
 //
 // Scoring never waits for gathering unless two jobs are already queued, so HBM sees one
 // continuous K stream with the V reads of earlier pairs mixed in.  The floating-point sums

@@ -41,6 +41,8 @@ def test_argument_validation_without_gpu():
     assert L.ffa_cache_init(capi.F16, 1, 1, 9, 8, 64, None, None, None, None, None) == -3
     assert L.ffa_attention(None, None, None, None, None, None, None, 1.0, 0, None, 1, 0.0, None, None) == -4
     assert L.ffa_workspace_bytes(None, 0) == 0
+    assert L.ffa_peer_push_target(None, None) == -4
+    assert L.ffa_static_scratch_status(None, None) == -4
     assert L.ffa_launch_count() == 0
 
 
