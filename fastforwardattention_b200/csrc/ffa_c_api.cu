@@ -50,9 +50,10 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 // 48.9 us in favour of the aligned cut; 8 K tokens 603 vs 594 us against it)
 constexpr long long kAlignedBelowUnitsPerSlot = 200;
 // pruned steps that stream at least this many bytes of K take the streaming kernel when the score scratch is bound
-// (bf16 x 128, 1024 pairs, 5 % of the V rows kept: 2 K tokens 119 vs 112 us for the cluster kernel, 3 K 162 vs 167 us,
-// 4 K 202 vs 223 us, 8 K 378 vs 428 us, 32 K 1492 vs 1830 us)
-constexpr double kStreamPruneAboveBytes = 700e6;
+// (5 % of the V rows kept; streaming vs cluster kernel: fp16 x 64, 320 pairs, 1256 tokens = 51 MB: 25.8 vs 18.8 us;
+// 134-168 MB, four shapes: 39.3-61.5 vs 32.6-60.3 us; bf16 x 128, 1024 pairs: 1 K tokens = 268 MB 58.4 vs 61.0 us,
+// 2 K 102 vs 107 us, 4 K 190 vs 221 us, 8 K 359 vs 428 us, 32 K 1441 vs 1799 us)
+constexpr double kStreamPruneAboveBytes = 250e6;
 
 }  // namespace
 
@@ -124,9 +125,11 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
     // head_dim 80 (160- and 320-byte rows): a batch of the row loop is 128 / 64 rows there
     if ((row_bytes / 16) % 5 == 0) s.tile_rows = 20480 / row_bytes;
     if (tensors == 1) {
-        // the streaming pruning kernel: K tiles only carry half the bytes per row-loop iteration: twice the
-        // compute warps keep up with the ring, and twice the stages keep as many bytes in flight
-        s.warps = 8, s.stages = 4;
+        // the streaming pruning kernel: K tiles only carry half the bytes per row-loop iteration: twice the compute
+        // warps keep up with the ring, and tiles twice as large keep as many bytes in flight with the same two
+        // stages -- two row batches per warp and barrier round trip instead of one (bf16 x 128, 1024 pairs, 8 K /
+        // 32 K tokens: 362 / 1432 us against 378 / 1479 us for four stages of 16 KB)
+        s.warps = 8, s.tile_rows *= 2;
     }
     return s;
 }
@@ -145,6 +148,7 @@ Shape default_shape(const ffa_plan* p, int row_bytes, long long rows_total, int 
 Shape measured_shape(const ffa_plan* p, int row_bytes, long long rows_total, int tensors)
 {
     Shape s = default_shape(p, row_bytes, rows_total, tensors);
+    if (tensors == 1) return s;   // the refinements below were measured on the exact kernel (K and V tiles)
     const double bytes = (double)rows_total * row_bytes * tensors;
     const long long BH = (long long)p->B * p->H;
     if (bytes < 48e6) {
@@ -185,6 +189,7 @@ int fit_launch(const ffa_plan* p, int cap_rows, int tensors, ffa_launch_t* out, 
     if (s.warps < 1) s.warps = 1;
     if (s.warps > 8) s.warps = 8;   // the kernels are compiled for at most 1 + 8 warps
     if (tensors == 1 && p->Dh == 80 && s.warps > 4) s.warps = 4;   // streaming pruning kernel, five vectors per lane: register budget
+    if (tensors == 1 && s.cps > 2) s.cps = 2;   // its 13 warps of 72 registers leave room for two CTAs per SM
     if (s.cps < 1) s.cps = 1;
     if (s.cps > kMaxCtasPerSm) s.cps = kMaxCtasPerSm;
     if (s.stages < 2) s.stages = 2;
