@@ -301,10 +301,10 @@ bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out
         int r = (((rowb / 16) % 5 == 0 ? 20480 : 16384) / rowb) / 8 * 8;   // one 16 KB K tile (20 KB for head_dim 80)
         if (r < 8) r = 8;
         if (r > chunk) r = (chunk + 7) / 8 * 8;
-        const int smem = ffa_k_fused_smem_bytes(p->dtype, p->Dh, r, 2, chunk);
+        const int smem = ffa_k_fused_smem_bytes(p->dtype, p->Dh, r, 2, chunk, c);
         if (smem > p->smem_per_cta) continue;
         int resident = p->smem_per_sm / (smem + kSmemReservePerCta);
-        if (resident > 7) resident = 7;  // 160 threads x <= 72 registers
+        if (resident > 7) resident = 7;  // 160 threads x 56 registers
         const long long slots = (long long)p->sms * resident;
         const long long waves = (BH * c + slots - 1) / slots;
         const long long cost = waves * (chunk + 512);

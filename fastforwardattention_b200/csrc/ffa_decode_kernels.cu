@@ -137,12 +137,12 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
 
 int ffa_k_prune_stream_threads(int scorer_warps) { return 32 * (1 + scorer_warps + kPsGatherWarps); }
 
-int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows)
+int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows, int cluster)
 {
     const int rowb = head_dim * elem_size(dtype);
     const int lpr = lanes_per_row(rowb);
     const int ng = 128 / lpr;
-    return stages * tile_rows * rowb + chunk_rows * 4 + kFusedListCap * 8 + kFusedListCap / 32 * 4 + ng * (head_dim + 4) * 4 + head_dim * 4 + 16 +
+    return stages * tile_rows * rowb + chunk_rows * 4 + kFusedListCap * 4 + kFusedListCap / 32 * 4 + ng * (head_dim + 4) * 4 + cluster * head_dim * 4 + 2 * kMaxClusterCtas * 4 +
            2 * stages * 8 + 16;
 }
 

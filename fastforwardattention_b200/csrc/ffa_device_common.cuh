@@ -26,6 +26,10 @@ constexpr int kStatusBadLength = 2;
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Cache hints: ask for the 128-byte line at p to be brought into L2 (into L1 as well); nothing waits for them.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -151,6 +155,16 @@ __device__ __forceinline__ uint32_t cluster_rank()
 __device__ __forceinline__ void cluster_sync_all()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The two halves of a cluster barrier, for a CTA that has other work between "I am here" and "are the others".
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Stores v at the same shared-memory offset in CTA peer_rank of the cluster; visible there after the next cluster barrier.
+__device__ __forceinline__ void st_peer_smem_f32(void* own_smem_ptr, uint32_t peer_rank, float v)
+{
+    uint32_t peer;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_smem_ptr)), "r"(peer_rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(peer), "f"(v) : "memory");
 }
 __device__ __forceinline__ float ld_peer_smem_f32(const void* own_smem_ptr, uint32_t peer_rank)
 {

@@ -79,7 +79,7 @@ int ffa_k_prune_stream_threads(int scorer_warps);
 int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int consumer_warps, int tensors_per_stage);
 // p > 0 or round-like-torch, small steps whose slices' scores fit in shared memory: one cluster launch.
 int ffa_k_decode_fused_prune(int dtype, int head_dim, const FfaStepParams& P, int smem, cudaStream_t stream);
-int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows);
+int ffa_k_fused_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int chunk_rows, int cluster);
 // diagnostic: a bounded wait that must time out (see ffa_selftest_wait_timeout)
 int ffa_k_wait_selftest(int* status, unsigned long long limit_ns, unsigned long long* waited_ns, cudaStream_t stream);
 // all-gather of the step outputs: a few CTAs per rank

@@ -11,16 +11,16 @@ namespace ffa_dev {
 // touched (attention.cu:1184-1191), so the score pass and the value pass cannot be one
 // streaming sweep.  Here both live in one kernel: a cluster of C CTAs owns a (batch, head);
 // CTA r scores its slice of rows from a K-only bulk-copy ring into its OWN shared memory,
-// the C pairs (max, sum) are exchanged through distributed shared memory behind a cluster
-// barrier, every CTA prunes and gathers the V rows of its slice, and CTA 0 adds the C partial
-// outputs (again through distributed shared memory).  No score scratch in HBM, no second
-// launch, no arrival counters.  Used for small steps whose slices' scores fit in shared memory; the
-// streaming pruning kernel takes everything else.
+// stores its (max, sum) into every peer's shared memory ahead of a cluster barrier, prunes and
+// gathers the V rows of its slice, and stores its partial output into CTA 0's shared memory ahead
+// of a second cluster barrier; CTA 0 adds the C partial outputs.  Nothing is loaded remotely.
+// No score scratch in HBM, no second launch, no arrival counters.  Used for small steps whose
+// slices' scores fit in shared memory; the streaming pruning kernel takes everything else.
 //
-// Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (index, probability)
-// | ballot words | group reduction area [NG][DH + 4] | partial output [DH] | (max, sum) | barriers | flags.
+// Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (row indices)
+// | ballot words | group reduction area [NG][DH + 4] | partial outputs [C][DH] | (max, sum) [8] | barriers | flags.
 constexpr int kFusedThreads = 160;   // 1 copy warp + 4 compute warps
-constexpr int kFusedListCap = 512;   // rows pruned and gathered per round (multiple of 32)
+constexpr int kFusedListCap = 1024;  // rows pruned and gathered per round: 32 ballot words, one per lane of the prefix scan
 
 template <typename T, int DH>
 __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const FfaStepParams P)
@@ -35,16 +35,16 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     const uint32_t tile_bytes = (uint32_t)R * ROWB;
     float* sc = reinterpret_cast<float*>(smem + (size_t)S * tile_bytes);
     int* list_idx = reinterpret_cast<int*>(sc + chunk);
-    float* list_p = reinterpret_cast<float*>(list_idx + kFusedListCap);
-    unsigned* words = reinterpret_cast<unsigned*>(list_p + kFusedListCap);   // one ballot per 32 rows of a round
+    unsigned* words = reinterpret_cast<unsigned*>(list_idx + kFusedListCap);   // one ballot per 32 rows of a round
     float* red = reinterpret_cast<float*>(words + kFusedListCap / 32);
-    float* accs = red + NG * RS;
-    float* stat = accs + DH;                       // [0] max, [1] sum of this CTA's slice
-    uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4);
-    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead, [1] list length
+    float* accs = red + NG * RS;                   // [C][DH]: in CTA 0, the partial outputs of all slices
+    float* stat = accs + (size_t)C * DH;           // [8][2]: (max, sum) of every slice of the pair
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 2 * kMaxClusterCtas);
+    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S), ring = smem_u32(smem);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    cluster_arrive();   // "this CTA runs": its peers wait for that before they store into its shared memory
     pdl_release();
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
@@ -100,6 +100,11 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
             }
         }
     } else {
+        // the new token's k is needed after the score loop and its v after the gather: ask for their lines now
+        if (owns_new && g == 0 && li * 128 < ROWB) {
+            prefetch_l1(static_cast<const unsigned char*>(P.k) + (size_t)bh * ROWB + li * 128);
+            prefetch_l1(static_cast<const unsigned char*>(P.v) + (size_t)bh * ROWB + li * 128);
+        }
         load_row_f32<T, DH>(static_cast<const unsigned char*>(P.q) + (size_t)bh * ROWB, li, qf);
 #pragma unroll
         for (int x = 0; x < VPL; ++x)
@@ -196,21 +201,50 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
         if (li == 0) red[g * RS] = m, red[g * RS + 1] = l;
     }
     __syncthreads();
-    if (tid == 0) {
-        float Mc = -CUDART_INF_F, Lc = 0.f;
-        for (int gg = 0; gg < NG; ++gg) Mc = fmaxf(Mc, red[gg * RS]);
-        for (int gg = 0; gg < NG; ++gg)
-            if (red[gg * RS] != -CUDART_INF_F) Lc += red[gg * RS + 1] * __expf(red[gg * RS] - Mc);
-        stat[0] = Mc, stat[1] = Lc;
+    {
+        // (max, sum) of this slice: every warp combines the NG groups with shuffles; warp 0 publishes them
+        float Mc = -CUDART_INF_F;
+        for (int gg = lane; gg < NG; gg += 32) Mc = fmaxf(Mc, red[gg * RS]);
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) Mc = fmaxf(Mc, __shfl_xor_sync(0xffffffffu, Mc, off));
+        if (warp == 0) {
+            float Lc = 0.f;
+            for (int gg = lane; gg < NG; gg += 32)
+                if (red[gg * RS] != -CUDART_INF_F) Lc += red[gg * RS + 1] * __expf(red[gg * RS] - Mc);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) Lc += __shfl_xor_sync(0xffffffffu, Lc, off);
+            // every CTA of the cluster receives every slice's pair: pushed, so nobody loads remotely after the barrier
+            cluster_wait();
+            if (lane < C) {
+                st_peer_smem_f32(stat + 2 * rank, lane, Mc);
+                st_peer_smem_f32(stat + 2 * rank + 1, lane, Lc);
+            }
+        } else {
+            cluster_wait();
+        }
+        // While the cluster exchanges its statistics, start moving the V rows that can still survive towards L2:
+        // a row survives only if its score is within ln(p) of the pair's max (attention.cu:1185), and the pair's max
+        // is at least this slice's.  A hint only -- the rule below decides; at most two rows per thread.
+        if (prune && Mc != -CUDART_INF_F) {
+            const float thr = Mc + __logf(P.p) - 0.25f;
+            int sent = 0;
+            for (int i = lo + tid; i < hi && sent < 2; i += kFusedThreads)
+                if (sc[i - c0] > thr) {
+                    const unsigned char* vrow = static_cast<const unsigned char*>(P.v_cache) + cache_row_offset(P, bh, i, ROWB);
+#pragma unroll
+                    for (int b = 0; b < ROWB; b += 128) prefetch_l2(vrow + b);
+                    ++sent;
+                }
+        }
     }
     cluster_sync_all();   // every slice's (max, sum) is visible cluster-wide; also a CTA barrier
 
     // ---------------- global statistics of the (batch, head) ----------------
     float M = -CUDART_INF_F, Lsum = 0.f;
-    for (int c = 0; c < C; ++c) M = fmaxf(M, ld_peer_smem_f32(stat, c));
+    for (int c = 0; c < C; ++c) M = fmaxf(M, stat[2 * c]);
     for (int c = 0; c < C; ++c) {
-        const float mc = ld_peer_smem_f32(stat, c);
-        if (mc != -CUDART_INF_F) Lsum += ld_peer_smem_f32(stat + 1, c) * __expf(mc - M);
+        const float mc = stat[2 * c];
+        if (mc != -CUDART_INF_F) Lsum += stat[2 * c + 1] * __expf(mc - M);
     }
     // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
     // the torch-rounding mode divides exactly like torch's softmax does
@@ -234,46 +268,39 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
         // words), so the order of the floating-point sums below never depends on timing.
         __syncthreads();
         const int sub_hi = min(sub + kFusedListCap, hi_mask);
-        constexpr int kMine = (kFusedListCap / 32 + 4) / 5;   // 32-row words per warp and round
-        float my_p[kMine];
-#pragma unroll
-        for (int k = 0; k < kMine; ++k) {
-            const int base = sub + (warp + 5 * k) * 32;
-            my_p[k] = -1.f;
-            if (base >= sub_hi) continue;   // warp-uniform
-            const int i = base + lane;
-            const bool cached = i >= lo && i < hi;
-            float pr = 0.f;
-            bool keep = false;
-            if (cached) {
-                pr = prob_of(sc[i - c0]);
-                keep = prune ? !Elem<T>::leq(pr, theta) : true;
+        constexpr int kWords = kFusedListCap / 32;      // 32: one ballot word per lane of the scan below
+#pragma unroll 1
+        for (int w = warp; w < kWords; w += kFusedThreads / 32) {
+            const int base = sub + w * 32;
+            unsigned bal = 0u;
+            if (base < sub_hi) {             // warp-uniform
+                const int i = base + lane;
+                bool keep = false;
+                if (i >= lo && i < hi) keep = prune ? !Elem<T>::leq(prob_of(sc[i - c0]), theta) : true;
+                bal = __ballot_sync(0xffffffffu, keep);
+                if (P.kept_mask != nullptr && lane == 0)
+                    P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
+                        bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
             }
-            const unsigned bal = __ballot_sync(0xffffffffu, keep);
-            if (P.kept_mask != nullptr && lane == 0)
-                P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] =
-                    bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
-            if (lane == 0) words[warp + 5 * k] = bal;
-            if (keep) my_p[k] = pr;
+            if (lane == 0) words[w] = bal;
         }
         __syncthreads();
-        const int nwords = (sub_hi - sub + 31) >> 5;
+        // every warp scans the 32 word counts itself: exclusive prefix = list position of a word's first survivor
+        const int cnt = __popc(words[lane]);
+        int incl = cnt;
 #pragma unroll
-        for (int k = 0; k < kMine; ++k) {
-            if (my_p[k] >= 0.f) {
-                const int w = warp + 5 * k;
-                int pos = __popc(words[w] & ((1u << lane) - 1u));
-                for (int ww = 0; ww < w; ++ww) pos += __popc(words[ww]);
-                list_idx[pos] = sub + w * 32 + lane, list_p[pos] = my_p[k];
-            }
+        for (int off = 1; off < 32; off <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += up;
         }
-        if (tid == 0) {
-            int tot = 0;
-            for (int w = 0; w < nwords; ++w) tot += __popc(words[w]);
-            flags[1] = tot;
+        const int n = __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll 1
+        for (int w = warp; w < kWords; w += kFusedThreads / 32) {
+            const unsigned bal = words[w];
+            const int first = __shfl_sync(0xffffffffu, incl - cnt, w);
+            if ((bal >> lane) & 1u) list_idx[first + __popc(bal & ((1u << lane) - 1u))] = sub + w * 32 + lane;
         }
         __syncthreads();
-        const int n = flags[1];
         if (warp > 0) {
             for (int base = 0; base < n; base += RB * NG) {
                 uint4 raw[RB][VPL];
@@ -282,8 +309,9 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
                 for (int uu = 0; uu < RB; ++uu) {
                     const int idx = base + uu * NG + g;
                     const bool okr = idx < n;
-                    pr[uu] = okr ? list_p[idx] : 0.f;
-                    const size_t roff = okr ? cache_row_offset(P, bh, list_idx[idx], ROWB) : 0;
+                    const int row = okr ? list_idx[idx] : c0;
+                    pr[uu] = okr ? prob_of(sc[row - c0]) : 0.f;
+                    const size_t roff = okr ? cache_row_offset(P, bh, row, ROWB) : 0;
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
                         raw[uu][x] = make_uint4(0, 0, 0, 0);
@@ -341,18 +369,17 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
     for (int d = tid; d < DH; d += kFusedThreads) {
         float A = 0.f;
         for (int gg = 0; gg < NG; ++gg) A += red[gg * RS + d];
-        accs[d] = A;
+        st_peer_smem_f32(accs + (size_t)rank * DH + d, 0, A);   // into CTA 0's shared memory
     }
-    cluster_sync_all();   // every slice's partial output is visible cluster-wide
+    cluster_sync_all();   // every slice's partial output has arrived in CTA 0
     if (rank == 0) {
         T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
         for (int d = tid; d < DH; d += kFusedThreads) {
             float A = 0.f;
-            for (int c = 0; c < C; ++c) A += ld_peer_smem_f32(accs + d, c);   // slice order: deterministic
+            for (int c = 0; c < C; ++c) A += accs[(size_t)c * DH + d];   // slice order: deterministic
             Elem<T>::store(outp + d, sr.ok ? A : 0.f);
         }
     }
-    cluster_sync_all();   // peers keep their shared memory alive until CTA 0 has read it
     if (tid == 0) {
         if (flags[0]) atomicOr(P.status, kStatusWaitTimeout);
         if (!sr.ok && rank == 0) atomicOr(P.status, kStatusBadLength);
