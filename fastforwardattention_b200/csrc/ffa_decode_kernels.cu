@@ -131,8 +131,8 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
         return stages * tile_rows * rowb + kPsGatherWarps * kPsStageBytes + ng * 4 * 8 + kPsGatherWarps * kPsListCap * 8 + kPsJobs * kPsGatherWarps * head_dim * 4 +
                (int)sizeof(PsJob) * (kPsJobs + (kPsJobs & 1)) + (2 * stages + 3 * kPsJobs) * 8 + 16;
     }
-    // ring, group reduction area, barriers, flags, the CTA's partial for the cluster merge
-    return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16 + (head_dim + 4) * 4;
+    // ring, group reduction area, barriers, flags, the slots that receive a cluster's partials
+    return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16 + kMaxClusterCtas * (head_dim + 2) * 4;
 }
 
 int ffa_k_prune_stream_threads(int scorer_warps) { return 32 * (1 + scorer_warps + kPsGatherWarps); }

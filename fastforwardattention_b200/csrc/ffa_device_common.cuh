@@ -73,6 +73,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+
 // Waits for the phase with the given parity.  Never spins for ever: after kWaitLimitNs of wall
 // time (or as soon as another thread of the CTA gave up) it raises the CTA's `dead` flag and
 // returns false; callers then skip the data but keep walking the same control flow so every

@@ -36,8 +36,8 @@ __device__ __forceinline__ void merge_partials(const FfaStepParams& P, uint32_t 
 // ------------------------------------------------------------------------------------------
 // Shared memory: [stages][K tile | V tile] ring, then the group
 // reduction area [NG][DH + 4] (rows 16-byte aligned; max and sum in the tail), then
-// full/empty barriers, then two flags, then the CTA's partial result [DH + 2] for the merge
-// inside a thread-block cluster.
+// full/empty barriers, then two flags, then [8][DH + 2] slots in which CTA 0 of a thread-block
+// cluster receives the partial results of the cluster's CTAs.
 // Warp 0 issues the copies (one elected lane); warps 1.. compute.  A lane group of LPR lanes
 // owns a row: 16-byte shared-memory reads, fp32 FMAs, butterfly sum.  Each group keeps its
 // own online-softmax state, so the row loop has no CTA-level synchronisation at all.
@@ -64,15 +64,16 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
     uint64_t* bars = reinterpret_cast<uint64_t*>(red + NG * RS);
     volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S);  // [0] dead, [1] last-arriver
     // Cluster merge (one-pass, few pairs): the C CTAs that share a (batch, head) are one thread-block
-    // cluster; each leaves its partial (weighted sum, max, sum) in its own shared memory and CTA 0
-    // of the cluster combines them through distributed shared memory -- no partials in global
-    // memory, no fence, no arrival counter.  The launcher guarantees grid = B*H*C, so a CTA owns
-    // exactly one part of exactly one pair.
-    float* clp = reinterpret_cast<float*>(const_cast<int*>(flags) + 4);
+    // cluster; each stores its partial (weighted sum, max, sum) into slot [rank] of CTA 0's shared
+    // memory ahead of one cluster barrier, and CTA 0 combines the slots -- no partials in global
+    // memory, no fence, no arrival counter, no remote load.  The launcher guarantees grid = B*H*C,
+    // so a CTA owns exactly one part of exactly one pair.
+    float* clp = reinterpret_cast<float*>(const_cast<int*>(flags) + 4);   // [kMaxClusterCtas][DH + 2]
     const bool cl = P.cluster > 1;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
     const uint32_t ring = smem_u32(smem);
 
+    if (cl) cluster_arrive();   // "this CTA runs": its peers wait for that before they store into its shared memory
     pdl_release();
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -82,8 +83,6 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         flags[0] = 0, flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (cl)
-        for (int i = threadIdx.x; i < DH + 2; i += blockDim.x) clp[i] = i == DH ? -CUDART_INF_F : 0.f;   // "nothing seen"
     __syncthreads();
     pdl_wait();   // nothing above touches global memory; everything below may read what the previous kernel wrote
     const bool push = P.push_world > 1;
@@ -129,6 +128,8 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 }
             }
         }
+        __syncwarp();
+        if (cl) cluster_wait();   // every thread pairs the arrival above with one wait
     } else {
         // ---------------- consumers ----------------
         const int ctid = threadIdx.x - 32;
@@ -138,6 +139,8 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         constexpr bool kAllLanes = (VPR == LPR * VPL);  // every lane of a group owns VPL vectors
         uint32_t stage = 0, phase = 0;
         long long u = u0;
+        bool sent = false;   // cluster merge: this CTA's partial is in CTA 0's shared memory
+        float* slot_in_leader = clp + (size_t)(cl ? cluster_rank() : 0u) * (DH + 2);
         // q of the first (batch, head) of this CTA's run; the next one is fetched while the
         // current one is being processed, so its global-memory latency is never exposed
         const unsigned char* qbase = static_cast<const unsigned char*>(P.q);
@@ -348,16 +351,22 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             named_bar_sync(1, nct);
             float M = -CUDART_INF_F;
             for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, red[gg * RS + DH]);
+            // one exponential per group, not per group and element: thread gg leaves group gg's weight in the row's pad
+            for (int gg = ctid; gg < NG; gg += nct) {
+                const float mg = red[gg * RS + DH];
+                red[gg * RS + DH + 2] = mg == -CUDART_INF_F ? 0.f : expo(mg - M);
+            }
+            named_bar_sync(1, nct);
             const bool whole = (j0 == 0 && j1 == upb);
             bool wrote_out = whole;   // this CTA wrote out[bh, :]: a whole pair, or the last arriver's merge
             const int slot = blockIdx.x + bh;
             float* part = P.partials + (size_t)slot * (DH + 2);
             T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+            if (cl && !whole && !sent) cluster_wait();   // CTA 0 runs
             for (int d = ctid; d < DH; d += nct) {
                 float A = 0.f, L = 0.f;
                 for (int gg = 0; gg < NG; ++gg) {
-                    const float mg = red[gg * RS + DH];
-                    const float w = mg == -CUDART_INF_F ? 0.f : expo(mg - M);
+                    const float w = red[gg * RS + DH + 2];
                     A = fmaf(w, red[gg * RS + d], A);
                     L = fmaf(w, red[gg * RS + DH + 1], L);
                 }
@@ -367,13 +376,14 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                     outp[d] = o;
                     if (push) push_store<T, DH>(P, push_seq, bh, d, o);
                 } else if (cl) {
-                    clp[d] = A;
-                    if (d == 0) clp[DH] = M, clp[DH + 1] = L;
+                    st_peer_smem_f32(slot_in_leader + d, 0, A);
+                    if (d == 0) st_peer_smem_f32(slot_in_leader + DH, 0, M), st_peer_smem_f32(slot_in_leader + DH + 1, 0, L);
                 } else {
                     part[d] = A;
                     if (d == 0) part[DH] = M, part[DH + 1] = L;
                 }
             }
+            if (cl && !whole) sent = true;
             if (!whole && !cl) {
                 // cross-CTA merge without waiting: whoever arrives last does it
                 __threadfence();
@@ -398,6 +408,10 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             if (!sr.ok && ctid == 0) atomicOr(P.status, kStatusBadLength);
             u += j1 - j0;
         }
+        if (cl && !sent) {   // a CTA without rows (or with a whole pair): its slot says "nothing seen"
+            cluster_wait();
+            for (int d = ctid; d < DH + 2; d += nct) st_peer_smem_f32(slot_in_leader + d, 0, d == DH ? -CUDART_INF_F : 0.f);
+        }
     }
     __syncthreads();
     if (cl) {
@@ -409,29 +423,17 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
         const bool leader = cluster_rank() == 0;
         T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
         float* part = P.partials + ((size_t)bh * K + kc) * (DH + 2);
-        cluster_sync_all();   // every CTA's partial is in its shared memory
+        cluster_sync_all();   // every CTA's partial has arrived in CTA 0's shared memory
         if (leader) {
-            // all remote reads of a thread are issued before the first is used: one trip, not Q
             for (int d = threadIdx.x; d < DH; d += blockDim.x) {
-                float mc[kMaxClusterCtas], lc[kMaxClusterCtas], ac[kMaxClusterCtas];
-#pragma unroll
-                for (int c = 0; c < kMaxClusterCtas; ++c) {
-                    mc[c] = -CUDART_INF_F, lc[c] = 0.f, ac[c] = 0.f;
-                    if (c < Q) {
-                        mc[c] = ld_peer_smem_f32(clp + DH, c);
-                        lc[c] = ld_peer_smem_f32(clp + DH + 1, c);
-                        ac[c] = ld_peer_smem_f32(clp + d, c);
-                    }
-                }
                 float MM = -CUDART_INF_F;
-#pragma unroll
-                for (int c = 0; c < kMaxClusterCtas; ++c) MM = fmaxf(MM, mc[c]);
+                for (int c = 0; c < Q; ++c) MM = fmaxf(MM, clp[c * (DH + 2) + DH]);
                 float A = 0.f, L = 0.f;
-#pragma unroll
-                for (int c = 0; c < kMaxClusterCtas; ++c) {   // rank order: deterministic
-                    const float w = mc[c] == -CUDART_INF_F ? 0.f : (kPrecise ? expf(mc[c] - MM) : fast_exp2(mc[c] - MM));
-                    A = fmaf(w, ac[c], A);
-                    L = fmaf(w, lc[c], L);
+                for (int c = 0; c < Q; ++c) {   // rank order: deterministic
+                    const float mc = clp[c * (DH + 2) + DH];
+                    const float w = mc == -CUDART_INF_F ? 0.f : (kPrecise ? expf(mc - MM) : fast_exp2(mc - MM));
+                    A = fmaf(w, clp[c * (DH + 2) + d], A);
+                    L = fmaf(w, clp[c * (DH + 2) + DH + 1], L);
                 }
                 if (K == 1) {
                     T o;
@@ -444,9 +446,11 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
                 }
             }
         }
-        if (push && leader && K == 1) __threadfence_system();   // rows at the peers before the pair is counted
-        cluster_sync_all();   // peers kept their shared memory alive until the leader had read it
-        if (push && leader && K == 1 && threadIdx.x == 0) push_pair_done(P, push_seq);
+        if (push && leader && K == 1) {
+            __threadfence_system();   // rows at the peers before the pair is counted
+            __syncthreads();
+            if (threadIdx.x == 0) push_pair_done(P, push_seq);
+        }
         if (leader && K > 1) {
             __threadfence();
             __syncthreads();
