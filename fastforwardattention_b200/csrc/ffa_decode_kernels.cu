@@ -128,7 +128,7 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
     if (tensors_per_stage == 1) {
         // the streaming pruning kernel: K ring, scorer groups' (max, sum), survivor lists, gather partials,
         // job slots, barriers, flags
-        return stages * tile_rows * rowb + kPsGatherWarps * kPsStageBytes + ng * 4 * 8 + kPsGatherWarps * kPsListCap * 8 + kPsJobs * kPsGatherWarps * head_dim * 4 +
+        return stages * tile_rows * rowb + kPsGatherWarps * kPsStageBytes + 2 * ng * 4 * 8 + kPsGatherWarps * kPsListCap * 8 + kPsJobs * kPsGatherWarps * head_dim * 4 +
                (int)sizeof(PsJob) * (kPsJobs + (kPsJobs & 1)) + (2 * stages + 3 * kPsJobs) * 8 + 16;
     }
     // ring, group reduction area, barriers, flags, the slots that receive a cluster's partials

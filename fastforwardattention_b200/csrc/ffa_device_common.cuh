@@ -195,6 +195,8 @@ struct Elem<float> {
         f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
     }
     static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ uint32_t bits(float x) { return __float_as_uint(x); }
+    static __device__ __forceinline__ float from_bits(uint32_t b) { return __uint_as_float(b); }
     static __device__ __forceinline__ float to_float(float x) { return x; }
     static __device__ __forceinline__ void store(float* p, float x) { *p = x; }
     // attention.cu:461-464
@@ -219,6 +221,9 @@ struct Elem<__half> {
         for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
     }
     static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    // the 16 bits of a value that round() produced, and back
+    static __device__ __forceinline__ uint32_t bits(float x) { return __half_as_ushort(__float2half_rn(x)); }
+    static __device__ __forceinline__ float from_bits(uint32_t b) { return __half2float(__ushort_as_half((unsigned short)b)); }
     static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
     static __device__ __forceinline__ void store(__half* p, float x) { *p = __float2half_rn(x); }
     // attention.cu:466-469 hands two raw bit patterns to __hle; the unsigned short -> __half
@@ -250,6 +255,8 @@ struct Elem<__nv_bfloat16> {
         for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
     }
     static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ uint32_t bits(float x) { return __bfloat16_as_ushort(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ float from_bits(uint32_t b) { return __bfloat162float(__ushort_as_bfloat16((unsigned short)b)); }
     static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
     static __device__ __forceinline__ void store(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
     // the reference has no bf16; plain value comparison

@@ -37,12 +37,12 @@ namespace ffa_dev {
 // in index order), so results do not depend on timing.  Every wait is time-bounded.
 //
 // Shared memory: [stages][K tile] ring | per gather warp: V-row staging [kPsStageBytes] | scorer groups'
-// (max, sum) [NG * RB][2] | per gather warp: survivor list (row, probability) [kPsListCap] | gather partial
+// (max, sum) [2][NG * RB][2] | per gather warp: survivor list [2 * kPsListCap words] | gather partial
 // outputs [jobs][warps][DH] | job slots | barriers: full[S], empty[S], job_full[J], job_empty[J],
 // gather_done[J] | flags.
 constexpr int kPsGatherWarps = 4;
-constexpr int kPsListCap = 256;   // rows a gather warp tests per round: 8 words of 32 rows
-constexpr int kPsWordsPerRound = kPsListCap / 32;
+constexpr int kPsListCap = 256;   // survivor list of a gather warp: 256 (row, probability) entries of 8 bytes, or 512 packed into 4
+constexpr int kPsWordsPerRound = kPsListCap / 32;   // 32-row words a gather warp tests per round (twice that for 16-bit tensors)
 constexpr int kPsStageBytes = 8192;   // per gather warp: surviving V rows land here (cp.async), up to 32 rows in flight
 constexpr int kPsJobs = 2;        // queued (batch, head) pairs between scorers and gatherers
 
@@ -73,10 +73,9 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
     const int nct = nsw * 32, NG = nct / LPR;      // scorer threads, scorer lane groups
     const uint32_t tile_bytes = (uint32_t)R * ROWB;
     unsigned char* gstage = smem + (size_t)S * tile_bytes;                           // [NGW][kPsStageBytes]
-    float* red = reinterpret_cast<float*>(gstage + NGW * kPsStageBytes);             // [NG * RB][2]
-    int* list_idx = reinterpret_cast<int*>(red + 2 * NG * RB);                            // [NGW][kPsListCap]
-    float* list_p = reinterpret_cast<float*>(list_idx + NGW * kPsListCap);           // [NGW][kPsListCap]
-    float* gred = list_p + NGW * kPsListCap;                                         // [kPsJobs][NGW][DH]
+    float* red = reinterpret_cast<float*>(gstage + NGW * kPsStageBytes);             // [2][NG * RB][2], alternating per segment
+    uint32_t* lists = reinterpret_cast<uint32_t*>(red + 4 * NG * RB);                // [NGW][2 * kPsListCap] words
+    float* gred = reinterpret_cast<float*>(lists + NGW * 2 * kPsListCap);            // [kPsJobs][NGW][DH]
     PsJob* jobs = reinterpret_cast<PsJob*>(gred + kPsJobs * NGW * DH);               // [kPsJobs]
     uint64_t* bars = reinterpret_cast<uint64_t*>(jobs + kPsJobs + (kPsJobs & 1));    // 8-byte aligned: sizeof(PsJob) = 12
     volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S + 3 * kPsJobs);  // [0] dead, [1] last-arriver
@@ -165,6 +164,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
             if (++jslot == kPsJobs) jslot = 0, ++juse;
         };
         long long u = u0;
+        int rbuf = 0;   // which half of `red` this segment uses
         while (u < u1) {
             const int bh = (int)(u / upb), j0 = (int)(u - (long long)bh * upb);
             const int j1 = (int)min((long long)upb, j0 + (u1 - u));
@@ -280,17 +280,24 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 }
             }
             // ---- (max, sum) of this CTA's piece: the first scorer warp combines the lane groups ----
-            if (store_lane) red[2 * (g * RB + myrow)] = m, red[2 * (g * RB + myrow) + 1] = l;   // one entry per (group, row class)
-            __threadfence();   // this thread's scores are visible device-wide before anybody is told about them
+            // The other scorer warps go straight on to the next segment: `red` alternates between two halves, and a
+            // half is written again only after the barrier of the segment in between, which the first warp joins
+            // when it is done here.  The scores were stored by all scorer threads; the barrier orders those stores
+            // before the first warp's device-wide fence below, which is what makes them visible to whoever is told
+            // about them (the same chain a grid-wide barrier is built from).
+            float* redb = red + rbuf * 2 * NG * RB;
+            if (store_lane) redb[2 * (g * RB + myrow)] = m, redb[2 * (g * RB + myrow) + 1] = l;   // one entry per (group, row class)
             named_bar_sync(1, nct);
+            rbuf ^= 1;
             const bool whole = (j0 == 0 && j1 == upb);
             if (warp == 1) {
+                __threadfence();
                 float Mg = -CUDART_INF_F, Lg = 0.f;
-                for (int gg = lane; gg < NG * RB; gg += 32) Mg = fmaxf(Mg, red[2 * gg]);
+                for (int gg = lane; gg < NG * RB; gg += 32) Mg = fmaxf(Mg, redb[2 * gg]);
 #pragma unroll
                 for (int off = 16; off >= 1; off >>= 1) Mg = fmaxf(Mg, __shfl_xor_sync(0xffffffffu, Mg, off));
                 for (int gg = lane; gg < NG * RB; gg += 32)
-                    if (red[2 * gg] != -CUDART_INF_F) Lg += red[2 * gg + 1] * __expf(red[2 * gg] - Mg);
+                    if (redb[2 * gg] != -CUDART_INF_F) Lg += redb[2 * gg + 1] * __expf(redb[2 * gg] - Mg);
 #pragma unroll
                 for (int off = 16; off >= 1; off >>= 1) Lg += __shfl_xor_sync(0xffffffffu, Lg, off);
                 if (!sr.ok) {
@@ -332,7 +339,6 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                     }
                 }
             }
-            named_bar_sync(1, nct);   // `red` is reused by the next segment
             u += j1 - j0;
         }
         if (tid == 32) post_job(-1, 0.f, 0.f);   // no more jobs from this CTA
@@ -340,8 +346,11 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         // ---------------- gatherers ----------------
         const int gw = warp - 1 - nsw;
         const int gl = lane / LPR, li = lane % LPR;
-        int* my_idx = list_idx + gw * kPsListCap;
-        float* my_p = list_p + gw * kPsListCap;
+        // Survivors of a round, in row order.  16-bit tensors: one word per survivor (row offset within the round,
+        // probability as the 16 bits it was rounded to), so a round covers 16 words of 32 rows; fp32: (row, probability).
+        constexpr bool kPacked = sizeof(T) == 2;
+        constexpr int WPR = kPacked ? 2 * kPsWordsPerRound : kPsWordsPerRound;
+        uint32_t* my_list = lists + gw * 2 * kPsListCap;
         const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
         const unsigned char* my_stage_p = gstage + gw * kPsStageBytes;
         const uint32_t my_stage = smem_u32(my_stage_p);
@@ -362,6 +371,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 return Elem<T>::round(expf(s - M) / Lsum);
             };
             const float* sc_row = P.scores + (size_t)bh * P.score_stride;
+            uint32_t* mask_row = P.kept_mask != nullptr ? P.kept_mask + (size_t)bh * P.mask_words : nullptr;
             float2 acc2[VPL][E2];
 #pragma unroll
             for (int x = 0; x < VPL; ++x)
@@ -370,45 +380,43 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
 
             const int nwords = (sr.row >> 5) + 1;   // 32-row words that hold rows 0..sr.row
             // scores of up to 16 words, all loads before the first use (written by other threads: read at L2)
-            auto load_scores = [&](int w0, float (&s)[kPsWordsPerRound]) {
+            auto load_scores = [&](int w0, float (&s)[WPR]) {
 #pragma unroll
-                for (int k = 0; k < kPsWordsPerRound; ++k) {
+                for (int k = 0; k < WPR; ++k) {
                     const int i = (w0 + k) * 32 + lane;
                     s[k] = (w0 + k < nwords && i >= sr.first && i < sr.row) ? __ldcg(sc_row + i) : 0.f;
                 }
             };
-            float s[kPsWordsPerRound];
-            int w0 = gw * kPsWordsPerRound;
+            float s[WPR];
+            int w0 = gw * WPR;
             if (w0 < nwords) load_scores(w0, s);
-            for (; w0 < nwords; w0 += NGW * kPsWordsPerRound) {
+            for (; w0 < nwords; w0 += NGW * WPR) {
                 int n = 0;
                 __syncwarp();   // the previous round's list has been consumed by every lane
+                // straight-line code, no branch per word: the 16 (8) words' chains of exponential, rounding and vote
+                // overlap; only the running count n links them
 #pragma unroll
-                for (int k = 0; k < kPsWordsPerRound; ++k) {
-                    if (w0 + k >= nwords) break;   // warp-uniform
+                for (int k = 0; k < WPR; ++k) {
                     const int base = (w0 + k) * 32, i = base + lane;
-                    const bool cached = i >= sr.first && i < sr.row;
-                    float pr = 0.f;
-                    bool keep = false;
-                    if (cached) {
-                        pr = prob_of(s[k]);
-                        keep = prune ? !Elem<T>::leq(pr, theta) : true;
-                    }
+                    const bool cached = w0 + k < nwords && i >= sr.first && i < sr.row;
+                    const float pr = prob_of(s[k]);
+                    const bool keep = cached && (prune ? !Elem<T>::leq(pr, theta) : true);
                     const unsigned bal = __ballot_sync(0xffffffffu, keep);
-                    if (P.kept_mask != nullptr && lane == 0)
-                        P.kept_mask[(size_t)bh * P.mask_words + (w0 + k)] =
-                            bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
-                    if (keep) {
-                        const int pos = n + __popc(bal & ((1u << lane) - 1u));
-                        my_idx[pos] = i, my_p[pos] = pr;
+                    if (mask_row != nullptr && lane == 0 && w0 + k < nwords)
+                        mask_row[w0 + k] = bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+                    const int pos = n + __popc(bal & ((1u << lane) - 1u));
+                    if constexpr (kPacked) {
+                        if (keep) my_list[pos] = (uint32_t)(i - w0 * 32) | (Elem<T>::bits(pr) << 16);
+                    } else {
+                        if (keep) my_list[2 * pos] = (uint32_t)i, my_list[2 * pos + 1] = __float_as_uint(pr);
                     }
                     n += __popc(bal);
                 }
                 // This round's score lines (one per 32-row word; every lane has used its values by now) are not needed
                 // again: spare HBM their write-back.  The word of the new token's row is read once more and left alone.
-                if (lane < kPsWordsPerRound && w0 + lane < nwords - 1) l2_discard_line(sc_row + (size_t)(w0 + lane) * 32);
+                if (lane < WPR && w0 + lane < nwords - 1) l2_discard_line(sc_row + (size_t)(w0 + lane) * 32);
                 // the next round's scores travel while this round's V rows are fetched
-                if (w0 + NGW * kPsWordsPerRound < nwords) load_scores(w0 + NGW * kPsWordsPerRound, s);
+                if (w0 + NGW * WPR < nwords) load_scores(w0 + NGW * WPR, s);
                 __syncwarp();
                 // survivors in row order; lane group gl takes entries gl, gl + GPW, ...; a batch of SROWS rows is
                 // copied into the warp's staging area (every lane its own 16-byte pieces), then accumulated
@@ -417,7 +425,8 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                     for (int st = 0; st < STEPS; ++st) {
                         const int e = base + st * GPW + gl;
                         if (e < n) {
-                            const unsigned char* src = vc + cache_row_offset(P, bh, my_idx[e], ROWB);
+                            const int row = kPacked ? w0 * 32 + (int)(my_list[e] & 0xffffu) : (int)my_list[2 * e];
+                            const unsigned char* src = vc + cache_row_offset(P, bh, row, ROWB);
 #pragma unroll
                             for (int x = 0; x < VPL; ++x)
                                 if (kAllLanes || li + x * LPR < VPR)
@@ -429,7 +438,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                     for (int st = 0; st < STEPS; ++st) {
                         const int e = base + st * GPW + gl;
                         if (e < n) {
-                            const float pe = my_p[e];
+                            const float pe = kPacked ? Elem<T>::from_bits(my_list[e] >> 16) : __uint_as_float(my_list[2 * e + 1]);
                             const float2 p2 = make_float2(pe, pe);
 #pragma unroll
                             for (int x = 0; x < VPL; ++x)
