@@ -128,8 +128,8 @@ int ffa_k_smem_bytes(int dtype, int head_dim, int tile_rows, int stages, int con
     if (tensors_per_stage == 1) {
         // the streaming pruning kernel: K ring, scorer groups' (max, sum), survivor lists, gather partials,
         // job slots, barriers, flags
-        return stages * tile_rows * rowb + kPsGatherWarps * kPsStageBytes + 2 * ng * 4 * 8 + kPsGatherWarps * kPsListCap * 8 + kPsJobs * kPsGatherWarps * head_dim * 4 +
-               (int)sizeof(PsJob) * (kPsJobs + (kPsJobs & 1)) + (2 * stages + 3 * kPsJobs) * 8 + 16;
+        return stages * tile_rows * rowb + kPsGatherWarps * kPsStageBytes + 2 * ng * 4 * 8 + kPsGatherWarps * kPsListCap * 8 + kPsJobs * kPsStreams * head_dim * 4 +
+               (int)sizeof(PsJob) * kPsJobs + 2 * kPsJobs * 4 + (2 * stages + 2 * kPsJobs) * 8 + 16;
     }
     // ring, group reduction area, barriers, flags, the slots that receive a cluster's partials
     return stages * tensors_per_stage * tile_rows * rowb + ng * (head_dim + 4) * 4 + 2 * stages * 8 + 16 + kMaxClusterCtas * (head_dim + 2) * 4;

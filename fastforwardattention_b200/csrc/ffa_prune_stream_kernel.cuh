@@ -24,31 +24,37 @@ namespace ffa_dev {
 //                       new token's score and its K append ride along.  A pair cut over several CTAs
 //                       is combined by whoever arrives last (partials + ticket, no waiting).  The CTA
 //                       that completes a pair's (max, sum) posts a JOB;
-//   gather warps        (4) take jobs: re-read the pair's scores, apply the reference rule
-//                       (P = cvt_T(e * inv), Theta = cvt_T(p * inv), skip iff leq(P, Theta)),
-//                       write the optional kept mask, list the survivors per warp in row order,
-//                       fetch only those V rows (16-byte cp.async into a staging area, 8 KB in flight per
-//                       warp), drop the consumed score lines from L2, append the new token's v, and store
-//                       the output row.
+//   gather warps        (4) take jobs: a job's rows are dealt round by round to 12 STREAMS; a warp claims a stream
+//                       (a counter in shared memory), re-reads its scores, applies the reference rule
+//                       (P = cvt_T(e * inv), Theta = cvt_T(p * inv), skip iff leq(P, Theta)), writes the
+//                       optional kept mask, lists the survivors in row order, fetches only those V rows
+//                       (16-byte cp.async into a staging area), drops the consumed score lines from L2, and
+//                       leaves the stream's partial output in shared memory; the warp that completes a job's
+//                       last stream adds the 12 partials in stream order, appends the new token's v and
+//                       stores the output row.  Who computed which stream never shows in the result.
 //
 // Scoring never waits for gathering unless two jobs are already queued, so HBM sees one
-// continuous K stream with the V reads of earlier pairs mixed in.  The floating-point sums
-// follow a fixed order (row -> gather warp and lane group by position, groups and warps added
-// in index order), so results do not depend on timing.  Every wait is time-bounded.
+// continuous K stream with the V reads of earlier pairs mixed in.  When a CTA's scorer warps run out
+// of K rows they turn into gather warps for the job they posted last (their staging areas are
+// carved from the K ring, which is idle by then): the gather of a CTA's final pair, which nothing
+// can overlap, is spread over all its warps instead of four.  Every wait is time-bounded.
 //
 // Shared memory: [stages][K tile] ring | per gather warp: V-row staging [kPsStageBytes] | scorer groups'
-// (max, sum) [2][NG * RB][2] | per gather warp: survivor list [2 * kPsListCap words] | gather partial
-// outputs [jobs][warps][DH] | job slots | barriers: full[S], empty[S], job_full[J], job_empty[J],
-// gather_done[J] | flags.
+// (max, sum) [2][NG * RB][2] | per gather warp: survivor list [2 * kPsListCap words] | stream partial
+// outputs [jobs][streams][DH] | job slots | stream counters: claimed[J], finished[J] | barriers: full[S],
+// empty[S], job_full[J], job_empty[J] | flags.
 constexpr int kPsGatherWarps = 4;
+constexpr int kPsStreams = 12;    // partial sums per job; also the most warps that can work on one job
 constexpr int kPsListCap = 256;   // survivor list of a gather warp: 256 (row, probability) entries of 8 bytes, or 512 packed into 4
 constexpr int kPsWordsPerRound = kPsListCap / 32;   // 32-row words a gather warp tests per round (twice that for 16-bit tensors)
-constexpr int kPsStageBytes = 8192;   // per gather warp: surviving V rows land here (cp.async), up to 32 rows in flight
+constexpr int kPsStageBytes = 4096;   // per gather warp: surviving V rows land here (cp.async), up to 16 rows in flight
+constexpr int kPsHelperBytes = kPsStageBytes + 2 * kPsListCap * 4;   // staging + list of a scorer warp that helps
 constexpr int kPsJobs = 2;        // queued (batch, head) pairs between scorers and gatherers
 
 struct PsJob {
     int bh;       // pair to gather; -1: no more jobs
     float M, L;   // max and sum(exp) over the pair's rows, new token included
+    int seq;      // how often this slot has been used before: tells a late warp that the slot has moved on
 };
 
 // head_dim 80 keeps five vectors per lane in flight: at most 4 scorer warps there, for the register budget of
@@ -63,7 +69,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
     constexpr int E2 = EPV / 2;
     constexpr bool kAllLanes = (VPR == LPR * VPL);
     constexpr int NGW = kPsGatherWarps, GPW = 32 / LPR;     // gather warps; lane groups (rows in flight per step) per warp
-    constexpr int STEPS = VPL >= 4 ? 2 : 16 / VPL;          // V rows a lane group keeps in flight per batch
+    constexpr int STEPS = VPL >= 4 ? 1 : 8 / VPL;           // V rows a lane group keeps in flight per batch
     constexpr int SROWS = STEPS * GPW;                      // rows per batch and gather warp
     static_assert(SROWS * ROWB <= kPsStageBytes, "a batch of V rows fits the warp's staging area");
 
@@ -75,12 +81,14 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
     unsigned char* gstage = smem + (size_t)S * tile_bytes;                           // [NGW][kPsStageBytes]
     float* red = reinterpret_cast<float*>(gstage + NGW * kPsStageBytes);             // [2][NG * RB][2], alternating per segment
     uint32_t* lists = reinterpret_cast<uint32_t*>(red + 4 * NG * RB);                // [NGW][2 * kPsListCap] words
-    float* gred = reinterpret_cast<float*>(lists + NGW * 2 * kPsListCap);            // [kPsJobs][NGW][DH]
-    PsJob* jobs = reinterpret_cast<PsJob*>(gred + kPsJobs * NGW * DH);               // [kPsJobs]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(jobs + kPsJobs + (kPsJobs & 1));    // 8-byte aligned: sizeof(PsJob) = 12
-    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S + 3 * kPsJobs);  // [0] dead, [1] last-arriver
+    float* gred = reinterpret_cast<float*>(lists + NGW * 2 * kPsListCap);            // [kPsJobs][kPsStreams][DH]
+    PsJob* jobs = reinterpret_cast<PsJob*>(gred + kPsJobs * kPsStreams * DH);        // [kPsJobs]
+    int* claimed = reinterpret_cast<int*>(jobs + kPsJobs);                           // [kPsJobs] streams handed out, over all uses of the slot
+    int* finished = claimed + kPsJobs;                                               // [kPsJobs] streams completed, likewise
+    uint64_t* bars = reinterpret_cast<uint64_t*>(finished + kPsJobs);
+    volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * S + 2 * kPsJobs);  // [0] dead, [2] jobs this CTA posted
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + S);
-    const uint32_t bar_jfull = smem_u32(bars + 2 * S), bar_jempty = bar_jfull + 8 * kPsJobs, bar_gdone = bar_jempty + 8 * kPsJobs;
+    const uint32_t bar_jfull = smem_u32(bars + 2 * S), bar_jempty = bar_jfull + 8 * kPsJobs;
     const uint32_t ring = smem_u32(smem);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -93,9 +101,9 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         for (int j = 0; j < kPsJobs; ++j) {
             mbar_init(bar_jfull + 8 * j, 1);
             mbar_init(bar_jempty + 8 * j, 1);
-            mbar_init(bar_gdone + 8 * j, NGW);
+            claimed[j] = 0, finished[j] = 0;
         }
-        flags[0] = 0, flags[1] = 0;
+        flags[0] = 0, flags[1] = 0, flags[2] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -137,13 +145,23 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 }
             }
         }
-    } else if (warp <= nsw) {
+    } else {
+      // one job to the gather warps (first scorer thread): wait for a free slot, fill it, publish it
+      uint32_t pslot = 0, puse = 0;
+      auto post_job = [&](int bh, float M, float L) {
+          if (puse > 0 && !mbar_wait_bounded(bar_jempty + 8 * pslot, (puse - 1) & 1, flags)) return;
+          jobs[pslot].bh = bh, jobs[pslot].M = M, jobs[pslot].L = L, jobs[pslot].seq = (int)puse;
+          mbar_arrive(bar_jfull + 8 * pslot);
+          if (++pslot == kPsJobs) pslot = 0, ++puse;
+      };
+      int help_job = -1;   // scorer warps: the job they join once they have no K rows left
+      if (warp <= nsw) {
         // ---------------- scorers ----------------
         const int ctid = tid - 32;
         const int g = ctid / LPR, li = ctid % LPR;
         const int myrow = transposed_row<LPR, RB>(li);                  // which of a batch's RB rows this lane ends up holding
         const bool store_lane = (li % (LPR / RB)) == 0;                 // one lane per (group, row) writes the score
-        uint32_t stage = 0, phase = 0, jslot = 0, juse = 0;
+        uint32_t stage = 0, phase = 0;
         const unsigned char* qbase = static_cast<const unsigned char*>(P.q);
         uint4 qraw[VPL];
 #pragma unroll
@@ -155,13 +173,6 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         auto score_of = [&](float dot) -> float {
             if (P.round_like_torch) return Elem<T>::round(Elem<T>::round(dot) * P.scale);
             return dot * P.scale;
-        };
-        // one job to the gather warps (scorer thread 0): wait for a free slot, fill it, publish it
-        auto post_job = [&](int bh, float M, float L) {
-            if (juse > 0 && !mbar_wait_bounded(bar_jempty + 8 * jslot, (juse - 1) & 1, flags)) return;
-            jobs[jslot].bh = bh, jobs[jslot].M = M, jobs[jslot].L = L;
-            mbar_arrive(bar_jfull + 8 * jslot);
-            if (++jslot == kPsJobs) jslot = 0, ++juse;
         };
         long long u = u0;
         int rbuf = 0;   // which half of `red` this segment uses
@@ -341,168 +352,202 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
             }
             u += j1 - j0;
         }
-        if (tid == 32) post_job(-1, 0.f, 0.f);   // no more jobs from this CTA
-    } else {
-        // ---------------- gatherers ----------------
-        const int gw = warp - 1 - nsw;
+        // out of K rows: the ring is idle once every scorer warp is here; join the gather of the job posted last
+        if (tid == 32) flags[2] = (int)(puse * kPsJobs + pslot);
+        named_bar_sync(1, nct);
+        help_job = flags[2] - 1;
+      }
+      // ---------------- gather: the gather warps take every job, the scorer warps the last one ----------------
+      {
+        const bool helper = warp <= nsw;
         const int gl = lane / LPR, li = lane % LPR;
         // Survivors of a round, in row order.  16-bit tensors: one word per survivor (row offset within the round,
         // probability as the 16 bits it was rounded to), so a round covers 16 words of 32 rows; fp32: (row, probability).
         constexpr bool kPacked = sizeof(T) == 2;
         constexpr int WPR = kPacked ? 2 * kPsWordsPerRound : kPsWordsPerRound;
-        uint32_t* my_list = lists + gw * 2 * kPsListCap;
-        const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
-        const unsigned char* my_stage_p = gstage + gw * kPsStageBytes;
+        // a scorer warp's staging area and list come out of the K ring (as many warps as fit help)
+        const bool has_room = !helper || (size_t)warp * kPsHelperBytes <= (size_t)S * tile_bytes;
+        unsigned char* my_stage_p = helper ? smem + (size_t)(warp - 1) * kPsHelperBytes : gstage + (warp - 1 - nsw) * kPsStageBytes;
+        uint32_t* my_list = helper ? reinterpret_cast<uint32_t*>(my_stage_p + kPsStageBytes) : lists + (warp - 1 - nsw) * 2 * kPsListCap;
         const uint32_t my_stage = smem_u32(my_stage_p);
+        const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
         const uint64_t once = l2_policy_evict_first();   // surviving V rows are read once too
-        uint32_t jslot = 0, jphase = 0;
-        for (;;) {
-            if (!mbar_wait_bounded(bar_jfull + 8 * jslot, jphase, flags)) break;
-            const int bh = jobs[jslot].bh;
-            const float M = jobs[jslot].M, Lsum = jobs[jslot].L;
+        uint32_t gslot = 0, guse = 0;
+        if (helper) gslot = (uint32_t)(help_job < 0 ? 0 : help_job % kPsJobs), guse = (uint32_t)(help_job < 0 ? 0 : help_job / kPsJobs);
+        const bool idle = helper && (help_job < 0 || !has_room);
+        while (!idle) {
+            // a gather warp waits for the slot's next job; a helper's job was posted by its own CTA before the barrier above
+            if (!helper && !mbar_wait_bounded(bar_jfull + 8 * gslot, guse & 1, flags)) break;
+            const int bh = jobs[gslot].bh;
+            const float M = jobs[gslot].M, Lsum = jobs[gslot].L;
+            const int seq = jobs[gslot].seq;
             if (bh < 0) break;
-            const SampleRange sr = sample_range(P, bh / P.H);
-            // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
-            // the torch-rounding mode divides exactly like torch's softmax does
-            const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
-            const float theta = Elem<T>::round(P.p * inv);
-            auto prob_of = [&](float s) -> float {
-                if (prune) return Elem<T>::round(__expf(s - M) * inv);
-                return Elem<T>::round(expf(s - M) / Lsum);
-            };
-            const float* sc_row = P.scores + (size_t)bh * P.score_stride;
-            uint32_t* mask_row = P.kept_mask != nullptr ? P.kept_mask + (size_t)bh * P.mask_words : nullptr;
-            float2 acc2[VPL][E2];
+            if (seq == (int)guse) {   // otherwise the job this warp came for is finished and the slot holds a later one
+                const SampleRange sr = sample_range(P, bh / P.H);
+                // pruning follows the reference kernel's arithmetic (attention.cu:1113, 1122, 1125, 1185);
+                // the torch-rounding mode divides exactly like torch's softmax does
+                const float inv = prune ? __fdividef(1.f, Lsum + 1.e-6f) : 1.f / Lsum;
+                const float theta = Elem<T>::round(P.p * inv);
+                auto prob_of = [&](float sv) -> float {
+                    if (prune) return Elem<T>::round(__expf(sv - M) * inv);
+                    return Elem<T>::round(expf(sv - M) / Lsum);
+                };
+                const float* sc_row = P.scores + (size_t)bh * P.score_stride;
+                uint32_t* mask_row = P.kept_mask != nullptr ? P.kept_mask + (size_t)bh * P.mask_words : nullptr;
+                const int nwords = (sr.row >> 5) + 1;   // 32-row words that hold rows 0..sr.row
+                const int ticket_end = ((int)guse + 1) * kPsStreams;
+                // scores of a round's words, all loads before the first use (written by other threads: read at L2)
+                auto load_scores = [&](int w0, float (&sv)[WPR]) {
 #pragma unroll
-            for (int x = 0; x < VPL; ++x)
-#pragma unroll
-                for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
-
-            const int nwords = (sr.row >> 5) + 1;   // 32-row words that hold rows 0..sr.row
-            // scores of up to 16 words, all loads before the first use (written by other threads: read at L2)
-            auto load_scores = [&](int w0, float (&s)[WPR]) {
-#pragma unroll
-                for (int k = 0; k < WPR; ++k) {
-                    const int i = (w0 + k) * 32 + lane;
-                    s[k] = (w0 + k < nwords && i >= sr.first && i < sr.row) ? __ldcg(sc_row + i) : 0.f;
-                }
-            };
-            float s[WPR];
-            int w0 = gw * WPR;
-            if (w0 < nwords) load_scores(w0, s);
-            for (; w0 < nwords; w0 += NGW * WPR) {
-                int n = 0;
-                __syncwarp();   // the previous round's list has been consumed by every lane
-                // straight-line code, no branch per word: the 16 (8) words' chains of exponential, rounding and vote
-                // overlap; only the running count n links them
-#pragma unroll
-                for (int k = 0; k < WPR; ++k) {
-                    const int base = (w0 + k) * 32, i = base + lane;
-                    const bool cached = w0 + k < nwords && i >= sr.first && i < sr.row;
-                    const float pr = prob_of(s[k]);
-                    const bool keep = cached && (prune ? !Elem<T>::leq(pr, theta) : true);
-                    const unsigned bal = __ballot_sync(0xffffffffu, keep);
-                    if (mask_row != nullptr && lane == 0 && w0 + k < nwords)
-                        mask_row[w0 + k] = bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
-                    const int pos = n + __popc(bal & ((1u << lane) - 1u));
-                    if constexpr (kPacked) {
-                        if (keep) my_list[pos] = (uint32_t)(i - w0 * 32) | (Elem<T>::bits(pr) << 16);
-                    } else {
-                        if (keep) my_list[2 * pos] = (uint32_t)i, my_list[2 * pos + 1] = __float_as_uint(pr);
+                    for (int k = 0; k < WPR; ++k) {
+                        const int i = (w0 + k) * 32 + lane;
+                        sv[k] = (w0 + k < nwords && i >= sr.first && i < sr.row) ? __ldcg(sc_row + i) : 0.f;
                     }
-                    n += __popc(bal);
-                }
-                // This round's score lines (one per 32-row word; every lane has used its values by now) are not needed
-                // again: spare HBM their write-back.  The word of the new token's row is read once more and left alone.
-                if (lane < WPR && w0 + lane < nwords - 1) l2_discard_line(sc_row + (size_t)(w0 + lane) * 32);
-                // the next round's scores travel while this round's V rows are fetched
-                if (w0 + NGW * WPR < nwords) load_scores(w0 + NGW * WPR, s);
-                __syncwarp();
-                // survivors in row order; lane group gl takes entries gl, gl + GPW, ...; a batch of SROWS rows is
-                // copied into the warp's staging area (every lane its own 16-byte pieces), then accumulated
-                for (int base = 0; base < n; base += SROWS) {
-#pragma unroll
-                    for (int st = 0; st < STEPS; ++st) {
-                        const int e = base + st * GPW + gl;
-                        if (e < n) {
-                            const int row = kPacked ? w0 * 32 + (int)(my_list[e] & 0xffffu) : (int)my_list[2 * e];
-                            const unsigned char* src = vc + cache_row_offset(P, bh, row, ROWB);
-#pragma unroll
-                            for (int x = 0; x < VPL; ++x)
-                                if (kAllLanes || li + x * LPR < VPR)
-                                    cp_async_16_hint(my_stage + (uint32_t)((st * GPW + gl) * ROWB + (li + x * LPR) * 16), src + (li + x * LPR) * 16, once);
+                };
+                for (;;) {
+                    // claim the job's next stream (tickets count over all uses of the slot, so a warp that comes late
+                    // can never take one of a later job by mistake)
+                    int strm = -1;
+                    if (lane == 0) {
+                        int cur = *reinterpret_cast<volatile int*>(claimed + gslot);
+                        while (cur < ticket_end) {
+                            const int old = atomicCAS(claimed + gslot, cur, cur + 1);
+                            if (old == cur) {
+                                strm = cur - (int)guse * kPsStreams;
+                                break;
+                            }
+                            cur = old;
                         }
                     }
-                    cp_async_wait_all();
+                    strm = __shfl_sync(0xffffffffu, strm, 0);
+                    if (strm < 0) break;
+                    float2 acc2[VPL][E2];
 #pragma unroll
-                    for (int st = 0; st < STEPS; ++st) {
-                        const int e = base + st * GPW + gl;
-                        if (e < n) {
-                            const float pe = kPacked ? Elem<T>::from_bits(my_list[e] >> 16) : __uint_as_float(my_list[2 * e + 1]);
-                            const float2 p2 = make_float2(pe, pe);
+                    for (int x = 0; x < VPL; ++x)
 #pragma unroll
-                            for (int x = 0; x < VPL; ++x)
-                                if (kAllLanes || li + x * LPR < VPR) {
-                                    float2 v2[E2];
-                                    Elem<T>::unpack2(*reinterpret_cast<const uint4*>(my_stage_p + (st * GPW + gl) * ROWB + (li + x * LPR) * 16), v2);
+                        for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
+                    float sv[WPR];
+                    int w0 = strm * WPR;
+                    if (w0 < nwords) load_scores(w0, sv);
+                    for (; w0 < nwords; w0 += kPsStreams * WPR) {
+                        int n = 0;
+                        __syncwarp();   // the previous round's list has been consumed by every lane
+                        // straight-line code, no branch per word: the 16 (8) words' chains of exponential, rounding and vote
+                        // overlap; only the running count n links them
 #pragma unroll
-                                    for (int e2 = 0; e2 < E2; ++e2) acc2[x][e2] = __ffma2_rn(p2, v2[e2], acc2[x][e2]);
+                        for (int k = 0; k < WPR; ++k) {
+                            const int base = (w0 + k) * 32, i = base + lane;
+                            const bool cached = w0 + k < nwords && i >= sr.first && i < sr.row;
+                            const float pr = prob_of(sv[k]);
+                            const bool keep = cached && (prune ? !Elem<T>::leq(pr, theta) : true);
+                            const unsigned bal = __ballot_sync(0xffffffffu, keep);
+                            if (mask_row != nullptr && lane == 0 && w0 + k < nwords)
+                                mask_row[w0 + k] = bal | ((sr.row >= base && sr.row < base + 32) ? (1u << (sr.row - base)) : 0u);
+                            const int pos = n + __popc(bal & ((1u << lane) - 1u));
+                            if constexpr (kPacked) {
+                                if (keep) my_list[pos] = (uint32_t)(i - w0 * 32) | (Elem<T>::bits(pr) << 16);
+                            } else {
+                                if (keep) my_list[2 * pos] = (uint32_t)i, my_list[2 * pos + 1] = __float_as_uint(pr);
+                            }
+                            n += __popc(bal);
+                        }
+                        // This round's score lines (one per 32-row word; every lane has used its values by now) are not needed
+                        // again: spare HBM their write-back.  The word of the new token's row is read once more and left alone.
+                        if (lane < WPR && w0 + lane < nwords - 1) l2_discard_line(sc_row + (size_t)(w0 + lane) * 32);
+                        // the next round's scores travel while this round's V rows are fetched
+                        if (w0 + kPsStreams * WPR < nwords) load_scores(w0 + kPsStreams * WPR, sv);
+                        __syncwarp();
+                        // survivors in row order; lane group gl takes entries gl, gl + GPW, ...; a batch of SROWS rows is
+                        // copied into the warp's staging area (every lane its own 16-byte pieces), then accumulated
+                        for (int base = 0; base < n; base += SROWS) {
+#pragma unroll
+                            for (int st = 0; st < STEPS; ++st) {
+                                const int e = base + st * GPW + gl;
+                                if (e < n) {
+                                    const int row = kPacked ? w0 * 32 + (int)(my_list[e] & 0xffffu) : (int)my_list[2 * e];
+                                    const unsigned char* src = vc + cache_row_offset(P, bh, row, ROWB);
+#pragma unroll
+                                    for (int x = 0; x < VPL; ++x)
+                                        if (kAllLanes || li + x * LPR < VPR)
+                                            cp_async_16_hint(my_stage + (uint32_t)((st * GPW + gl) * ROWB + (li + x * LPR) * 16), src + (li + x * LPR) * 16, once);
                                 }
+                            }
+                            cp_async_wait_all();
+#pragma unroll
+                            for (int st = 0; st < STEPS; ++st) {
+                                const int e = base + st * GPW + gl;
+                                if (e < n) {
+                                    const float pe = kPacked ? Elem<T>::from_bits(my_list[e] >> 16) : __uint_as_float(my_list[2 * e + 1]);
+                                    const float2 p2 = make_float2(pe, pe);
+#pragma unroll
+                                    for (int x = 0; x < VPL; ++x)
+                                        if (kAllLanes || li + x * LPR < VPR) {
+                                            float2 v2[E2];
+                                            Elem<T>::unpack2(*reinterpret_cast<const uint4*>(my_stage_p + (st * GPW + gl) * ROWB + (li + x * LPR) * 16), v2);
+#pragma unroll
+                                            for (int e2 = 0; e2 < E2; ++e2) acc2[x][e2] = __ffma2_rn(p2, v2[e2], acc2[x][e2]);
+                                        }
+                                }
+                            }
                         }
                     }
-                }
-            }
-            // lane groups of the warp added in index order (butterfly over the group bits), then one
-            // vector per warp in shared memory
+                    // lane groups of the warp added in index order (butterfly over the group bits), then the
+                    // stream's vector to shared memory
 #pragma unroll
-            for (int off = LPR; off < 32; off <<= 1)
+                    for (int off = LPR; off < 32; off <<= 1)
 #pragma unroll
-                for (int x = 0; x < VPL; ++x)
+                        for (int x = 0; x < VPL; ++x)
 #pragma unroll
-                    for (int e = 0; e < E2; ++e) {
-                        acc2[x][e].x += __shfl_xor_sync(0xffffffffu, acc2[x][e].x, off);
-                        acc2[x][e].y += __shfl_xor_sync(0xffffffffu, acc2[x][e].y, off);
-                    }
-            float* mine = gred + ((size_t)jslot * NGW + gw) * DH;
-            if (gl == 0) {
+                            for (int e = 0; e < E2; ++e) {
+                                acc2[x][e].x += __shfl_xor_sync(0xffffffffu, acc2[x][e].x, off);
+                                acc2[x][e].y += __shfl_xor_sync(0xffffffffu, acc2[x][e].y, off);
+                            }
+                    float* mine = gred + ((size_t)gslot * kPsStreams + strm) * DH;
+                    if (gl == 0) {
 #pragma unroll
-                for (int x = 0; x < VPL; ++x) {
-                    const int vec = li + x * LPR;
-                    if (vec < VPR) {
+                        for (int x = 0; x < VPL; ++x) {
+                            const int vec = li + x * LPR;
+                            if (vec < VPR) {
 #pragma unroll
-                        for (int e = 0; e < E2; ++e) {
-                            mine[vec * EPV + 2 * e] = acc2[x][e].x;
-                            mine[vec * EPV + 2 * e + 1] = acc2[x][e].y;
+                                for (int e = 0; e < E2; ++e) {
+                                    mine[vec * EPV + 2 * e] = acc2[x][e].x;
+                                    mine[vec * EPV + 2 * e + 1] = acc2[x][e].y;
+                                }
+                            }
                         }
                     }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_gdone + 8 * jslot);
-            if (gw == 0) {
-                // the first gather warp adds the warps' vectors in order, then the new token, which is
-                // never pruned (attention.cu:1227-1256): append v, add P_t * v
-                const bool ready = mbar_wait_bounded(bar_gdone + 8 * jslot, jphase, flags);
-                const float pt = prob_of(__ldcg(sc_row + sr.row));
-                const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
-                const T* vnew = static_cast<const T*>(P.v) + (size_t)bh * DH;
-                T* vdst = reinterpret_cast<T*>(static_cast<unsigned char*>(P.v_cache) + row_off);
-                T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
-                if (ready) {
-                    for (int d = lane; d < DH; d += 32) {
-                        float A = 0.f;
+                    __threadfence_block();
+                    __syncwarp();
+                    int last = 0;
+                    if (lane == 0) last = atomicAdd(finished + gslot, 1) == ticket_end - 1;
+                    last = __shfl_sync(0xffffffffu, last, 0);
+                    if (last) {
+                        // the job's last stream: add the streams' vectors in order, then the new token, which is
+                        // never pruned (attention.cu:1227-1256): append v, add P_t * v
+                        __threadfence_block();
+                        const float pt = prob_of(__ldcg(sc_row + sr.row));
+                        const size_t row_off = cache_row_offset(P, bh, sr.row, ROWB);
+                        const T* vnew = static_cast<const T*>(P.v) + (size_t)bh * DH;
+                        T* vdst = reinterpret_cast<T*>(static_cast<unsigned char*>(P.v_cache) + row_off);
+                        T* outp = static_cast<T*>(P.out) + (size_t)bh * DH;
+                        for (int d = lane; d < DH; d += 32) {
+                            float A = 0.f;
 #pragma unroll
-                        for (int w = 0; w < NGW; ++w) A += gred[((size_t)jslot * NGW + w) * DH + d];
-                        const T vd = vnew[d];
-                        vdst[d] = vd;
-                        Elem<T>::store(outp + d, fmaf(pt, Elem<T>::to_float(vd), A));
+                            for (int w = 0; w < kPsStreams; ++w) A += gred[((size_t)gslot * kPsStreams + w) * DH + d];
+                            const T vd = vnew[d];
+                            vdst[d] = vd;
+                            Elem<T>::store(outp + d, fmaf(pt, Elem<T>::to_float(vd), A));
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_jempty + 8 * gslot);   // the slot and its vectors are free again
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_jempty + 8 * jslot);   // the slot and its vectors are free again
             }
-            if (++jslot == kPsJobs) jslot = 0, jphase ^= 1;
+            if (helper) break;
+            if (++gslot == kPsJobs) gslot = 0, ++guse;
         }
+      }
+      if (tid == 32) post_job(-1, 0.f, 0.f);   // no more jobs from this CTA
     }
     __syncthreads();
     if (tid == 0 && flags[0]) atomicOr(P.status, kStatusWaitTimeout);
