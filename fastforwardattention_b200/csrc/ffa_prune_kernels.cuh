@@ -305,12 +305,20 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
             for (int base = 0; base < n; base += RB * NG) {
                 uint4 raw[RB][VPL];
                 float pr[RB];
+                // lane uu of a group looks up row uu of the group's batch and its probability (one exponential per
+                // row, not one per lane); shuffles hand both to the whole group
+                int row_mine = c0;
+                float pr_mine = 0.f;
+                if (li < RB && base + li * NG + g < n) {
+                    row_mine = list_idx[base + li * NG + g];
+                    pr_mine = prob_of(sc[row_mine - c0]);
+                }
 #pragma unroll
                 for (int uu = 0; uu < RB; ++uu) {
                     const int idx = base + uu * NG + g;
                     const bool okr = idx < n;
-                    const int row = okr ? list_idx[idx] : c0;
-                    pr[uu] = okr ? prob_of(sc[row - c0]) : 0.f;
+                    const int row = __shfl_sync(0xffffffffu, row_mine, (lane - li) + uu);
+                    pr[uu] = __shfl_sync(0xffffffffu, pr_mine, (lane - li) + uu);
                     const size_t roff = okr ? cache_row_offset(P, bh, row, ROWB) : 0;
 #pragma unroll
                     for (int x = 0; x < VPL; ++x) {
