@@ -145,17 +145,17 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 }
             }
         }
-    } else {
-      // one job to the gather warps (first scorer thread): wait for a free slot, fill it, publish it
-      uint32_t pslot = 0, puse = 0;
-      auto post_job = [&](int bh, float M, float L) {
-          if (puse > 0 && !mbar_wait_bounded(bar_jempty + 8 * pslot, (puse - 1) & 1, flags)) return;
-          jobs[pslot].bh = bh, jobs[pslot].M = M, jobs[pslot].L = L, jobs[pslot].seq = (int)puse;
-          mbar_arrive(bar_jfull + 8 * pslot);
-          if (++pslot == kPsJobs) pslot = 0, ++puse;
-      };
-      int help_job = -1;   // scorer warps: the job they join once they have no K rows left
-      if (warp <= nsw) {
+    }
+    // one job to the gather warps (first scorer thread): wait for a free slot, fill it, publish it
+    uint32_t pslot = 0, puse = 0;
+    auto post_job = [&](int bh, float M, float L) {
+        if (puse > 0 && !mbar_wait_bounded(bar_jempty + 8 * pslot, (puse - 1) & 1, flags)) return;
+        jobs[pslot].bh = bh, jobs[pslot].M = M, jobs[pslot].L = L, jobs[pslot].seq = (int)puse;
+        mbar_arrive(bar_jfull + 8 * pslot);
+        if (++pslot == kPsJobs) pslot = 0, ++puse;
+    };
+    int help_job = -1;   // scorer warps: the job they join once they have no K rows left
+    if (warp >= 1 && warp <= nsw) {
         // ---------------- scorers ----------------
         const int ctid = tid - 32;
         const int g = ctid / LPR, li = ctid % LPR;
@@ -356,9 +356,9 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
         if (tid == 32) flags[2] = (int)(puse * kPsJobs + pslot);
         named_bar_sync(1, nct);
         help_job = flags[2] - 1;
-      }
-      // ---------------- gather: the gather warps take every job, the scorer warps the last one ----------------
-      {
+    }
+    // ---------------- gather: the gather warps take every job, the scorer warps the last one ----------------
+    if (warp >= 1) {
         const bool helper = warp <= nsw;
         const int gl = lane / LPR, li = lane % LPR;
         // Survivors of a round, in row order.  16-bit tensors: one word per survivor (row offset within the round,
@@ -546,9 +546,8 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
             if (helper) break;
             if (++gslot == kPsJobs) gslot = 0, ++guse;
         }
-      }
-      if (tid == 32) post_job(-1, 0.f, 0.f);   // no more jobs from this CTA
     }
+    if (tid == 32) post_job(-1, 0.f, 0.f);   // no more jobs from this CTA
     __syncthreads();
     if (tid == 0 && flags[0]) atomicOr(P.status, kStatusWaitTimeout);
 }
