@@ -50,10 +50,10 @@ constexpr int kSmemReservePerCta = 1024;  // the driver keeps 1 KB per resident 
 // 48.9 us in favour of the aligned cut; 8 K tokens 603 vs 594 us against it)
 constexpr long long kAlignedBelowUnitsPerSlot = 200;
 // pruned steps that stream at least this many bytes of K take the streaming kernel when the score scratch is bound
-// (5 % of the V rows kept; streaming vs cluster kernel: fp16 x 64, 320 pairs, 1256 tokens = 51 MB: 25.8 vs 18.8 us;
-// 134-168 MB, four shapes: 39.3-61.5 vs 32.6-60.3 us; bf16 x 128, 1024 pairs: 1 K tokens = 268 MB 58.4 vs 61.0 us,
-// 2 K 102 vs 107 us, 4 K 190 vs 221 us, 8 K 359 vs 428 us, 32 K 1441 vs 1799 us)
-constexpr double kStreamPruneAboveBytes = 250e6;
+// (5 % of the V rows kept; streaming vs cluster kernel: fp16 x 64, 320 pairs, 1256 tokens = 51 MB: 27.2 vs 17.5 us;
+// 134 MB, three shapes: 42.5-45.2 vs 31.2-37.6 us; 268 MB, five shapes: 52.3-67.3 vs 53.3-63.5 us; bf16 x 128, 1024
+// pairs: 2 K tokens = 537 MB 105.3 vs 106.4 us, 4 K 193 vs 212 us, 8 K 342 vs 428 us, 32 K 1393 vs 1799 us)
+constexpr double kStreamPruneAboveBytes = 500e6;
 
 }  // namespace
 

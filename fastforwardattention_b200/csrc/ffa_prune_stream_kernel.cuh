@@ -396,6 +396,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 uint32_t* mask_row = P.kept_mask != nullptr ? P.kept_mask + (size_t)bh * P.mask_words : nullptr;
                 const int nwords = (sr.row >> 5) + 1;   // 32-row words that hold rows 0..sr.row
                 const int ticket_end = ((int)guse + 1) * kPsStreams;
+                const int active = min(kPsStreams, (nwords + WPR - 1) / WPR);   // streams that have rows; the rest are empty
                 // scores of a round's words, all loads before the first use (written by other threads: read at L2)
                 auto load_scores = [&](int w0, float (&sv)[WPR]) {
 #pragma unroll
@@ -407,19 +408,22 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                 for (;;) {
                     // claim the job's next stream (tickets count over all uses of the slot, so a warp that comes late
                     // can never take one of a later job by mistake)
-                    int strm = -1;
+                    int strm = -1, took = 0;
                     if (lane == 0) {
                         int cur = *reinterpret_cast<volatile int*>(claimed + gslot);
                         while (cur < ticket_end) {
-                            const int old = atomicCAS(claimed + gslot, cur, cur + 1);
+                            const int idx = cur - (int)guse * kPsStreams;
+                            const int n_take = idx >= active ? ticket_end - cur : 1;   // the empty streams go in one claim
+                            const int old = atomicCAS(claimed + gslot, cur, cur + n_take);
                             if (old == cur) {
-                                strm = cur - (int)guse * kPsStreams;
+                                strm = idx, took = n_take;
                                 break;
                             }
                             cur = old;
                         }
                     }
                     strm = __shfl_sync(0xffffffffu, strm, 0);
+                    took = __shfl_sync(0xffffffffu, took, 0);
                     if (strm < 0) break;
                     float2 acc2[VPL][E2];
 #pragma unroll
@@ -503,7 +507,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                                 acc2[x][e].y += __shfl_xor_sync(0xffffffffu, acc2[x][e].y, off);
                             }
                     float* mine = gred + ((size_t)gslot * kPsStreams + strm) * DH;
-                    if (gl == 0) {
+                    if (gl == 0 && strm < active) {
 #pragma unroll
                         for (int x = 0; x < VPL; ++x) {
                             const int vec = li + x * LPR;
@@ -519,7 +523,7 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                     __threadfence_block();
                     __syncwarp();
                     int last = 0;
-                    if (lane == 0) last = atomicAdd(finished + gslot, 1) == ticket_end - 1;
+                    if (lane == 0) last = atomicAdd(finished + gslot, took) + took == ticket_end;
                     last = __shfl_sync(0xffffffffu, last, 0);
                     if (last) {
                         // the job's last stream: add the streams' vectors in order, then the new token, which is
@@ -533,7 +537,8 @@ __global__ void __launch_bounds__(32 * (1 + ps_max_scorer_warps(DH) + kPsGatherW
                         for (int d = lane; d < DH; d += 32) {
                             float A = 0.f;
 #pragma unroll
-                            for (int w = 0; w < kPsStreams; ++w) A += gred[((size_t)gslot * kPsStreams + w) * DH + d];
+                            for (int w = 0; w < kPsStreams; ++w)
+                                if (w < active) A += gred[((size_t)gslot * kPsStreams + w) * DH + d];
                             const T vd = vnew[d];
                             vdst[d] = vd;
                             Elem<T>::store(outp + d, fmaf(pt, Elem<T>::to_float(vd), A));
