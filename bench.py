@@ -378,7 +378,7 @@ def main():
         gather_kind = "peer-memory kernel" if peer_ok else "nccl all_gather_into_tensor"
     shape = engines[0].launch_shape(w.max_len - 1)
 
-    total = args.warmup + args.steps
+    total = max(args.warmup + args.steps, nrep)   # the end-to-end legs warm every replica once
     qkv_d = device_step_qkv(w, total, dev)
     qkv_h = qkv_d.cpu().pin_memory()
     out_d = torch.empty(w.B, w.H, w.Dh, dtype=w.dtype, device=dev)
@@ -462,7 +462,7 @@ def main():
 
     # ---- leg 2: end to end with host buffers (upload, attention, gather, download, sync every step) ----
     def timed_leg(step):
-        for s in range(min(3, args.warmup)):
+        for s in range(max(min(3, args.warmup), nrep)):   # every replica's step (and its CUDA graph) has run once
             step(s)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
