@@ -596,8 +596,12 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     // launch is fixed cost).  Large steps: the streaming kernel (a persistent grid keeps HBM busy; the cluster
     // kernel pays its start, two cluster barriers and the merge once per CTA).  The streaming kernel needs
     // the score scratch; without it the cluster kernel runs whenever it fits.
+    // With every row kept (torch rounding, p = 0) the cluster kernel streams the V tiles through its ring like the K
+    // tiles and wins at every size it fits (bf16 x 128, 1024 pairs, 512 / 2 K / 8 K / 32 K tokens: 52 / 167 / 651 /
+    // 2848 us against 138 / 238 / 921 / 3566 us for the streaming kernel, whose gather warps fetch row by row).
     const double k_bytes = (double)BH * cap * plan->Dh * elem_size(plan->dtype);
-    const bool stream_first = plan->prune_path == 2 || (plan->prune_path == 0 && plan->scores != nullptr && k_bytes >= kStreamPruneAboveBytes);
+    const bool stream_first = plan->prune_path == 2 ||
+                              (plan->prune_path == 0 && plan->scores != nullptr && p > 0.f && k_bytes >= kStreamPruneAboveBytes);
     if (twopass && !stream_first) {
         FfaStepParams F = P;
         int smem_f = 0;

@@ -77,27 +77,39 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
         return dot * P.scale;
     };
 
+    // The copy thread's ring position and the compute warps' (each side walks the same sequence of tiles: the K
+    // tiles of the slice, then -- when every row is kept -- its V tiles).
+    uint32_t pstage = 0, puse = 0;     // thread 0
+    uint32_t cstage = 0, cphase = 0;   // compute warps
+    // Issues tile j of the slice from `cache` (thread 0).  Rows of one page are contiguous; a tile that crosses a
+    // page boundary arrives as one copy per page, all counted on the same barrier (contiguous caches: one copy).
+    auto issue_tile = [&](const unsigned char* cache, int j) -> bool {
+        if (puse > 0 && !mbar_wait_bounded(bar_empty + 8 * pstage, (puse - 1) & 1, flags)) return false;
+        const int run_rows = P.page_table != nullptr ? P.page_rows : P.Lmax;
+        const int n = min(R, nrows - j * R);
+        mbar_expect_tx(bar_full + 8 * pstage, (uint32_t)n * ROWB);
+        for (int done = 0; done < n;) {
+            const int row = lo + j * R + done;
+            const int seg = min(n - done, run_rows - row % run_rows);
+            bulk_copy_g2s(ring + pstage * tile_bytes + (uint32_t)done * ROWB, cache + cache_row_offset(P, bh, row, ROWB),
+                          (uint32_t)seg * ROWB, bar_full + 8 * pstage);
+            done += seg;
+        }
+        if (++pstage == (uint32_t)S) pstage = 0, ++puse;
+        return true;
+    };
+    // Every row kept (the torch-rounding mode): the value phase streams the slice's V tiles through the same ring
+    // instead of gathering rows.  The first `dense_ahead` of them are requested as soon as the K tiles release
+    // their buffers, so they travel while the statistics are exchanged.
+    const bool dense = !prune;
+    const int dense_ahead = dense ? min(S, ntiles) : 0;
+
     // ---------------- phase 1: scores of this slice into shared memory ----------------
     if (warp == 0) {
         if (tid == 0) {
-            const unsigned char* kc = static_cast<const unsigned char*>(P.k_cache);
-            // rows of one page are contiguous; a tile that crosses a page boundary arrives as
-            // one copy per page, all counted on the same barrier (contiguous caches: one copy)
-            const int run_rows = P.page_table != nullptr ? P.page_rows : P.Lmax;
-            uint32_t stage = 0, use = 0;
-            for (int j = 0; j < ntiles; ++j) {
-                if (use > 0 && !mbar_wait_bounded(bar_empty + 8 * stage, (use - 1) & 1, flags)) break;
-                const int n = min(R, nrows - j * R);
-                mbar_expect_tx(bar_full + 8 * stage, (uint32_t)n * ROWB);
-                for (int done = 0; done < n;) {
-                    const int row = lo + j * R + done;
-                    const int seg = min(n - done, run_rows - row % run_rows);
-                    bulk_copy_g2s(ring + stage * tile_bytes + (uint32_t)done * ROWB, kc + cache_row_offset(P, bh, row, ROWB),
-                                  (uint32_t)seg * ROWB, bar_full + 8 * stage);
-                    done += seg;
-                }
-                if (++stage == (uint32_t)S) stage = 0, ++use;
-            }
+            bool ok = true;
+            for (int j = 0; ok && j < ntiles; ++j) ok = issue_tile(static_cast<const unsigned char*>(P.k_cache), j);
+            for (int j = 0; ok && j < dense_ahead; ++j) ok = issue_tile(static_cast<const unsigned char*>(P.v_cache), j);
         }
     } else {
         // the new token's k is needed after the score loop and its v after the gather: ask for their lines now
@@ -111,11 +123,10 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
 #pragma unroll
             for (int e = 1; e < EPV; e += 2) q2[x][e >> 1] = make_float2(qf[x][e - 1], qf[x][e]);
 
-        uint32_t stage = 0, phase = 0;
         for (int j = 0; j < ntiles; ++j) {
             const int n = min(R, nrows - j * R);
-            const bool ready = mbar_wait_bounded(bar_full + 8 * stage, phase, flags);
-            const unsigned char* ks = smem + (size_t)stage * tile_bytes;
+            const bool ready = mbar_wait_bounded(bar_full + 8 * cstage, cphase, flags);
+            const unsigned char* ks = smem + (size_t)cstage * tile_bytes;
             float* sc_tile = sc + (lo - c0) + j * R;
             if (ready) {
                 // RB rows per lane group at a time, loads first; FULL: every row of the batch exists
@@ -169,8 +180,8 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
                 if (base < n) batch(std::false_type{}, base);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
-            if (++stage == (uint32_t)S) stage = 0, phase ^= 1;
+            if (lane == 0) mbar_arrive(bar_empty + 8 * cstage);
+            if (++cstage == (uint32_t)S) cstage = 0, cphase ^= 1;
         }
         // the new token: score against k, append k at row sr.row (attention.cu:900-958)
         if (owns_new) {
@@ -263,7 +274,65 @@ __global__ void __launch_bounds__(kFusedThreads) ffa_prune_cluster_kernel(const 
         for (int e = 0; e < E2; ++e) acc2[x][e] = make_float2(0.f, 0.f);
     const unsigned char* vc = static_cast<const unsigned char*>(P.v_cache);
     const int hi_mask = sr.ok ? min(c0 + chunk, sr.row + 1) : c0;   // rows whose mask bit this slice writes
-    for (int sub = c0; sub < hi_mask; sub += kFusedListCap) {
+    if (dense) {
+        if (warp == 0) {
+            // the rest of the V tiles; and the kept mask: every cached row of the slice and the new token
+            if (tid == 0) {
+                bool ok = true;
+                for (int j = dense_ahead; ok && j < ntiles; ++j) ok = issue_tile(vc, j);
+            }
+            if (P.kept_mask != nullptr)
+                for (int base = c0 + 32 * lane; base < hi_mask; base += 32 * 32) {
+                    unsigned bits = 0u;
+                    for (int i = max(base, lo); i < min(base + 32, hi); ++i) bits |= 1u << (i - base);
+                    if (sr.row >= base && sr.row < base + 32) bits |= 1u << (sr.row - base);
+                    P.kept_mask[(size_t)bh * P.mask_words + (base >> 5)] = bits;
+                }
+        } else {
+            for (int j = 0; j < ntiles; ++j) {
+                const int n = min(R, nrows - j * R);
+                const bool ready = mbar_wait_bounded(bar_full + 8 * cstage, cphase, flags);
+                const unsigned char* vs = smem + (size_t)cstage * tile_bytes;
+                const float* sc_tile = sc + (lo - c0) + j * R;
+                if (ready) {
+                    for (int base = 0; base < n; base += RB * NG) {
+                        // lane uu of a group computes the probability of row uu of the group's batch; shuffles share it
+                        const int r_mine = base + li * NG + g;
+                        const float pr_mine = (li < RB && r_mine < n) ? prob_of(sc_tile[r_mine]) : 0.f;
+                        uint4 raw[RB][VPL];
+                        float pr[RB];
+#pragma unroll
+                        for (int uu = 0; uu < RB; ++uu) {
+                            const int r = min(base + uu * NG + g, n - 1);   // rows past the tile: probability 0 on a real row
+                            pr[uu] = __shfl_sync(0xffffffffu, pr_mine, (lane - li) + uu);
+#pragma unroll
+                            for (int x = 0; x < VPL; ++x)
+                                if (kAllLanes || li + x * LPR < VPR)
+                                    raw[uu][x] = *reinterpret_cast<const uint4*>(vs + (size_t)r * ROWB + (li + x * LPR) * 16);
+                        }
+#pragma unroll
+                        for (int uu = 0; uu < RB; ++uu) {
+                            if (base + uu * NG + g < n) {
+                                const float2 p2 = make_float2(pr[uu], pr[uu]);
+#pragma unroll
+                                for (int x = 0; x < VPL; ++x)
+                                    if (kAllLanes || li + x * LPR < VPR) {
+                                        float2 v2[E2];
+                                        Elem<T>::unpack2(raw[uu][x], v2);
+#pragma unroll
+                                        for (int e = 0; e < E2; ++e) acc2[x][e] = __ffma2_rn(p2, v2[e], acc2[x][e]);
+                                    }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * cstage);
+                if (++cstage == (uint32_t)S) cstage = 0, cphase ^= 1;
+            }
+        }
+    }
+    for (int sub = c0; !dense && sub < hi_mask; sub += kFusedListCap) {
         // Survivors are listed in row order (ballots first, then a prefix over the 32-row
         // words), so the order of the floating-point sums below never depends on timing.
         __syncthreads();
