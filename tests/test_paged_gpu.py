@@ -158,3 +158,37 @@ def test_torch_rounding_mode_over_pages():
         b = ffa.attention(q, k, v, Dh ** -0.5, Lp + i, 0)
         assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -9
     assert seqs.engine.device_status() == 0
+
+
+@pytest.mark.parametrize("dt,Dh,pr", [(torch.float16, 64, 128), (torch.bfloat16, 128, 128), (torch.float32, 80, 128)])
+def test_torch_rounding_mode_ragged_over_small_pages(dt, Dh, pr):
+    """Every row kept: the cluster kernel streams the V tiles of a slice through its ring.  Ragged
+    sequences over 128-row pages handed out in a scrambled order, pool poisoned with NaN outside the
+    sequences' rows: tiles that start between page boundaries arrive as one copy per page.  Checked
+    against the same-dtype torch function (the mode's target) on every sequence."""
+    from fastforwardattention_b200 import PagedFastForwardAttn, PagePool
+
+    g = torch.Generator().manual_seed(5 + Dh)
+    B, H, Lp = 4, 3, 900
+    lengths = [0, pr - 1, 300, 900]
+    K = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    V = torch.randn(B, H, Lp, Dh, generator=g).to(dt)
+    pool = PagePool(num_pages=24, heads=H, head_dim=Dh, dtype=dt, device="cuda", page_rows=pr)
+    pool._free = [7, 3, 19, 0, 11, 14, 5, 9, 2, 17, 12, 1, 15, 4, 18, 8, 13, 6, 16, 10, 23, 20, 22, 21]
+    pool.k.fill_(float("nan"))
+    pool.v.fill_(float("nan"))
+    seqs = PagedFastForwardAttn(pool, K, V, max_len=1024, lengths=lengths)
+    seqs.engine.set_mode("round_like_torch")
+    Ks = [K[b, :, :lengths[b]] for b in range(B)]
+    Vs = [V[b, :, :lengths[b]] for b in range(B)]
+    gate = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 2e-3}[dt]
+    for i in range(3):
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        out = seqs.attention(q.cuda(), k.cuda(), v.cuda(), Dh ** -0.5).cpu()
+        for b in range(B):
+            Ks[b] = torch.cat([Ks[b], k[b]], dim=1)
+            Vs[b] = torch.cat([Vs[b], v[b]], dim=1)
+            same = O.torch_attn_func(q[b].view(H, 1, Dh), Ks[b], Vs[b], Dh ** -0.5)[:, 0]
+            err = (out[b].float() - same.float()).abs().max().item()
+            assert err <= gate, (b, i, err)
+    assert seqs.engine.device_status() == 0
