@@ -189,9 +189,10 @@ struct FastForwardAttn {
             if (!kept_mask.defined()) kept_mask = torch::zeros({B, H, (Lmax + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
             mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
         }
-        // pruned and torch-rounding steps of any size go through an fp32 score scratch (4 bytes per cache row,
-        // under 1 % of the caches): bound the first time such a step is asked for
-        if ((p > 0.0 || mode == FFA_MODE_ROUND_LIKE_TORCH) && !has_scores) bind_workspace(true);
+        // large pruned steps go through an fp32 score scratch (4 bytes per cache row, under 1 % of the caches): bound
+        // the first time a pruned step is asked for.  (Torch-rounding steps keep their scores in shared memory; the
+        // retry below binds the scratch for the rare shape that does not fit there.)
+        if (p > 0.0 && !has_scores) bind_workspace(true);
         auto call = [&]() {
             return ffa_attention(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
                                  (float)softmax_scale, (int)t, seq_lengths ? sl.data_ptr<int>() : nullptr, right_or_no_padding,
@@ -485,7 +486,7 @@ struct PagedEngine {
                 kept_mask = torch::zeros({B, H, (max_pages * page_rows + 31) / 32}, torch::TensorOptions().dtype(torch::kInt).device(device));
             mask_ptr = reinterpret_cast<uint32_t*>(kept_mask.data_ptr());
         }
-        if ((p > 0.0 || mode == FFA_MODE_ROUND_LIKE_TORCH) && !has_scores) bind_workspace(true);
+        if (p > 0.0 && !has_scores) bind_workspace(true);   // torch-rounding steps keep their scores in shared memory
         auto call = [&]() {
             return ffa_attention_paged(plan, q.data_ptr(), k.data_ptr(), v.data_ptr(), kp.data_ptr(), vp.data_ptr(),
                                        table.data_ptr<int>(), (int)max_pages, (int)page_rows, out.data_ptr(), (float)softmax_scale,
