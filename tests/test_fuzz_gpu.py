@@ -99,3 +99,35 @@ def run_random_steps(seed, rng, dt, Dh, B, H, Lmax, force_launch):
             Vc[b, :, rows[b]] = v[b, :, 0]
         assert torch.equal(eng.k_cache.cpu(), Kc) and torch.equal(eng.v_cache.cpu(), Vc), (seed, "cache contents")
     assert eng.status() == 0
+
+
+@pytest.mark.parametrize("seed", range(300, 332))
+def test_random_torch_rounding_mode(seed):
+    """The torch-rounding mode on random shapes against its target, the same-dtype torch function:
+    fp32 within 2e-6, fp16 and bf16 within 2e-3; with and without a score scratch bound (the
+    scores stay in shared memory), planner's choice or the cluster kernel forced."""
+    rng = random.Random(seed)
+    dt = rng.choice(DTS)
+    Dh = rng.choice([64, 80, 128, 256])
+    B, H = rng.randint(1, 4), rng.randint(1, 6)
+    Lmax = rng.choice([1, 2, 9, 33, 100, 257, 700, 1300, 2100, 5000])
+    g = torch.Generator().manual_seed(5000 + seed)
+    Kc = torch.randn(B, H, Lmax, Dh, generator=g).to(dt)
+    Vc = torch.randn(B, H, Lmax, Dh, generator=g).to(dt)
+    eng = CAbiEngine(Kc, Vc, Lmax, with_scores=rng.random() < 0.5)
+    eng.set_mode(1)
+    eng.set_prune_path(rng.choice([0, 0, 1]))
+    scale = Dh ** -0.5
+    gate = {torch.float32: 2e-6, torch.float16: 2e-3, torch.bfloat16: 2e-3}[dt]
+    for step in range(2):
+        q, k, v = (torch.randn(B, H, 1, Dh, generator=g).to(dt) for _ in range(3))
+        t = rng.randint(0, Lmax - 1)
+        got = eng.attention(q, k, v, scale, t).cpu()
+        Kc[:, :, t] = k[:, :, 0]
+        Vc[:, :, t] = v[:, :, 0]
+        same = O.torch_attn_func(q.reshape(B * H, 1, Dh), Kc[:, :, :t + 1].reshape(B * H, t + 1, Dh),
+                                 Vc[:, :, :t + 1].reshape(B * H, t + 1, Dh), scale)[:, 0].reshape(B, H, Dh)
+        err = (got.float() - same.float()).abs().max().item()
+        assert err <= gate, (seed, dt, Dh, B, H, Lmax, t, err)
+        assert torch.equal(eng.k_cache.cpu(), Kc) and torch.equal(eng.v_cache.cpu(), Vc), (seed, "cache contents")
+    assert eng.status() == 0
