@@ -510,7 +510,7 @@ def main():
         achieved = sum(alg) / (ksum_ms * 1e-3) / 1e9          # per GPU: this rank's bytes over its kernel time
         per_launch_alg = sum(alg) / len(alg)
         kernel_name = ("ffa_stream_kernel (one-pass)" if w.p == 0 else
-                       "ffa_prune_stream_kernel" if w.B * w.H * w.max_len * w.Dh * es >= 500e6 else "ffa_prune_cluster_kernel")
+                       "ffa_prune_stream_kernel" if w.B * w.H * w.max_len * w.Dh * es >= 1e9 else "ffa_prune_cluster_kernel")
         line = {"metric": METRIC, "value": args.steps / (loop_ms * 1e-3), "unit": "steps/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": loop_ms / args.steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

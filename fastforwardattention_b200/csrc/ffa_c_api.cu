@@ -52,8 +52,11 @@ constexpr long long kAlignedBelowUnitsPerSlot = 200;
 // pruned steps that stream at least this many bytes of K take the streaming kernel when the score scratch is bound
 // (5 % of the V rows kept; streaming vs cluster kernel: fp16 x 64, 320 pairs, 1256 tokens = 51 MB: 27.2 vs 17.5 us;
 // 134 MB, three shapes: 42.5-45.2 vs 31.2-37.6 us; 268 MB, five shapes: 52.3-67.3 vs 53.3-63.5 us; bf16 x 128, 1024
-// pairs: 2 K tokens = 537 MB 105.3 vs 106.4 us, 4 K 193 vs 212 us, 8 K 342 vs 428 us, 32 K 1393 vs 1799 us)
-constexpr double kStreamPruneAboveBytes = 500e6;
+// pairs: 2 K tokens = 537 MB 105.3 vs 106.4 us, 4 K 193 vs 212 us, 8 K 342 vs 408 us, 32 K 1393 vs 1713 us).
+// The streaming kernel fetches survivors row by row and is slow when the threshold prunes little (nothing pruned: 2 K
+// tokens 234 vs 167 us, 8 K 920 vs 667 us -- the cluster kernel streams the V tiles of such slices), so it is the
+// default only where it can win by 9 % or more.
+constexpr double kStreamPruneAboveBytes = 1e9;
 
 }  // namespace
 

@@ -111,7 +111,7 @@ int ffa_plan_set_mode(ffa_plan_t* plan, int mode);
  * kernel: a persistent grid streams the K rows of all pairs, leaves fp32 scores in the
  * workspace's score scratch, and its gather warps fetch the surviving V rows of finished
  * pairs while the K stream goes on (any size).  0 (default) picks 2 for pruned steps (p > 0) that
- * stream at least 500 MB of K when the score scratch is bound, else 1 whenever a slice fits in shared
+ * stream at least 1 GB of K when the score scratch is bound, else 1 whenever a slice fits in shared
  * memory (with every row kept, i.e. torch rounding with p = 0, implementation 1 streams V tiles
  * instead of gathering rows and is the faster one at every size).  The reference does both phases in one CTA per (batch, head) (attention.cu:1077-1257),
  * which is what caps its sequence length. */
