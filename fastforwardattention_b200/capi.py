@@ -16,7 +16,7 @@ MODE_EXACT, MODE_ROUND_LIKE_TORCH = 0, 1
 SYMBOLS = ["ffa_cache_bytes", "ffa_cache_init", "ffa_plan_create", "ffa_plan_destroy", "ffa_plan_get_launch",
            "ffa_plan_set_launch", "ffa_plan_set_mode", "ffa_workspace_bytes", "ffa_workspace_bind", "ffa_attention",
            "ffa_device_status", "ffa_launch_count", "ffa_last_error", "ffa_attention_static_scratch", "ffa_static_scratch_status", "ffa_static_scratch_selftest_wait_timeout", "ffa_selftest_wait_timeout", "ffa_plan_set_prune_path", "ffa_plan_create_offline",
-           "ffa_plan_get_prune_launch", "ffa_cache_copy", "ffa_attention_paged", "ffa_peer_gather_bytes",
+           "ffa_plan_get_prune_launch", "ffa_plan_get_prune_path", "ffa_cache_copy", "ffa_attention_paged", "ffa_peer_gather_bytes",
            "ffa_peer_mem_alloc", "ffa_peer_mem_open", "ffa_peer_mem_close", "ffa_peer_mem_free", "ffa_peer_gather_attach",
            "ffa_peer_gather", "ffa_plan_set_cluster_merge", "ffa_peer_push_target"]
 
@@ -48,6 +48,7 @@ def lib() -> C.CDLL:
         L.ffa_plan_create.argtypes = [i, i, i, i, i, i, i, C.POINTER(vp)]
         L.ffa_plan_create_offline.argtypes = [i, i, i, i, i, i, i, i, i, C.POINTER(vp)]
         L.ffa_plan_get_prune_launch.argtypes = [vp, i] + [C.POINTER(i)] * 5
+        L.ffa_plan_get_prune_path.argtypes = [vp, i, C.c_float, i, C.POINTER(i)]
         L.ffa_plan_destroy.argtypes = [vp]
         L.ffa_plan_destroy.restype = None
         L.ffa_plan_get_launch.argtypes = [vp, i, C.POINTER(Launch)]

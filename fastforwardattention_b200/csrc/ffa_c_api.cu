@@ -320,6 +320,14 @@ bool plan_fused(const ffa_plan* p, int cap_rows, FfaStepParams* P, int* smem_out
     return true;
 }
 
+// Which two-pass kernel a step prefers: the streaming kernel when it is forced, or for pruned steps (p > 0) that stream at
+// least kStreamPruneAboveBytes of K while the score scratch is bound; else the cluster kernel (if its slices fit).
+bool prefers_stream(const ffa_plan* plan, int cap_rows, float p, bool have_scores)
+{
+    const double k_bytes = (double)plan->B * plan->H * cap_rows * plan->Dh * elem_size(plan->dtype);
+    return plan->prune_path == 2 || (plan->prune_path == 0 && have_scores && p > 0.f && k_bytes >= kStreamPruneAboveBytes);
+}
+
 // cudaOccupancyMaxActiveClusters for the one-pass kernel, remembered per launch shape (the query
 // costs tens of microseconds); 0 when the device will not say
 int max_active_clusters(ffa_plan* p, int threads, int smem, int cluster)
@@ -483,6 +491,19 @@ int ffa_plan_get_prune_launch(const ffa_plan_t* plan, int t, int* cluster, int* 
     return FFA_OK;
 }
 
+int ffa_plan_get_prune_path(const ffa_plan_t* plan, int t, float p, int with_scores, int* path)
+{
+    if (plan == nullptr || path == nullptr) return fail(FFA_ERR_ARG, "null pointer");
+    if (t < 0 || t >= plan->Lmax) return fail(FFA_ERR_RANGE, "t = %d outside [0, %d)", t, plan->Lmax);
+    FfaStepParams P;
+    std::memset(&P, 0, sizeof(P));
+    int smem = 0;
+    if (prefers_stream(plan, t, p, with_scores != 0)) *path = 2;
+    else if (plan->prune_path != 2 && plan_fused(plan, t, &P, &smem)) *path = 1;
+    else *path = with_scores ? 2 : 0;
+    return FFA_OK;
+}
+
 void ffa_plan_destroy(ffa_plan_t* plan) { delete plan; }
 
 int ffa_plan_get_launch(const ffa_plan_t* plan, int t, ffa_launch_t* launch)
@@ -581,7 +602,6 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     const bool paged = pages.table != nullptr;
     const bool twopass = p > 0.f || plan->mode == FFA_MODE_ROUND_LIKE_TORCH;
     const int cap = t;   // rows the unit list covers: every sample is at row t, or (per-sample lengths) at a row no greater than the bound t
-    const long long BH = (long long)plan->B * plan->H;
     FfaStepParams P;
     std::memset(&P, 0, sizeof(P));
     P.q = q, P.k = k, P.v = v, P.k_cache = k_cache, P.v_cache = v_cache, P.out = out;
@@ -602,9 +622,7 @@ int run_step(ffa_plan_t* plan, const void* q, const void* k, const void* v, void
     // With every row kept (torch rounding, p = 0) the cluster kernel streams the V tiles through its ring like the K
     // tiles and wins at every size it fits (bf16 x 128, 1024 pairs, 512 / 2 K / 8 K / 32 K tokens: 52 / 167 / 651 /
     // 2848 us against 138 / 238 / 921 / 3566 us for the streaming kernel, whose gather warps fetch row by row).
-    const double k_bytes = (double)BH * cap * plan->Dh * elem_size(plan->dtype);
-    const bool stream_first = plan->prune_path == 2 ||
-                              (plan->prune_path == 0 && plan->scores != nullptr && p > 0.f && k_bytes >= kStreamPruneAboveBytes);
+    const bool stream_first = prefers_stream(plan, cap, p, plan->scores != nullptr);
     if (twopass && !stream_first) {
         FfaStepParams F = P;
         int smem_f = 0;

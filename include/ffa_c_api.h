@@ -125,6 +125,10 @@ int ffa_plan_set_cluster_merge(ffa_plan_t* plan, int on);
  * would run instead (path 2, or no cluster shape fits). */
 int ffa_plan_get_prune_launch(const ffa_plan_t* plan, int t, int* cluster, int* chunk_rows, int* tile_rows, int* grid,
                               int* smem_bytes);
+/* Which implementation a step at row t with threshold p takes (p = 0: a torch-rounding step): 1 or 2 as in
+ * ffa_plan_set_prune_path, 0 when neither can run (the cluster kernel's slices do not fit in shared memory and no
+ * score scratch is bound).  with_scores: whether the workspace was sized with the score scratch. */
+int ffa_plan_get_prune_path(const ffa_plan_t* plan, int t, float p, int with_scores, int* path);
 
 /* Scratch the engine needs in device memory: split partials, arrival counters, the status
  * word and, when with_scores != 0 (needed for p > 0 and FFA_MODE_ROUND_LIKE_TORCH), one fp32

@@ -137,3 +137,29 @@ def test_fused_pruning_launch_rules():
         L, p = offline(capi.F16, 3, 5, 80, 501)
         c, chunk, r, grid, smem = prune_launch(L, p, t)
         assert c >= 1 and chunk % 32 == 0 and chunk * c >= t + 1 and r % 8 == 0 and grid == 15 * c
+
+
+def prune_path(L, p, t, thresh, with_scores=1):
+    v = C.c_int()
+    capi.check(L.ffa_plan_get_prune_path(p, t, thresh, with_scores, C.byref(v)))
+    return v.value
+
+
+def test_which_pruning_kernel_a_step_takes():
+    # config 4 (51 MB of K): the cluster kernel
+    L, p = offline(capi.F16, 10, 32, 64, 1256)
+    assert prune_path(L, p, 1255, 1e-3) == 1
+    # bf16 B32 H32 Dh128: 2 K tokens stream 537 MB of K (cluster kernel), 8 K tokens 2.1 GB (streaming kernel)
+    L, p = offline(capi.BF16, 32, 32, 128, 32768)
+    assert prune_path(L, p, 2047, 1e-3) == 1
+    assert prune_path(L, p, 8191, 1e-3) == 2
+    assert prune_path(L, p, 8191, 1e-3, with_scores=0) == 1      # no score scratch bound: the cluster kernel whenever it fits
+    assert prune_path(L, p, 32767, 0.0) == 1                     # torch rounding, every row kept: always the cluster kernel
+    capi.check(L.ffa_plan_set_prune_path(p, 2))
+    assert prune_path(L, p, 100, 1e-3) == 2
+    capi.check(L.ffa_plan_set_prune_path(p, 1))
+    assert prune_path(L, p, 32767, 1e-3) == 1
+    # a sequence no 8 slices can hold in shared memory: the streaming kernel, or nothing without the scratch
+    L, p = offline(capi.F32, 1, 1, 64, 2000000)
+    assert prune_path(L, p, 1999999, 1e-3) == 2
+    assert prune_path(L, p, 1999999, 1e-3, with_scores=0) == 0
