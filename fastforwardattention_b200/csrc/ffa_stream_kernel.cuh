@@ -13,16 +13,41 @@ __device__ __forceinline__ void merge_partials(const FfaStepParams& P, uint32_t 
                                                T* outp, int tid, int nthreads)
 {
     auto expo = [&](float x) -> float { return kPrecise ? expf(x) : fast_exp2(x); };
+    constexpr int kAtOnce = 4;   // partials whose loads are all issued before the first is used (a split pair rarely has more)
     float MM = -CUDART_INF_F;
-    for (int k = 0; k < count; ++k) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
+    if (count > kAtOnce)
+        for (int k = 0; k < count; ++k) MM = fmaxf(MM, __ldcg(pbase + (size_t)k * (DH + 2) + DH));
     for (int d = tid; d < DH; d += nthreads) {
         float A = 0.f, L = 0.f;
-        for (int k = 0; k < count; ++k) {
-            const float* pk = pbase + (size_t)k * (DH + 2);
-            const float mk = __ldcg(pk + DH);
-            const float w = mk == -CUDART_INF_F ? 0.f : expo(mk - MM);
-            A = fmaf(w, __ldcg(pk + d), A);
-            L = fmaf(w, __ldcg(pk + DH + 1), L);
+        if (count <= kAtOnce) {
+            // one trip to L2 instead of two: every partial's max, sum and element d are requested together
+            float mk[kAtOnce], lk[kAtOnce], ak[kAtOnce];
+#pragma unroll
+            for (int k = 0; k < kAtOnce; ++k) {
+                mk[k] = -CUDART_INF_F, lk[k] = 0.f, ak[k] = 0.f;
+                if (k < count) {
+                    const float* pk = pbase + (size_t)k * (DH + 2);
+                    mk[k] = __ldcg(pk + DH), lk[k] = __ldcg(pk + DH + 1), ak[k] = __ldcg(pk + d);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kAtOnce; ++k) MM = fmaxf(MM, mk[k]);
+#pragma unroll
+            for (int k = 0; k < kAtOnce; ++k) {   // slot order, as in the loop below
+                if (k < count) {
+                    const float w = mk[k] == -CUDART_INF_F ? 0.f : expo(mk[k] - MM);
+                    A = fmaf(w, ak[k], A);
+                    L = fmaf(w, lk[k], L);
+                }
+            }
+        } else {
+            for (int k = 0; k < count; ++k) {
+                const float* pk = pbase + (size_t)k * (DH + 2);
+                const float mk = __ldcg(pk + DH);
+                const float w = mk == -CUDART_INF_F ? 0.f : expo(mk - MM);
+                A = fmaf(w, __ldcg(pk + d), A);
+                L = fmaf(w, __ldcg(pk + DH + 1), L);
+            }
         }
         T o;
         Elem<T>::store(&o, L > 0.f ? A / L : 0.f);
@@ -385,18 +410,21 @@ __global__ void __launch_bounds__(DH == 80 ? 288 : 320, DH == 80 ? 1 : 2) ffa_st
             }
             if (cl && !whole) sent = true;
             if (!whole && !cl) {
-                // cross-CTA merge without waiting: whoever arrives last does it
-                __threadfence();
+                // cross-CTA merge without waiting: whoever arrives last does it.  The barrier orders every thread's
+                // partial stores before the first thread's fence, which publishes them with the ticket; its fence after
+                // the ticket and the second barrier order the other CTAs' partials before this CTA's reads (the chain a
+                // grid-wide barrier is built from).
                 named_bar_sync(1, nct);
                 const int c_first = cut.first_cta_of(bh), c_last = cut.last_cta_of(bh);
                 const int count = c_last - c_first + 1;
                 if (ctid == 0) {
+                    __threadfence();
                     const int old = atomicAdd(P.tickets + bh, 1);
+                    __threadfence();
                     flags[1] = (old == count - 1);
                 }
                 named_bar_sync(1, nct);
                 if (flags[1]) {
-                    __threadfence();
                     merge_partials<T, DH, kPrecise>(P, push_seq, bh, P.partials + (size_t)(c_first + bh) * (DH + 2), count, outp, ctid, nct);
                     if (ctid == 0) P.tickets[bh] = 0;  // ready for the next launch on this stream
                     wrote_out = true;
