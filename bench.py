@@ -262,15 +262,16 @@ def measure_config(name, dev, peak, mode=None, steps=32):
     return res
 
 
-def result_check(w, world, rank, engine, sharded, host_step, qkv_host, t, dev):
+def result_check(w, world, rank, engine, sharded, host_step, qkv_host, t, dev, same_dtype=False):
     """One step outside the timed regions, checked three ways: (N > 1) the gathered [B, H, Dh]
     holds this rank's own shard bit for bit and equals an NCCL all-gather of the same shards;
     the tensor the end-to-end step leaves in pinned host memory agrees with the per-call path;
     four sampled (batch, head) pairs of this rank's shard agree with the checker's float64
-    evaluation of softmax(q K^T scale) V over the cache rows 0..t."""
+    evaluation of softmax(q K^T scale) V over the cache rows 0..t (torch-rounding mode: with the
+    same function evaluated in the tensors' own dtype, which is what that mode reproduces)."""
     import torch.distributed as dist
 
-    from oracle.ffa_oracle import attention_reference, pruned_attention   # the checker, not the product
+    from oracle.ffa_oracle import attention_reference, pruned_attention, torch_attn_func   # the checker, not the product
 
     q, k, v = (qkv_host[i].to(dev) for i in range(3))
     local = engine.attention(q, k, v, w.scale, t, w.p)
@@ -301,13 +302,16 @@ def result_check(w, world, rank, engine, sharded, host_step, qkv_host, t, dev):
         Kp, Vp, qp = kc[b, h, :t + 1].cpu()[None], vc[b, h, :t + 1].cpu()[None], qkv_host[0][b, h]
         if w.p > 0:
             ref64 = pruned_attention(qp.view(1, w.Dh), Kp, Vp, w.scale, w.p)[0][0].double()   # the pruning rule, restated
+        elif same_dtype:
+            ref64 = torch_attn_func(qp.view(1, 1, w.Dh), Kp, Vp, w.scale)[0, 0].double()
         else:
             ref64 = attention_reference(qp.view(1, 1, w.Dh), Kp, Vp, w.scale, torch.float64)[0]
         worst = max(worst, (delivered[b, rank * w.H + h].double() - ref64).abs().max().item())
     tol = 1e-6 if w.dtype == torch.float32 else 2e-3
     res.update({"max_err": worst, "tolerance": tol, "pairs_checked_per_rank": 4,
-                "against": "float64 evaluation of softmax(q K^T scale) V on the cache rows" if w.p == 0 else
-                "the restated pruning rule on the cache rows"})
+                "against": "the restated pruning rule on the cache rows" if w.p > 0 else
+                "softmax(q K^T scale) V on the cache rows, evaluated by torch in the tensors' dtype" if same_dtype else
+                "float64 evaluation of softmax(q K^T scale) V on the cache rows"})
     res["ok"] = res["ok"] and worst <= tol
     return res
 
@@ -329,6 +333,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--workload", default="long-32768", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="exact", choices=["exact", "round_like_torch"],
+                    help="round_like_torch: the engine's torch-rounding mode (reproduces the rounding points of torch's same-dtype "
+                         "path; checked against that function instead of the float64 evaluation); single GPU, p = 0 workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the `configs` key (the other configurations, N = 1)")
     ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
@@ -338,6 +345,8 @@ def main():
     if args.impl == "reference":
         return run_reference(args, full)
 
+    if args.mode != "exact" and (args.gpus != 1 or full.p > 0):
+        raise SystemExit("--mode round_like_torch: single GPU and a workload without a pruning threshold")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -370,6 +379,8 @@ def main():
             engines.append(sharded[-1].engine)
         else:
             engines.append(FastForwardAttn(K, V, w.max_len, False))
+        if args.mode != "exact":
+            engines[-1].set_mode(args.mode)
         del K, V
     torch.cuda.empty_cache()
     gather_kind = "none"
@@ -493,7 +504,8 @@ def main():
         in_place_ms = timed_leg(in_place_step)
     # ---- outside every timed region: is what the end-to-end step delivers the right tensor? ----
     check = result_check(w, world, rank, engines[0], sharded[0] if world > 1 else None,
-                         host_steps[0] if host_steps is not None else None, qkv_h[args.warmup], w.prompt + 5, dev)
+                         host_steps[0] if host_steps is not None else None, qkv_h[args.warmup], w.prompt + 5, dev,
+                         same_dtype=args.mode != "exact")
     status = max(e.device_status() for e in engines)
 
     # ---- max over ranks ----
@@ -509,12 +521,13 @@ def main():
         peak, peak_kind = measured_peak()
         achieved = sum(alg) / (ksum_ms * 1e-3) / 1e9          # per GPU: this rank's bytes over its kernel time
         per_launch_alg = sum(alg) / len(alg)
-        kernel_name = ("ffa_stream_kernel (one-pass)" if w.p == 0 else
+        kernel_name = ("ffa_prune_cluster_kernel" if args.mode != "exact" else "ffa_stream_kernel (one-pass)" if w.p == 0 else
                        "ffa_prune_stream_kernel" if w.B * w.H * w.max_len * w.Dh * es >= 1e9 else "ffa_prune_cluster_kernel")
         line = {"metric": METRIC, "value": args.steps / (loop_ms * 1e-3), "unit": "steps/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": loop_ms / args.steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": DTYPE_NAME[w.dtype], "accumulate": "f32", "data": "synthetic", "config": workload_config(full, world),
+                "dtype": DTYPE_NAME[w.dtype], "accumulate": "f32", "data": "synthetic",
+                "config": dict(workload_config(full, world), **({} if args.mode == "exact" else {"mode": args.mode})),
                 "hbm_gbs_all_gpus": world * sum(alg) / (loop_ms * 1e-3) / 1e9,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
