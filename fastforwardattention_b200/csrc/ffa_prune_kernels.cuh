@@ -1,4 +1,4 @@
-// Pruning (and torch-rounding) at small sizes: the fused cluster kernel.
+// Pruning and torch-rounding steps whose slices' scores fit in shared memory: the fused cluster kernel.
 #pragma once
 #include "ffa_device_common.cuh"
 
@@ -14,8 +14,11 @@ namespace ffa_dev {
 // stores its (max, sum) into every peer's shared memory ahead of a cluster barrier, prunes and
 // gathers the V rows of its slice, and stores its partial output into CTA 0's shared memory ahead
 // of a second cluster barrier; CTA 0 adds the C partial outputs.  Nothing is loaded remotely.
-// No score scratch in HBM, no second launch, no arrival counters.  Used for small steps whose
-// slices' scores fit in shared memory; the streaming pruning kernel takes everything else.
+// No score scratch in HBM, no second launch, no arrival counters.  Where the rule prunes little
+// (45 % or more of a slice's first round survive) or nothing (the torch-rounding mode keeps every
+// row) the value phase is a second stream instead of a gather: the slice's V tiles follow its K
+// tiles through the ring and the rule decides row by row.  Used whenever the slices' scores fit in
+// shared memory, except for large pruned steps, which the streaming pruning kernel takes.
 //
 // Shared memory: [stages][K tile] ring | scores[chunk_rows] | kept list (row indices)
 // | ballot words | group reduction area [NG][DH + 4] | partial outputs [C][DH] | (max, sum) [8] | barriers | flags.
