@@ -11,15 +11,17 @@
 //   ffa_stream_kernel<T, DH>              p == 0: K and V tiles through a bulk-copy ring,
 //                                         online softmax, cross-CTA merge by the CTA that
 //                                         arrives last (no waiting), k/v append fused
-//   ffa_prune_stream_kernel<T, DH>        p > 0 at any size, one persistent launch: K tiles
+//   ffa_prune_stream_kernel<T, DH>        p > 0 on large steps, one persistent launch: K tiles
 //                                         through the ring, fp32 scores to scratch, global max
 //                                         and sum; gather warps test every cached row with the
 //                                         reference's pruning rule (attention.cu:1184-1191,
 //                                         461-469) and load only the V rows that survive, while
 //                                         the next pairs' K rows keep streaming
-//   ffa_prune_cluster_kernel<T, DH>       p > 0 at small sizes: a thread-block cluster per
-//                                         (batch, head), scores in shared memory, statistics
-//                                         and partial outputs over distributed shared memory
+//   ffa_prune_cluster_kernel<T, DH>       p > 0 on small and mid-size steps, and the torch-rounding
+//                                         mode: a thread-block cluster per (batch, head), scores in
+//                                         shared memory, statistics and partial outputs over
+//                                         distributed shared memory; surviving V rows gathered, or
+//                                         the V tiles streamed where little or nothing is pruned
 //   ffa_cache_init_kernel                 prompt K/V -> rows [0, prompt) of the caches
 //
 // One query row per head is a matrix-vector product (2 flops per cache element read), so the
